@@ -1,0 +1,319 @@
+"""Benchmark of the Llama-3 greedy-decode hot path on the CUDA device (and of the CPU reference arm).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                  [--model 8B] [--quant float16|int8] [--batch B] [--prompt P]
+
+A step is one decode step (one new token per batch row) of the whole model.  Default workload: Llama-3.1-8B
+architecture, fp16 weights ~N(0, 0.02) (seeded, generated on the device), batch 1, 512-token seeded prompt already
+in the KV cache, greedy decoding.  One JSON line is printed by rank 0:
+
+  value      decode tokens/s with everything resident in HBM: the captured step replays back to back and feeds its own
+             token back on the device (timed with CUDA events on the launching stream);
+  e2e        the same metric through the public per-token API: token ids and positions are copied up from page-locked
+             host memory, the step runs, the chosen ids are read back — every step, as the reference's chat loop does;
+  roofline   the dominant kernel (the weight-streaming matrix-vector kernel, timed alone on the gate/up projection
+             of every layer in turn) against the measured HBM copy bandwidth; `step` carries the same figure for the
+             whole decode step (all weights + KV read once per step);
+  cpu_baseline  the CPU restatement of the reference's CLANG path (oracle/), timed on this host's cores on a bounded
+             sample: full-width 1- and 4-layer slices of the same architecture, extrapolated linearly in depth.
+
+`--impl reference` times that CPU restatement as the reference arm (the reference itself needs a JS runtime and
+clang, neither of which exists here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_second"
+UNIT = "tok/s"
+
+
+def measured_peaks() -> tuple[float, str]:
+    """HBM GB/s denominator: the driver-measured copy bandwidth if present, else the stated fallback."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            self.proc.terminate()  # the exact child we started
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+            self.t.join(timeout=2)
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, col in (("hw_slowdown", 5), ("hw_thermal_slowdown", 6), ("sw_thermal_slowdown", 7), ("sw_power_cap", 8)):
+                if len(r) > col and r[col].lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ workload sizes
+def arch(model: str) -> dict:
+    from denograd_b200.llama3 import MODEL_PARAMS
+    return dict(MODEL_PARAMS[model]["args"]), MODEL_PARAMS[model]["tied"]
+
+
+def weight_bytes(p: dict, tied: bool, int8: bool) -> int:
+    """Bytes of weights one decode step streams: every projection once, the output matrix once (the embedding
+    gather touches one row per token)."""
+    d, hd = p["dim"], p["dim"] // p["n_heads"]
+    kv, f, V, L = p["n_kv_heads"] * hd, p["hidden_dim"], p["vocab_size"], p["n_layers"]
+    params = L * (2 * d * d + 2 * kv * d + 3 * f * d) + V * d
+    rows = L * (2 * d + 2 * kv + 2 * f + d) + V  # scale entries (one fp16 per output row) for int8
+    return params * (1 if int8 else 2) + (rows * 2 if int8 else 0) + L * 2 * d * 2 + d * 2  # + norm weights
+
+
+def kv_bytes_per_token(p: dict) -> int:
+    hd = p["dim"] // p["n_heads"]
+    return 2 * p["n_layers"] * p["n_kv_heads"] * hd * 2
+
+
+# ------------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample(model: str, int8: bool, steps: int, warmup: int) -> dict:
+    """Times the CPU restatement (oracle/) on full-width 1- and 4-layer slices of `model`, batch 1, and extrapolates
+    the per-token time of the full depth: t(L) = t_head + L * t_layer."""
+    from oracle import oracle as O  # the checker, used here only as the timed CPU baseline
+    from tests.util import build_oracle
+    from denograd_b200 import synth
+    p, tied = arch(model)
+    steps = max(6, min(steps, 48))
+    warmup = max(1, min(warmup, 4))
+    times = {}
+    for L in (1, 4):
+        q = dict(p); q["n_layers"] = L
+        m = build_oracle(q, max_context=warmup + steps + 8, max_batch=1, int8=int8, tied=tied)
+        toks = synth.prompt_tokens(warmup + steps, p["vocab_size"])
+        for i in range(warmup):
+            m.forward(toks[:, i:i + 1], i)
+        t0 = time.perf_counter()
+        for i in range(warmup, warmup + steps):
+            m.forward(toks[:, i:i + 1], i)
+        times[L] = (time.perf_counter() - t0) / steps
+        m.close()
+    t_layer = max((times[4] - times[1]) / 3.0, 1e-9)
+    t_head = max(times[1] - t_layer, 0.0)
+    t_full = t_head + p["n_layers"] * t_layer
+    cores = int(os.environ.get("OMP_NUM_THREADS") or os.cpu_count() or 1)
+    return {"value": 1.0 / t_full, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": (f"{model} architecture, batch 1: {steps} greedy steps each on full-width 1-layer and 4-layer slices "
+                       f"(embedding + layers + final norm + {p['vocab_size']}-row output), short context; "
+                       f"per-token time extrapolated to {p['n_layers']} layers as t_head + L*t_layer "
+                       f"(t_head {t_head * 1e3:.1f} ms, t_layer {t_layer * 1e3:.1f} ms); OpenMP over output rows on all "
+                       f"host cores (the reference's generated C itself is single-threaded)"),
+            "ms_per_token_est": t_full * 1e3}
+
+
+def run_reference(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    int8 = args.quant == "int8"
+    cb = cpu_sample(args.model, int8, args.steps, args.warmup)
+    p, tied = arch(args.model)
+    line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_token_est"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16 weights, f32 accumulate", "data": "synthetic",
+            "config": workload_config(args, p), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def workload_config(args, p) -> dict:
+    return {"workload": (f"Llama-3.1-{args.model} architecture greedy decode, {args.quant} weights, batch {args.batch}, "
+                         f"{args.prompt}-token seeded prompt in the KV cache"),
+            "batch": args.batch, "prompt_tokens": args.prompt, "weights": args.quant, "layers": p["n_layers"],
+            "l2": "inputs larger than L2: every step streams all weights (GBs) once, no flush needed",
+            "parallelism": "tp1" if args.gpus == 1 else f"{args.gpus} independent replicas"}
+
+
+# ------------------------------------------------------------------------------------------------ GPU arm
+def run_gpu(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from denograd_b200 import synth
+    from denograd_b200.device import Device, Tensor
+    from denograd_b200.llama3 import Llama3
+
+    int8 = args.quant == "int8"
+    p, tied = arch(args.model)
+    B, P, K, W = args.batch, args.prompt, args.steps, args.warmup
+    max_ctx = P + 2 * (K + W) + 16
+    max_ctx = (max_ctx + 63) // 64 * 64
+    dev_name = "CUDA" if local_rank == 0 else f"CUDA:{local_rank}"
+    llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=B, device=dev_name).load_synthetic()
+    dev = llm.model.dev
+    model = llm.model
+
+    def barrier():
+        dev.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64, device=f"cuda:{local_rank}")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- untimed set-up: the prompt goes through the model one position at a time (fills the KV cache)
+    prompt = synth.prompt_tokens(P, p["vocab_size"], batch=B, seed=synth.PROMPT_SEED + rank)
+    first = llm._prefill(prompt).numpy()
+    pos0 = llm.start_pos
+
+    # ---- value: device-resident loop (graph replay, token fed back on the device)
+    model.decode_loop(first, pos0, W, collect=False)  # warm-up steps (also captures the step)
+    barrier()
+    launches0 = dev.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        dev.timer_start()
+        model.decode_loop(first, pos0 + W, K, collect=False, resume=True)
+        secs = dev.timer_stop()
+        barrier()
+    launches = dev.launch_count() - launches0
+    secs = max_over_ranks(secs)
+    value = world * B * K / secs
+
+    # ---- e2e: public per-token API with host buffers (pinned H2D of ids + positions, D2H of the chosen ids)
+    llm.start_pos = pos0 + W + K
+    tok = model._workspace(B).next_tokens.numpy()
+    for _ in range(W):
+        tok = model.call_host(tok.reshape(B, 1), llm.start_pos); llm.start_pos += 1
+    barrier()
+    dev.timer_start()
+    for _ in range(K):
+        tok = model.call_host(tok.reshape(B, 1), llm.start_pos); llm.start_pos += 1
+    e2e_secs = max_over_ranks(dev.timer_stop())
+    barrier()
+    e2e_value = world * B * K / e2e_secs
+
+    # ---- roofline of the dominant kernel, timed alone: gate/up projection (norm + two matrices + SwiGLU) of every
+    #      layer in turn, so that consecutive launches never find their weights in L2
+    peak, peak_kind = measured_peaks()
+    ws = model._workspace(B)
+    d, f = p["dim"], p["hidden_dim"]
+
+    def gateup(layer):
+        ff = layer.feed_forward
+        dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, layer.ffn_norm.weight.ptr, layer.ffn_norm.eps, ff.w1.weight.ptr,
+                 ff.w1.scale_ptr, ff.w3.weight.ptr, ff.w3.scale_ptr, B, f, d)
+
+    for layer in model.layers:
+        gateup(layer)
+    dev.synchronize()
+    reps = max(1, 128 // len(model.layers))
+    dev.timer_start()
+    for _ in range(reps):
+        for layer in model.layers:
+            gateup(layer)
+    k_secs = dev.timer_stop() / (reps * len(model.layers))
+    k_bytes = 2 * f * d * (1 if int8 else 2) + (2 * f * 2 if int8 else 0) + B * d * 2 + d * 2 + B * f * 2
+    k_gbs = k_bytes / k_secs / 1e9
+
+    t_mid = pos0 + W + K / 2.0  # mean cached length over the timed steps
+    step_bytes = weight_bytes(p, tied, int8) + B * t_mid * kv_bytes_per_token(p) + B * d * 2
+    step_gbs = step_bytes / (secs / K) / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+        "ms_per_step": secs / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 activations, f32 accumulate, " + ("i8 weights" if int8 else "f16 weights"), "data": "synthetic",
+        "config": workload_config(args, p),
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 4 * B,
+                "ms_per_step": e2e_secs / K * 1e3},
+        "gpu_launches": int(launches),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (norm + gate/up + SwiGLU instantiation)", "achieved": k_gbs,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k_gbs / peak, "traffic": None,
+                     "bytes_per_launch": k_bytes, "us_per_launch": k_secs * 1e6,
+                     "step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak,
+                              "hbm_roofline_tok_s": B * peak * 1e9 / step_bytes}},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_sample(args.model, int8, 8, 2)
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="8B", choices=["1B", "3B", "8B", "70B"])
+    ap.add_argument("--quant", default="float16", choices=["float16", "int8"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

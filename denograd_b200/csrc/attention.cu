@@ -1,0 +1,472 @@
+// Paged KV cache, RoPE + cache write, and decode attention (one new token per batch row) with GQA head sharing.
+//
+// Attention follows Tensor.scaled_dot_product_attention as the reference graph computes it
+// (jsgrad/tensor.ts:3920-3934, softmax :2186-2214): fp32 scores = (q.k) * 1/sqrt(hd); e = exp2((s - max) * 1/ln2)
+// with the polynomial exp2; p = half(e * (1/sum e)); out = half(sum_t p_t * v_t) with fp32 accumulation.  Because
+// p is rounded to fp16 *after* normalisation, the context is processed in two kernels instead of one online-softmax
+// pass: (A) scores, per-split max and sum;  (B) probabilities from the global max/sum, p.v partials, and the
+// cross-split combine done by whichever CTA of a (row, kv head) finishes last (ticket counter, no spinning).
+// Scores and partials live in a scratch area owned by the cache object.
+//
+// One CTA serves one (context split, kv head, batch row) and all n_rep query heads that share the kv head
+// (repeat_kv: jsgrad/models/llama.ts:34-39, head h uses kv head h / n_rep), so K and V are read once per group.
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "transcendental.cuh"
+
+struct jg_kvcache {
+  jg_dev* dev;
+  jg_kvcache_desc d;
+  __half* k_pool;  // [L][n_pages][G][page][hd]
+  __half* v_pool;
+  int32_t* block_table;  // [max_batch][max_pages_per_seq]
+  float* scores;         // [max_batch][H][max_ctx]
+  float* part_ml;        // [max_batch][H][n_split][2]  (max, sum of exp relative to that max)
+  float* part_o;         // [max_batch][H][n_split][hd]
+  unsigned int* tickets; // [max_batch][G]
+  int n_split;
+  int max_ctx;
+  size_t layer_elems;  // elements of one layer of K (or V)
+  uint64_t bytes;
+};
+
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS = ATT_THREADS / 32;
+
+struct AttnArgs {
+  const __half* qkv;  // [B][qkv_stride], q heads first
+  const __half* k_layer;
+  const __half* v_layer;
+  const int32_t* block_table;
+  const int32_t* pos;  // [B]: index of the newest token; attends to [0, pos]
+  float* scores;
+  float* part_ml;
+  float* part_o;
+  unsigned int* tickets;
+  __half* out;  // [B][H*hd]
+  int qkv_stride, H, G, page, page_shift, max_pages_per_seq, n_split, max_ctx;
+  float scale;
+};
+
+// Context slice of split j: [t0, t1).  The same arithmetic is used by both kernels and the combine.
+__device__ __forceinline__ int attn_chunk(int T, int n_split) {
+  int c = (T + n_split - 1) / n_split;
+  c = (c + 31) & ~31;
+  return c < 32 ? 32 : c;
+}
+
+__device__ __forceinline__ const __half* kv_row(const __half* layer, const int32_t* bt_row, int t, int g, int G,
+                                                int page, int page_shift, int hd) {
+  const int pg = bt_row[t >> page_shift];
+  const int slot = t & (page - 1);
+  return layer + (((size_t)pg * G + g) * page + slot) * hd;
+}
+
+// ------------------------------------------------------------------------------------------------ kernel A
+template <int HD, int NREP>
+__global__ void __launch_bounds__(ATT_THREADS) attn_scores_kernel(const AttnArgs a) {
+  constexpr int LPR = HD / 8;    // lanes per K row (16 B each)
+  constexpr int RPW = 32 / LPR;  // rows per warp pass
+  constexpr int U = 4;           // row passes in flight
+  __shared__ float red[ATT_WARPS][NREP];
+  __shared__ float s_m[NREP];
+  const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane % LPR, rgrp = lane / LPR;
+  const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);  // positions outside the cache are clamped, never followed
+  const int chunk = attn_chunk(T, a.n_split);
+  const int t0 = j * chunk, t1 = min(T, t0 + chunk);
+  float* ml = a.part_ml + (((size_t)b * a.H + (size_t)g * NREP) * a.n_split + j) * 2;  // head r at + r*n_split*2
+  if (t0 >= t1) {
+    if (tid < NREP) { ml[(size_t)tid * a.n_split * 2 + 0] = -INFINITY; ml[(size_t)tid * a.n_split * 2 + 1] = 0.f; }
+    return;
+  }
+  const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
+
+  float qf[NREP][8];
+#pragma unroll
+  for (int r = 0; r < NREP; r++)
+    unpack8(ld_128(a.qkv + (size_t)b * a.qkv_stride + (size_t)(g * NREP + r) * HD + sub * 8), qf[r]);
+
+  float lmax[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) lmax[r] = -INFINITY;
+  float* srow = a.scores + ((size_t)b * a.H + (size_t)g * NREP) * a.max_ctx;  // head r at + r*max_ctx
+
+  // the trip count depends on the CTA's slice only, so every lane takes part in the shuffles below
+  for (int base = t0; base < t1; base += ATT_WARPS * RPW * U) {
+    const int tb = base + warp * RPW + rgrp;
+    uint4 kv[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+      kv[u] = (t < t1) ? ld_128(kv_row(a.k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8)
+                       : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        float p = dot8_acc(0.f, kv[u], qf[r]);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+        const float s = __fmul_rn(p, a.scale);
+        if (t < t1) {
+          lmax[r] = fmaxf(lmax[r], s);
+          if (sub == (r % LPR)) srow[(size_t)r * a.max_ctx + t] = s;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NREP; r++) {
+    float m = warp_max(lmax[r]);
+    if (lane == 0) red[warp][r] = m;
+  }
+  __syncthreads();
+  if (tid < NREP) {
+    float m = red[0][tid];
+    for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, red[w][tid]);
+    s_m[tid] = m;
+  }
+  __syncthreads();
+  // second pass over this split's scores: sum of exp relative to the split max
+  const float log2e = 1.4426950408889634f;
+  float lsum[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) lsum[r] = 0.f;
+  for (int t = t0 + tid; t < t1; t += ATT_THREADS) {
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+      lsum[r] = __fadd_rn(lsum[r], jg_xexp2_f32(__fmul_rn(__fsub_rn(srow[(size_t)r * a.max_ctx + t], s_m[r]), log2e)));
+  }
+  __syncthreads();  // red reuse
+#pragma unroll
+  for (int r = 0; r < NREP; r++) {
+    float s = warp_sum(lsum[r]);
+    if (lane == 0) red[warp][r] = s;
+  }
+  __syncthreads();
+  if (tid < NREP) {
+    float s = 0.f;
+    for (int w = 0; w < ATT_WARPS; w++) s += red[w][tid];
+    ml[(size_t)tid * a.n_split * 2 + 0] = s_m[tid];
+    ml[(size_t)tid * a.n_split * 2 + 1] = s;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ kernel B
+template <int HD, int NREP>
+__global__ void __launch_bounds__(ATT_THREADS) attn_pv_kernel(const AttnArgs a) {
+  constexpr int LPR = HD / 8;
+  constexpr int RPW = 32 / LPR;
+  constexpr int U = 4;
+  static_assert(NREP <= LPR, "one lane per query head of the group computes its probability");
+  __shared__ float s_M[NREP], s_rL[NREP];
+  __shared__ float part[ATT_WARPS][NREP][HD];
+  __shared__ int s_last;
+  const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane % LPR, rgrp = lane / LPR;
+  const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);  // positions outside the cache are clamped, never followed
+  const int chunk = attn_chunk(T, a.n_split);
+  const int n_active = (T + chunk - 1) / chunk;
+  const int t0 = j * chunk, t1 = min(T, t0 + chunk);
+  const size_t head0 = (size_t)b * a.H + (size_t)g * NREP;
+  const float log2e = 1.4426950408889634f;
+
+  if (t0 < t1) {
+    // global max and normaliser of each head from the per-split statistics: warp r handles head r
+    if (warp < NREP) {
+      const float* ml = a.part_ml + (head0 + warp) * a.n_split * 2;
+      float m = -INFINITY;
+      for (int s = lane; s < n_active; s += 32) m = fmaxf(m, ml[s * 2]);
+      m = warp_max(m);
+      float l = 0.f;
+      for (int s = lane; s < n_active; s += 32)
+        l = __fadd_rn(l, __fmul_rn(ml[s * 2 + 1], jg_xexp2_f32(__fmul_rn(__fsub_rn(ml[s * 2], m), log2e))));
+      l = warp_sum(l);
+      if (lane == 0) { s_M[warp] = m; s_rL[warp] = __fdiv_rn(1.0f, l); }
+    }
+    __syncthreads();
+
+    const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
+    const float* srow = a.scores + head0 * a.max_ctx;
+    const int my_r = sub < NREP ? sub : 0;
+    const float myM = s_M[my_r], myrL = s_rL[my_r];
+    float acc[NREP][8];
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
+
+    for (int base = t0; base < t1; base += ATT_WARPS * RPW * U) {
+      const int tb = base + warp * RPW + rgrp;
+      uint4 vv[U];
+      float pr[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int t = tb + u * ATT_WARPS * RPW;
+        const bool ok = t < t1;
+        vv[u] = ok ? ld_128(kv_row(a.v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8)
+                   : make_uint4(0, 0, 0, 0);
+        pr[u] = (ok && sub < NREP) ? srow[(size_t)my_r * a.max_ctx + t] : -INFINITY;
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        // p = half(e * 1/sum): lane `r` of each row group evaluates head r, then the group shares it
+        const float e = jg_xexp2_f32(__fmul_rn(__fsub_rn(pr[u], myM), log2e));
+        const float p = __half2float(__float2half_rn(__fmul_rn(e, myrL)));
+        float vf[8];
+        unpack8(vv[u], vf);
+#pragma unroll
+        for (int r = 0; r < NREP; r++) {
+          const float p_r = __shfl_sync(0xffffffffu, p, rgrp * LPR + r);
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[r][i] = fmaf(p_r, vf[i], acc[r][i]);
+        }
+      }
+    }
+    // fold the row groups of the warp, then the warps of the CTA
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+#pragma unroll
+        for (int o = 16; o >= LPR; o >>= 1) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], o);
+      }
+    if (rgrp == 0) {
+#pragma unroll
+      for (int r = 0; r < NREP; r++)
+#pragma unroll
+        for (int i = 0; i < 8; i++) part[warp][r][sub * 8 + i] = acc[r][i];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < NREP * HD; idx += ATT_THREADS) {
+      const int r = idx / HD, i = idx % HD;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < ATT_WARPS; w++) s += part[w][r][i];
+      a.part_o[((head0 + r) * a.n_split + j) * HD + i] = s;
+    }
+  }
+
+  // ---- ticket: the CTA that finishes last for this (row, kv head) sums the active splits in ascending order
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int ticket = atomicAdd(a.tickets + (size_t)b * a.G + g, 1u);
+    s_last = (ticket == (unsigned int)(a.n_split - 1));
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int idx = tid; idx < NREP * HD; idx += ATT_THREADS) {
+    const int r = idx / HD, i = idx % HD;
+    float s = 0.f;
+    for (int sp = 0; sp < n_active; sp++) s = __fadd_rn(s, __ldcg(a.part_o + ((head0 + r) * a.n_split + sp) * HD + i));
+    a.out[(size_t)b * a.H * HD + (size_t)(g * NREP + r) * HD + i] = __float2half_rn(s);
+  }
+  if (tid == 0) a.tickets[(size_t)b * a.G + g] = 0u;
+}
+
+// ------------------------------------------------------------------------------------------------ RoPE + cache write
+// apply_rotary_emb / complex_mult (jsgrad/models/llama.ts:17-32) on the interleaved pairs of Q and K, every op in
+// fp16; K and V of the new token go to their page (cache assign, jsgrad/models/llama.ts:87).
+// One thread handles 8 consecutive halves (4 pairs) of one head.
+__global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __restrict__ table,
+                                    const int32_t* __restrict__ pos, const int32_t* __restrict__ block_table,
+                                    __half* __restrict__ k_layer, __half* __restrict__ v_layer, int B, int H, int G,
+                                    int hd, int page, int page_shift, int max_pages_per_seq, int table_rows) {
+  const int per_head = hd / 8;
+  const int heads = H + 2 * G;
+  const long long total = (long long)B * heads * per_head;
+  for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < total; it += (long long)gridDim.x * blockDim.x) {
+    const int c = (int)(it % per_head);
+    const int h = (int)((it / per_head) % heads);
+    const int b = (int)(it / ((long long)per_head * heads));
+    const int p = pos[b];
+    if (p < 0 || p >= max_pages_per_seq * page || p >= table_rows) continue;  // out-of-range position: leave the row untouched
+    __half* src = qkv + ((size_t)b * heads + h) * hd + (size_t)c * 8;
+    uint4 raw = *reinterpret_cast<uint4*>(src);
+    if (h < H + G) {
+      uint4 traw = ld_128(table + ((size_t)p * (hd / 2) + (size_t)c * 4) * 2);
+      const __half* x = reinterpret_cast<const __half*>(&raw);
+      const __half* t = reinterpret_cast<const __half*>(&traw);
+      __align__(16) __half o[8];
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const __half xa = x[2 * i], xb = x[2 * i + 1], co = t[2 * i], si = t[2 * i + 1];
+        o[2 * i] = hsub1(hmul1(xa, co), hmul1(xb, si));
+        o[2 * i + 1] = hadd1(hmul1(xa, si), hmul1(xb, co));
+      }
+      raw = *reinterpret_cast<uint4*>(o);
+    }
+    if (h < H) {
+      *reinterpret_cast<uint4*>(src) = raw;
+    } else {
+      const int g = (h < H + G) ? (h - H) : (h - H - G);
+      __half* layer = (h < H + G) ? k_layer : v_layer;
+      const int pg = block_table[(size_t)b * max_pages_per_seq + (p >> page_shift)];
+      const int slot = p & (page - 1);
+      *reinterpret_cast<uint4*>(layer + (((size_t)pg * G + g) * page + slot) * hd + (size_t)c * 8) = raw;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+static int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
+
+JG_API int jg_kvcache_create(jg_dev* dev, const jg_kvcache_desc* desc, jg_kvcache** out) {
+  JG_ENTER(dev);
+  JG_REQUIRE(desc != nullptr && out != nullptr, "kvcache_create: null argument");
+  const jg_kvcache_desc& d = *desc;
+  JG_REQUIRE(d.n_layers > 0 && d.n_kv_heads > 0 && d.n_pages > 0 && d.max_batch > 0 && d.max_pages_per_seq > 0 && d.n_heads > 0,
+             "kvcache_create: non-positive dimension");
+  JG_REQUIRE(d.head_dim == 64 || d.head_dim == 128, "kvcache_create: head_dim %d not supported (64 or 128)", d.head_dim);
+  JG_REQUIRE(d.page_size == 16 || d.page_size == 32 || d.page_size == 64, "kvcache_create: page_size %d not in {16,32,64}", d.page_size);
+  JG_REQUIRE(d.n_heads % d.n_kv_heads == 0, "kvcache_create: n_heads %d not a multiple of n_kv_heads %d", d.n_heads, d.n_kv_heads);
+  const int n_rep = d.n_heads / d.n_kv_heads;
+  JG_REQUIRE(n_rep == 1 || n_rep == 2 || n_rep == 3 || n_rep == 4 || n_rep == 8, "kvcache_create: %d query heads per kv head not supported", n_rep);
+  JG_REQUIRE((long long)d.max_batch * d.max_pages_per_seq <= 0x7fffffffLL, "kvcache_create: block table too large");
+  jg_kvcache* kv = new jg_kvcache();
+  memset(kv, 0, sizeof(*kv));
+  kv->dev = dev;
+  kv->d = d;
+  kv->max_ctx = d.max_pages_per_seq * d.page_size;
+  int ns = d.n_split;
+  if (ns <= 0) {
+    ns = (2 * dev->sm_count + d.max_batch * d.n_kv_heads - 1) / (d.max_batch * d.n_kv_heads);
+    const int by_len = (kv->max_ctx + 63) / 64;  // no point in splits shorter than 64 positions at full length
+    if (ns > by_len) ns = by_len;
+  }
+  if (ns < 1) ns = 1;
+  if (ns > 64) ns = 64;
+  kv->n_split = ns;
+  kv->layer_elems = (size_t)d.n_pages * d.n_kv_heads * d.page_size * d.head_dim;
+  const size_t pool_bytes = kv->layer_elems * d.n_layers * sizeof(__half);
+  const size_t bt_bytes = (size_t)d.max_batch * d.max_pages_per_seq * sizeof(int32_t);
+  const size_t sc_bytes = (size_t)d.max_batch * d.n_heads * kv->max_ctx * sizeof(float);
+  const size_t ml_bytes = (size_t)d.max_batch * d.n_heads * ns * 2 * sizeof(float);
+  const size_t po_bytes = (size_t)d.max_batch * d.n_heads * ns * d.head_dim * sizeof(float);
+  const size_t tk_bytes = (size_t)d.max_batch * d.n_kv_heads * sizeof(unsigned int);
+  cudaError_t e = cudaSuccess;
+  if (e == cudaSuccess) e = cudaMalloc(&kv->k_pool, pool_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->v_pool, pool_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->block_table, bt_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->scores, sc_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->part_ml, ml_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->part_o, po_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&kv->tickets, tk_bytes);
+  if (e != cudaSuccess) {
+    jg_kvcache_destroy(kv);
+    return jg_cuda_fail(e, "cudaMalloc(kv cache)", __FILE__, __LINE__);
+  }
+  kv->bytes = 2 * pool_bytes + bt_bytes + sc_bytes + ml_bytes + po_bytes + tk_bytes;
+  // cache starts as zeros (Tensor.zeros, jsgrad/models/llama.ts:79); tickets must start at zero
+  JG_CUDA(cudaMemsetAsync(kv->k_pool, 0, pool_bytes, dev->stream));
+  JG_CUDA(cudaMemsetAsync(kv->v_pool, 0, pool_bytes, dev->stream));
+  JG_CUDA(cudaMemsetAsync(kv->tickets, 0, tk_bytes, dev->stream));
+  // identity block table: row b owns pages [b*mpps, (b+1)*mpps) as far as the pool reaches
+  int32_t* bt = (int32_t*)malloc(bt_bytes);
+  for (int b = 0; b < d.max_batch; b++)
+    for (int i = 0; i < d.max_pages_per_seq; i++) {
+      long long pg = (long long)b * d.max_pages_per_seq + i;
+      bt[(size_t)b * d.max_pages_per_seq + i] = (int32_t)(pg < d.n_pages ? pg : d.n_pages - 1);
+    }
+  cudaError_t e2 = cudaMemcpyAsync(kv->block_table, bt, bt_bytes, cudaMemcpyHostToDevice, dev->stream);
+  if (e2 == cudaSuccess) e2 = cudaStreamSynchronize(dev->stream);
+  free(bt);
+  if (e2 != cudaSuccess) {
+    jg_kvcache_destroy(kv);
+    return jg_cuda_fail(e2, "block table upload", __FILE__, __LINE__);
+  }
+  *out = kv;
+  return JG_OK;
+}
+
+JG_API int jg_kvcache_destroy(jg_kvcache* kv) {
+  if (!kv) return JG_OK;
+  cudaSetDevice(kv->dev->ordinal);
+  cudaStreamSynchronize(kv->dev->stream);
+  cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->block_table); cudaFree(kv->scores);
+  cudaFree(kv->part_ml); cudaFree(kv->part_o); cudaFree(kv->tickets);
+  delete kv;
+  return JG_OK;
+}
+
+JG_API int jg_kvcache_set_block_table(jg_kvcache* kv, const int32_t* table) {
+  JG_REQUIRE(kv != nullptr && table != nullptr, "kvcache_set_block_table: null argument");
+  JG_ENTER(kv->dev);
+  const size_t n = (size_t)kv->d.max_batch * kv->d.max_pages_per_seq;
+  for (size_t i = 0; i < n; i++)
+    JG_REQUIRE(table[i] >= 0 && table[i] < kv->d.n_pages, "kvcache_set_block_table: entry %zu = %d outside the pool of %d pages", i, table[i], kv->d.n_pages);
+  JG_CUDA(cudaMemcpyAsync(kv->block_table, table, n * sizeof(int32_t), cudaMemcpyHostToDevice, kv->dev->stream));
+  JG_CUDA(cudaStreamSynchronize(kv->dev->stream));
+  return JG_OK;
+}
+
+JG_API int jg_kvcache_bytes(jg_kvcache* kv, uint64_t* out) {
+  JG_REQUIRE(kv != nullptr && out != nullptr, "kvcache_bytes: null argument");
+  *out = kv->bytes;
+  return JG_OK;
+}
+
+JG_API int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table,
+                           int32_t table_rows, uint64_t pos, int32_t B, int32_t H) {
+  JG_ENTER(dev);
+  JG_REQUIRE(kv != nullptr && kv->dev == dev, "rope_kvwrite: cache belongs to another device");
+  JG_REQUIRE(layer >= 0 && layer < kv->d.n_layers, "rope_kvwrite: layer %d out of range", layer);
+  JG_REQUIRE(B > 0 && B <= kv->d.max_batch && H == kv->d.n_heads, "rope_kvwrite: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
+  JG_REQUIRE(jg_aligned(qkv, 16) && jg_aligned(table, 16) && jg_aligned(pos, 4), "rope_kvwrite: null or misaligned pointer");
+  const int G = kv->d.n_kv_heads, hd = kv->d.head_dim;
+  const long long total = (long long)B * (H + 2 * G) * (hd / 8);
+  int blocks = (int)((total + 127) / 128);
+  if (blocks > dev->sm_count * 8) blocks = dev->sm_count * 8;
+  rope_kvwrite_kernel<<<blocks, 128, 0, dev->stream>>>((__half*)qkv, (const __half*)table, (const int32_t*)pos, kv->block_table,
+                                                       kv->k_pool + kv->layer_elems * layer, kv->v_pool + kv->layer_elems * layer,
+                                                       B, H, G, hd, kv->d.page_size, ilog2(kv->d.page_size), kv->d.max_pages_per_seq, table_rows);
+  return jg_after_launch(dev, "rope_kvwrite");
+}
+
+template <int HD, int NREP>
+static int launch_attn(jg_dev* dev, const AttnArgs& a, int B) {
+  dim3 grid(a.n_split, a.G, B);
+  attn_scores_kernel<HD, NREP><<<grid, ATT_THREADS, 0, dev->stream>>>(a);
+  int rc = jg_after_launch(dev, "attn_scores");
+  if (rc) return rc;
+  attn_pv_kernel<HD, NREP><<<grid, ATT_THREADS, 0, dev->stream>>>(a);
+  return jg_after_launch(dev, "attn_pv");
+}
+
+JG_API int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos,
+                          int32_t B, int32_t H) {
+  JG_ENTER(dev);
+  JG_REQUIRE(kv != nullptr && kv->dev == dev, "attn_decode: cache belongs to another device");
+  JG_REQUIRE(layer >= 0 && layer < kv->d.n_layers, "attn_decode: layer %d out of range", layer);
+  JG_REQUIRE(B > 0 && B <= kv->d.max_batch && H == kv->d.n_heads, "attn_decode: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
+  JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(pos, 4), "attn_decode: null or misaligned pointer");
+  const int G = kv->d.n_kv_heads, hd = kv->d.head_dim, n_rep = H / G;
+  AttnArgs a = {};
+  a.qkv = (const __half*)qkv;
+  a.k_layer = kv->k_pool + kv->layer_elems * layer;
+  a.v_layer = kv->v_pool + kv->layer_elems * layer;
+  a.block_table = kv->block_table;
+  a.pos = (const int32_t*)pos;
+  a.scores = kv->scores; a.part_ml = kv->part_ml; a.part_o = kv->part_o; a.tickets = kv->tickets;
+  a.out = (__half*)out;
+  a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
+  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.n_split = kv->n_split; a.max_ctx = kv->max_ctx;
+  // 1/sqrt(hd) as the reference folds it: reciprocal of the fp32 constant sqrt(hd) (jsgrad/tensor.ts:3923)
+  a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));
+#define JG_ATT_CASE(HD_, NR_) if (hd == HD_ && n_rep == NR_) return launch_attn<HD_, NR_>(dev, a, B);
+  JG_ATT_CASE(64, 1) JG_ATT_CASE(64, 2) JG_ATT_CASE(64, 3) JG_ATT_CASE(64, 4) JG_ATT_CASE(64, 8)
+  JG_ATT_CASE(128, 1) JG_ATT_CASE(128, 2) JG_ATT_CASE(128, 3) JG_ATT_CASE(128, 4) JG_ATT_CASE(128, 8)
+#undef JG_ATT_CASE
+  jg_set_error("attn_decode: head_dim %d with %d query heads per kv head not supported", hd, n_rep);
+  return JG_ENOTSUP;
+}

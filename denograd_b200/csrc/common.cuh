@@ -1,0 +1,122 @@
+// Shared internals of libjsgrad_cuda: device object, error plumbing, small device helpers.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/jsgrad_cuda.h"
+
+#define JG_API extern "C" __attribute__((visibility("default")))
+
+struct jg_dev {
+  int ordinal;
+  cudaStream_t stream;
+  cudaDeviceProp prop;
+  int sm_count;
+  bool capturing;
+  uint64_t launches;          // kernels launched (graph replays add their node count)
+  uint64_t capture_launches;  // kernels recorded into the graph being captured
+  cudaEvent_t t0, t1;
+  void* pinned_stage;  // small page-locked staging area for jg_copyin of tiny payloads
+  size_t pinned_stage_bytes;
+};
+
+struct jg_graph {
+  cudaGraph_t graph;
+  cudaGraphExec_t exec;
+  uint64_t n_kernels;
+};
+
+void jg_set_error(const char* fmt, ...);
+int jg_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
+
+#define JG_CUDA(call)                                                        \
+  do {                                                                       \
+    cudaError_t _e = (call);                                                 \
+    if (_e != cudaSuccess) return jg_cuda_fail(_e, #call, __FILE__, __LINE__); \
+  } while (0)
+
+#define JG_REQUIRE(cond, ...)   \
+  do {                          \
+    if (!(cond)) {              \
+      jg_set_error(__VA_ARGS__); \
+      return JG_EINVAL;         \
+    }                           \
+  } while (0)
+
+// Makes `dev` current, and counts + checks a launch.  Used right after every <<<>>>.
+static inline int jg_after_launch(jg_dev* dev, const char* name) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return jg_cuda_fail(e, name, __FILE__, __LINE__);
+  if (dev->capturing) dev->capture_launches++;
+  else dev->launches++;
+  return JG_OK;
+}
+#define JG_ENTER(dev)                                              \
+  do {                                                             \
+    JG_REQUIRE((dev) != nullptr, "null device handle");            \
+    JG_CUDA(cudaSetDevice((dev)->ordinal));                        \
+  } while (0)
+
+static inline bool jg_aligned(uint64_t p, uint64_t a) { return p != 0 && (p % a) == 0; }
+
+// ------------------------------------------------------------------------------------------------ device side
+#ifdef __CUDACC__
+
+// 128-bit streaming load of read-only weights: bypass L1 allocation, they are read exactly once per launch.
+__device__ __forceinline__ uint4 ld_stream_128(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+// 128-bit cached load (activations, KV rows: L1/L2 resident or reused)
+__device__ __forceinline__ uint4 ld_128(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+
+__device__ __forceinline__ float2 h2_to_f2(uint32_t u) {
+  __half2 h = *reinterpret_cast<__half2*>(&u);
+  return __half22float2(h);
+}
+
+// exact fp16 x fp16 products accumulated in fp32 (an FMA of an exact product equals multiply-then-add)
+__device__ __forceinline__ float dot8_acc(float acc, const uint4& w, const float (&x)[8]) {
+  float2 a = h2_to_f2(w.x), b = h2_to_f2(w.y), c = h2_to_f2(w.z), d = h2_to_f2(w.w);
+  acc = fmaf(a.x, x[0], acc); acc = fmaf(a.y, x[1], acc);
+  acc = fmaf(b.x, x[2], acc); acc = fmaf(b.y, x[3], acc);
+  acc = fmaf(c.x, x[4], acc); acc = fmaf(c.y, x[5], acc);
+  acc = fmaf(d.x, x[6], acc); acc = fmaf(d.y, x[7], acc);
+  return acc;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&x)[8]) {
+  float2 a = h2_to_f2(v.x), b = h2_to_f2(v.y), c = h2_to_f2(v.z), d = h2_to_f2(v.w);
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// fp16 elementwise ops with exactly one rounding and no contraction into FMA.
+__device__ __forceinline__ __half hmul1(__half a, __half b) { return __hmul_rn(a, b); }
+__device__ __forceinline__ __half hadd1(__half a, __half b) { return __hadd_rn(a, b); }
+__device__ __forceinline__ __half hsub1(__half a, __half b) { return __hsub_rn(a, b); }
+__device__ __forceinline__ __half hrecip1(__half a) { return __float2half_rn(__fdiv_rn(1.0f, __half2float(a))); }
+
+// Order-preserving map of fp16 bits to uint16 (larger value -> larger key); NaNs are not expected.
+__device__ __forceinline__ uint32_t half_order_key(__half h) {
+  uint32_t u = __half_as_ushort(h);
+  return (u & 0x8000u) ? (~u & 0xFFFFu) : (u | 0x8000u);
+}
+// (value, lowest index) packed so that an unsigned max picks the largest value and, among equals, the smallest index
+__device__ __forceinline__ unsigned long long argmax_key(__half v, uint32_t idx) {
+  return ((unsigned long long)half_order_key(v) << 32) | (unsigned long long)(0xFFFFFFFFu - idx);
+}
+#endif

@@ -1,0 +1,331 @@
+"""The `CUDA` device: Python mirror of jsgrad's device plumbing for the hand-written sm_100a kernels.
+
+Same roles and names as the reference so that the model code above it reads like jsgrad's:
+  * ``CUDAAllocator``  — Allocator/LRUAllocator (jsgrad/runtime/allocator.ts:28-77): _alloc/_free/_copyin/_copyout/
+                          _offset/_transfer over uint64 device addresses;
+  * ``CUDA``           — Compiled (jsgrad/runtime/allocator.ts:166-191) registered under the name ``CUDA`` and looked
+                          up through ``Device[...]`` like jsgrad/device.ts:10-43;
+  * ``Buffer``         — jsgrad/device.ts:66-172 (allocate / view / copyin / copyout);
+  * ``Tensor``         — only the slice of jsgrad/tensor.ts the Llama path touches: a realized fp16/int8/int32 buffer
+                          with a shape.  There is no lazy graph here: every op is one of the library's kernels.
+  * ``CUDAGraph``      — the GraphRunner a TinyJit batch becomes (jsgrad/engine/jit.ts:71-141).
+All device work goes through the C ABI in ``ffi`` (no torch, no CPU fallback).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Sequence
+
+import numpy as np
+
+from . import ffi
+
+_DTYPE_SIZE = {"float16": 2, "int8": 1, "int32": 4, "float32": 4, "uint64": 8}
+_NP = {"float16": np.float16, "int8": np.int8, "int32": np.int32, "float32": np.float32, "uint64": np.uint64}
+
+
+class CUDAAllocator:
+    """LRU allocator over jg_alloc/jg_free (jsgrad/runtime/allocator.ts:53-77).  ``Buf`` is the device address."""
+
+    def __init__(self, dev: "CUDA"):
+        self.dev = dev  # BufferXfer reads `allocator.dev` on both sides (jsgrad/engine/realize.ts:126)
+        self.cache: dict[int, list[int]] = {}
+        self.allocated = 0
+
+    def alloc(self, size: int) -> int:
+        if size <= 0:
+            raise ValueError(f"alloc size must be positve, getting {size}")
+        c = self.cache.get(size)
+        if c:
+            return c.pop()
+        return self._alloc(size)
+
+    def free(self, opaque: int, size: int) -> None:
+        self.cache.setdefault(size, []).append(opaque)
+
+    def free_cache(self) -> None:
+        for bufs in self.cache.values():
+            for b in bufs:
+                self._free(b)
+        self.cache.clear()
+
+    def _alloc(self, size: int) -> int:
+        out = C.c_uint64(0)
+        try:
+            ffi.call("jg_alloc", self.dev.handle, size, C.byref(out))
+        except ffi.JgError as e:
+            if e.status != ffi.JG_ENOMEM or not self.cache:
+                raise
+            self.free_cache()  # LRUAllocator retries once after dropping its cache
+            ffi.call("jg_alloc", self.dev.handle, size, C.byref(out))
+        self.allocated += size
+        return out.value
+
+    def _free(self, opaque: int) -> None:
+        ffi.call("jg_free", self.dev.handle, opaque)
+
+    def _copyin(self, dest: int, src: np.ndarray) -> None:
+        src = np.ascontiguousarray(src)
+        ffi.call("jg_copyin", self.dev.handle, dest, src.ctypes.data_as(C.c_void_p), src.nbytes)
+
+    def _copyout(self, dest: np.ndarray, src: int) -> None:
+        assert dest.flags["C_CONTIGUOUS"]
+        ffi.call("jg_copyout", self.dev.handle, dest.ctypes.data_as(C.c_void_p), src, dest.nbytes)
+
+    @staticmethod
+    def _offset(buf: int, size: int, offset: int) -> int:
+        return buf + offset
+
+    def _transfer(self, dest: int, src: int, sz: int, src_dev: "CUDA", dest_dev: "CUDA") -> None:
+        ffi.call("jg_transfer", dest_dev.handle, dest, src_dev.handle, src, sz)
+
+
+class CUDA:
+    """Compiled device ``CUDA`` / ``CUDA:<n>``.  ``init`` is idempotent, as the engine awaits it before every use
+    (jsgrad/engine/realize.ts:133,157)."""
+
+    def __init__(self, device: str = "CUDA"):
+        self.device = device
+        self.ordinal = int(device.split(":")[1]) if ":" in device else 0
+        self.handle: C.c_void_p | None = None
+        self.allocator = CUDAAllocator(self)
+        self.props: ffi.Props | None = None
+
+    def init(self) -> "CUDA":
+        if self.handle is None:
+            ffi.load()
+            h = C.c_void_p()
+            ffi.call("jg_device_open", self.ordinal, C.byref(h))
+            self.handle = h
+            p = ffi.Props()
+            ffi.call("jg_device_props", self.handle, C.byref(p))
+            self.props = p
+        return self
+
+    def synchronize(self) -> None:
+        ffi.call("jg_device_sync", self.handle)
+
+    def launch_count(self) -> int:
+        out = C.c_uint64(0)
+        ffi.call("jg_launch_count", self.handle, C.byref(out))
+        return out.value
+
+    def timer_start(self) -> None:
+        ffi.call("jg_timer_start", self.handle)
+
+    def timer_stop(self) -> float:
+        s = C.c_double(0.0)
+        ffi.call("jg_timer_stop", self.handle, C.byref(s))
+        return s.value
+
+    def call(self, name: str, *args) -> None:
+        """Program.call: run one kernel entry point on this device's stream."""
+        ffi.call(name, self.handle, *args)
+
+    def close(self) -> None:
+        if self.handle is not None:
+            self.allocator.free_cache()
+            ffi.call("jg_device_close", self.handle)
+            self.handle = None
+
+
+class _DeviceRegistry:
+    """``Device['CUDA:1']`` (jsgrad/device.ts:10-43): canonicalise the name, open each device once."""
+
+    def __init__(self):
+        self._opened: dict[str, CUDA] = {}
+        self.DEFAULT = "CUDA"
+
+    @staticmethod
+    def canonicalize(device: str | None) -> str:
+        d = (device or "CUDA").upper()
+        name, _, ix = d.partition(":")
+        if name != "CUDA":
+            raise ValueError(f"unknown device {device!r}: this package registers the CUDA device only")
+        return "CUDA" if ix in ("", "0") else f"CUDA:{int(ix)}"
+
+    def __getitem__(self, device: str | None) -> CUDA:
+        ix = self.canonicalize(device)
+        if ix not in self._opened:
+            self._opened[ix] = CUDA(ix).init()
+        return self._opened[ix]
+
+    get = __getitem__
+
+
+Device = _DeviceRegistry()
+
+
+class Buffer:
+    """jsgrad/device.ts:66-172: a sized, typed region of device memory; ``view`` is an `_offset` sub-buffer."""
+
+    def __init__(self, device: str | CUDA, size: int, dtype: str, base: "Buffer | None" = None, offset: int = 0):
+        self.dev = device if isinstance(device, CUDA) else Device[device]
+        self.size, self.dtype = size, dtype
+        self.nbytes = size * _DTYPE_SIZE[dtype]
+        self.base, self.offset = base, offset
+        self._buf: int | None = None
+        if base is not None:
+            assert offset + self.nbytes <= base.nbytes, "view outside its base buffer"
+            self._buf = CUDAAllocator._offset(base.ptr, self.nbytes, offset)
+
+    def allocate(self) -> "Buffer":
+        if self._buf is None:
+            self._buf = self.dev.allocator.alloc(self.nbytes)
+        return self
+
+    @property
+    def ptr(self) -> int:
+        if self._buf is None:
+            self.allocate()
+        return self._buf
+
+    def view(self, size: int, dtype: str, offset: int) -> "Buffer":
+        return Buffer(self.dev, size, dtype, base=self.base or self, offset=(self.offset if self.base else 0) + offset)
+
+    def copyin(self, arr: np.ndarray) -> "Buffer":
+        arr = np.ascontiguousarray(arr)
+        if arr.nbytes != self.nbytes:
+            raise ValueError(f"size mismatch, src.nbytes={arr.nbytes} != self.nbytes={self.nbytes}")
+        self.dev.allocator._copyin(self.ptr, arr)
+        return self
+
+    def copyout(self, arr: np.ndarray) -> np.ndarray:
+        if arr.nbytes != self.nbytes:
+            raise ValueError(f"size mismatch, dst.nbytes={arr.nbytes} != self.nbytes={self.nbytes}")
+        self.dev.allocator._copyout(arr, self.ptr)
+        return arr
+
+    def __del__(self):
+        try:
+            if self.base is None and self._buf is not None and self.dev.handle is not None:
+                self.dev.allocator.free(self._buf, self.nbytes)
+        except Exception:
+            pass
+
+
+class Tensor:
+    """A realized tensor on the CUDA device (the subset of jsgrad/tensor.ts the Llama path needs)."""
+
+    def __init__(self, data, dtype: str | None = None, device: str | CUDA | None = None, shape: Sequence[int] | None = None):
+        if isinstance(data, Buffer):
+            self.buf, self.shape, self.dtype = data, tuple(shape), data.dtype
+            return
+        arr = np.asarray(data)
+        if dtype is not None:
+            arr = arr.astype(_NP[dtype])
+        dtype = {np.dtype(np.float16): "float16", np.dtype(np.int8): "int8", np.dtype(np.int32): "int32",
+                 np.dtype(np.float32): "float32", np.dtype(np.uint64): "uint64"}.get(arr.dtype)
+        if dtype is None:
+            raise TypeError(f"dtype {arr.dtype} is not used on the CUDA device's Llama path")
+        self.shape, self.dtype = tuple(arr.shape), dtype
+        self.buf = Buffer(device or Device.DEFAULT, int(arr.size), dtype).allocate()
+        self.buf.copyin(arr)
+
+    @staticmethod
+    def empty(shape: Sequence[int], dtype: str = "float16", device: str | CUDA | None = None) -> "Tensor":
+        n = int(math.prod(shape))
+        return Tensor(Buffer(device or Device.DEFAULT, n, dtype).allocate(), shape=shape)
+
+    @staticmethod
+    def zeros(shape: Sequence[int], dtype: str = "float16", device: str | CUDA | None = None) -> "Tensor":
+        t = Tensor.empty(shape, dtype, device)
+        ffi.call("jg_memset", t.dev.handle, t.ptr, 0, t.nbytes)
+        return t
+
+    @property
+    def dev(self) -> CUDA:
+        return self.buf.dev
+
+    @property
+    def device(self) -> str:
+        return self.buf.dev.device
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.ptr
+
+    @property
+    def nbytes(self) -> int:
+        return self.buf.nbytes
+
+    def numel(self) -> int:
+        return int(math.prod(self.shape))
+
+    def reshape(self, shape: Sequence[int]) -> "Tensor":
+        shape = list(shape)
+        if -1 in shape:
+            i = shape.index(-1)
+            shape[i] = self.numel() // int(-math.prod(shape))
+        assert math.prod(shape) == self.numel(), f"cannot reshape {self.shape} to {shape}"
+        return Tensor(self.buf, shape=shape)
+
+    def view_rows(self, start: int, stop: int) -> "Tensor":
+        """shrink on axis 0 of a contiguous tensor (an `_offset` sub-buffer, no copy)."""
+        row = self.numel() // self.shape[0]
+        b = self.buf.view((stop - start) * row, self.dtype, start * row * _DTYPE_SIZE[self.dtype])
+        return Tensor(b, shape=(stop - start,) + tuple(self.shape[1:]))
+
+    def assign(self, arr: np.ndarray) -> "Tensor":
+        self.buf.copyin(np.asarray(arr, dtype=_NP[self.dtype]).reshape(self.shape))
+        return self
+
+    def realize(self) -> "Tensor":
+        return self
+
+    def numpy(self) -> np.ndarray:
+        out = np.empty(self.shape, _NP[self.dtype])
+        self.buf.copyout(out)
+        return out
+
+    def item(self):
+        assert self.numel() == 1
+        return self.numpy().reshape(-1)[0].item()
+
+    def tolist(self):
+        return self.numpy().tolist()
+
+    def to(self, device: str | CUDA) -> "Tensor":
+        dst = device if isinstance(device, CUDA) else Device[device]
+        if dst is self.dev:
+            return self
+        out = Tensor.empty(self.shape, self.dtype, dst)
+        dst.allocator._transfer(out.ptr, self.ptr, self.nbytes, self.dev, dst)
+        return out
+
+
+class CUDAGraph:
+    """A captured kernel list replayed with one launch (GraphRunner, jsgrad/engine/jit.ts:71-141).  Values that
+    vary between replays are device-resident (tokens, positions), so nothing is patched at launch."""
+
+    def __init__(self, dev: CUDA):
+        self.dev = dev
+        self.handle: C.c_void_p | None = None
+
+    def __enter__(self) -> "CUDAGraph":
+        self.dev.call("jg_graph_begin")
+        return self
+
+    def __exit__(self, exc_type, exc, tb) -> bool:
+        h = C.c_void_p()
+        if exc_type is not None:
+            try:  # leave capture mode; the partial graph is discarded
+                ffi.call("jg_graph_end", self.dev.handle, C.byref(h))
+                ffi.call("jg_graph_destroy", h)
+            except ffi.JgError:
+                pass
+            return False
+        ffi.call("jg_graph_end", self.dev.handle, C.byref(h))
+        self.handle = h
+        return False
+
+    def launch(self) -> None:
+        ffi.call("jg_graph_launch", self.dev.handle, self.handle)
+
+    def __del__(self):
+        try:
+            if self.handle is not None and self.dev.handle is not None:
+                ffi.call("jg_graph_destroy", self.handle)
+        except Exception:
+            pass

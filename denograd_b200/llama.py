@@ -1,0 +1,399 @@
+"""Llama transformer on the CUDA device — Python mirror of jsgrad/models/llama.ts.
+
+Class and method names follow the reference (Attention, FeedForward, TransformerBlock, Transformer, TinyJit,
+precompute_freqs_cis, apply_rotary_emb, sample); each method issues the library's kernels through the C ABI instead of
+building a lazy graph.  Two ways through a block exist and compute the same values:
+
+  * the per-op path (``fused=False``): one kernel per reference op — RMSNorm, Linear x3, RoPE + cache write,
+    attention, Linear + add, RMSNorm, Linear x2, SiLU*mul, Linear + add;
+  * the fused path (default): RMSNorm folded into the QKV / gate-up / logits projections, residual adds and SwiGLU
+    folded into the projection epilogues, greedy selection folded into the logits kernel.
+
+A decode step (tokens [B,1], start_pos > 0) is captured once into a CUDA graph and replayed, the role TinyJit has
+in the reference (jsgrad/models/llama.ts:199,214-219, jsgrad/engine/jit.ts:236-353); `start_pos` and the tokens live
+in device memory so that the captured step serves every position.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import ffi
+from .device import CUDA, CUDAGraph, Device, Tensor
+from .nn import Embedding, Linear, RMSNorm, _dev
+
+
+def precompute_freqs_cis(dim: int, end: int, theta: float = 10000.0, device=None) -> Tensor:
+    """[end, dim/2, 2] table of (cos, sin), already cast to fp16 (jsgrad/models/llama.ts:10-14 and the cast at :205;
+    the reference shapes it [1, end, 1, dim/2, 2])."""
+    dev = _dev(device)
+    t = Tensor.empty((end, dim // 2, 2), "float16", dev)
+    dev.call("jg_freqs_cis", t.ptr, dim, end, float(theta))
+    return t
+
+
+class KVCache:
+    """The model's paged K/V pool (what Attention.cache_kv is per layer in the reference, jsgrad/models/llama.ts:78-90)."""
+
+    def __init__(self, dev: CUDA, n_layers: int, n_heads: int, n_kv_heads: int, head_dim: int, max_context: int,
+                 max_batch: int, page_size: int = 64, n_split: int = 0):
+        self.dev = dev
+        self.page_size = page_size
+        self.max_pages_per_seq = (max_context + page_size - 1) // page_size
+        self.n_pages = self.max_pages_per_seq * max_batch
+        self.max_batch = max_batch
+        d = ffi.KvDesc(n_layers, n_kv_heads, head_dim, page_size, self.n_pages, max_batch, self.max_pages_per_seq,
+                       n_heads, n_split)
+        self.handle = C.c_void_p()
+        ffi.call("jg_kvcache_create", dev.handle, C.byref(d), C.byref(self.handle))
+
+    def set_block_table(self, table: np.ndarray) -> None:
+        table = np.ascontiguousarray(table, dtype=np.int32)
+        assert table.shape == (self.max_batch, self.max_pages_per_seq), table.shape
+        ffi.call("jg_kvcache_set_block_table", self.handle, table.ctypes.data_as(C.c_void_p))
+
+    def nbytes(self) -> int:
+        out = C.c_uint64(0)
+        ffi.call("jg_kvcache_bytes", self.handle, C.byref(out))
+        return out.value
+
+    def close(self) -> None:
+        if self.handle:
+            ffi.call("jg_kvcache_destroy", self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            if self.dev.handle is not None:
+                self.close()
+        except Exception:
+            pass
+
+
+def apply_rotary_emb_kvwrite(qkv: Tensor, freqs_cis: Tensor, pos: Tensor, kv: KVCache, layer: int, n_heads: int) -> None:
+    """apply_rotary_emb on the Q and K slices of `qkv` plus the cache assignment (jsgrad/models/llama.ts:23-32,87)."""
+    qkv.dev.call("jg_rope_kvwrite", kv.handle, layer, qkv.ptr, freqs_cis.ptr, freqs_cis.shape[0], pos.ptr,
+                 qkv.numel() // qkv.shape[-1], n_heads)
+
+
+class Attention:
+    def __init__(self, dim: int, n_heads: int, n_kv_heads: int | None, max_context: int, linear=Linear, device=None):
+        self.n_heads = n_heads
+        self.n_kv_heads = n_kv_heads if n_kv_heads is not None else n_heads
+        self.head_dim = dim // n_heads
+        self.n_rep = self.n_heads // self.n_kv_heads
+        self.max_context = max_context
+        dev = _dev(device)
+        q_out, kv_out = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim
+        # wq|wk|wv share one allocation so that the three projections run as one pass over contiguous rows (the
+        # reference's WQKV option concatenates them the same way, jsgrad/models/llama.ts:63-66); each Linear's
+        # weight is a row view of it.
+        self._wqkv = linear(dim, q_out + 2 * kv_out, False, device=dev)
+        w = self._wqkv.weight
+        views = [w.view_rows(0, q_out), w.view_rows(q_out, q_out + kv_out), w.view_rows(q_out + kv_out, q_out + 2 * kv_out)]
+        if hasattr(self._wqkv, "scale"):
+            s = self._wqkv.scale
+            sv = [s.view_rows(0, q_out), s.view_rows(q_out, q_out + kv_out), s.view_rows(q_out + kv_out, q_out + 2 * kv_out)]
+            self.wq = linear(dim, q_out, False, weight=views[0], scale=sv[0])
+            self.wk = linear(dim, kv_out, False, weight=views[1], scale=sv[1])
+            self.wv = linear(dim, kv_out, False, weight=views[2], scale=sv[2])
+        else:
+            self.wq = linear(dim, q_out, False, weight=views[0])
+            self.wk = linear(dim, kv_out, False, weight=views[1])
+            self.wv = linear(dim, kv_out, False, weight=views[2])
+        self.wo = linear(q_out, dim, False, device=dev)
+        self._kv: KVCache | None = None
+        self._layer = 0
+
+    def call(self, x: Tensor, pos: Tensor, freqs_cis: Tensor, mask=None, residual: Tensor | None = None,
+             out: Tensor | None = None, qkv: Tensor | None = None, attn: Tensor | None = None) -> Tensor:
+        """x: already-normalised rows [B, 1, dim]; pos: device int32 [B] (the `start_pos` variable)."""
+        if mask is not None:
+            raise NotImplementedError("multi-token calls are fed one position at a time on this device")
+        B = x.numel() // x.shape[-1]
+        xqkv = self._wqkv.call(x, out=qkv)  # xq | xk | xv
+        apply_rotary_emb_kvwrite(xqkv, freqs_cis, pos, self._kv, self._layer, self.n_heads)
+        a = attn if attn is not None else Tensor.empty((B, self.n_heads * self.head_dim), "float16", x.dev)
+        x.dev.call("jg_attn_decode", self._kv.handle, self._layer, a.ptr, xqkv.ptr, pos.ptr, B, self.n_heads)
+        return self.wo.call(a, residual=residual, out=out)
+
+    __call__ = call
+
+
+class FeedForward:
+    def __init__(self, dim: int, hidden_dim: int, linear=Linear, device=None):
+        self.w1 = linear(dim, hidden_dim, False, device=device)
+        self.w2 = linear(hidden_dim, dim, False, device=device)
+        self.w3 = linear(dim, hidden_dim, False, device=device)  # the gate in Gated Linear Unit
+
+    def call(self, x: Tensor, residual: Tensor | None = None, out: Tensor | None = None) -> Tensor:
+        g, u = self.w1.call(x), self.w3.call(x)
+        x.dev.call("jg_swiglu", g.ptr, g.ptr, u.ptr, g.numel())  # w1(x).silu() * w3(x), in place on g
+        return self.w2.call(g, residual=residual, out=out)
+
+    __call__ = call
+
+
+class TransformerBlock:
+    def __init__(self, dim: int, hidden_dim: int, n_heads: int, n_kv_heads: int | None, norm_eps: float, max_context: int,
+                 linear=Linear, feed_forward=FeedForward, device=None):
+        self.attention = Attention(dim, n_heads, n_kv_heads, max_context, linear, device=device)
+        self.feed_forward = feed_forward(dim, hidden_dim, linear, device=device)
+        self.attention_norm = RMSNorm(dim, norm_eps, device=device)
+        self.ffn_norm = RMSNorm(dim, norm_eps, device=device)
+
+    def call(self, x: Tensor, pos: Tensor, freqs_cis: Tensor, mask=None) -> Tensor:
+        """Per-op path: h = x + attention(attention_norm(x)); return h + feed_forward(ffn_norm(h))."""
+        h = self.attention.call(self.attention_norm.call(x), pos, freqs_cis, mask, residual=x)
+        return self.feed_forward.call(self.ffn_norm.call(h), residual=h)
+
+    def call_fused(self, ws: "_Workspace", pos: Tensor, freqs_cis: Tensor) -> None:
+        """Same block on the workspace `ws` (h is updated in place) with the norms and elementwise ops folded into
+        the projection kernels."""
+        a, f, dev, B = self.attention, self.feed_forward, ws.h.dev, ws.B
+        d = ws.h.shape[-1]
+        wqkv = a._wqkv
+        dev.call("jg_norm_linear", ws.qkv.ptr, ws.h.ptr, self.attention_norm.weight.ptr, self.attention_norm.eps,
+                 wqkv.weight.ptr, wqkv.scale_ptr, B, wqkv.out_features, d)
+        apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
+        dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
+        a.wo.call(ws.attn, residual=ws.h, out=ws.h)
+        dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
+                 f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
+        f.w2.call(ws.ffn, residual=ws.h, out=ws.h)
+
+    __call__ = call
+
+
+def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float) -> Tensor:
+    """Greedy branch of `sample` (jsgrad/models/llama.ts:131-137): argmax with the lowest index among equals, per
+    row.  The stochastic branches (top-k / top-p / alpha penalties) are not part of this device's path."""
+    if temp >= 1e-6:
+        raise NotImplementedError("only temperature < 1e-6 (greedy) is implemented on the CUDA device path")
+    rows = logits.numel() // logits.shape[-1]
+    out = Tensor.empty((rows,), "int32", logits.dev)
+    logits.dev.call("jg_argmax", out.ptr, logits.ptr, rows, logits.shape[-1])
+    return out
+
+
+class _Workspace:
+    """Activation buffers of one decode step for a fixed batch size (what the memory planner would assign,
+    jsgrad/engine/memory.ts:8-58): reused by every layer and every step, so a captured step never allocates."""
+
+    def __init__(self, dev: CUDA, B: int, dim: int, qkv_dim: int, q_dim: int, hidden: int, vocab: int):
+        self.B = B
+        self.tokens = Tensor.zeros((B,), "int32", dev)
+        self.pos = Tensor.zeros((B,), "int32", dev)
+        self.h = Tensor.empty((B, dim), "float16", dev)
+        self.qkv = Tensor.empty((B, qkv_dim), "float16", dev)
+        self.attn = Tensor.empty((B, q_dim), "float16", dev)
+        self.ffn = Tensor.empty((B, hidden), "float16", dev)
+        self.logits = Tensor.empty((B, vocab), "float16", dev)
+        self.key = Tensor.zeros((B,), "uint64", dev)
+        self.next_tokens = Tensor.zeros((B,), "int32", dev)
+        # page-locked staging for the per-step token / position upload and the result read-back
+        self._pinned = C.c_void_p()
+        ffi.call("jg_host_alloc", 3 * 4 * B, C.byref(self._pinned))
+        arr = np.ctypeslib.as_array((C.c_int32 * (3 * B)).from_address(self._pinned.value))
+        self.h_tokens, self.h_pos, self.h_next = arr[:B], arr[B:2 * B], arr[2 * B:]
+
+    def __del__(self):
+        try:
+            if self._pinned:
+                ffi.call("jg_host_free", self._pinned)
+        except Exception:
+            pass
+
+
+class TinyJit:
+    """Call 0 runs eagerly, call 1 runs while being captured, later calls replay the capture
+    (jsgrad/engine/jit.ts:273-353).  The wrapped function must read its varying inputs from device memory."""
+
+    def __init__(self, fxn, dev: CUDA):
+        self.fxn, self.dev = fxn, dev
+        self.cnt = 0
+        self.graph: CUDAGraph | None = None
+
+    def reset(self) -> None:
+        self.cnt, self.graph = 0, None
+
+    def call(self, *args):
+        if self.cnt == 0:
+            self.fxn(*args)
+        elif self.cnt == 1:
+            g = CUDAGraph(self.dev)
+            with g:
+                self.fxn(*args)
+            self.graph = g
+            g.launch()  # a captured launch list has not run yet
+        else:
+            self.graph.launch()
+        self.cnt += 1
+
+    __call__ = call
+
+
+class Transformer:
+    def __init__(self, dim: int, hidden_dim: int, n_heads: int, n_layers: int, norm_eps: float, vocab_size: int,
+                 linear=Linear, embedding=Embedding, n_kv_heads: int | None = None, rope_theta: float = 10000,
+                 max_context: int = 1024, jit: bool = True, feed_forward=FeedForward, device=None, max_batch: int = 1,
+                 page_size: int = 64, tied_output: bool = False, fused: bool = True, n_split: int = 0):
+        dev = _dev(device)
+        self.dev, self.dim, self.hidden_dim, self.vocab_size = dev, dim, hidden_dim, vocab_size
+        self.n_heads, self.n_kv_heads = n_heads, (n_kv_heads if n_kv_heads is not None else n_heads)
+        self.head_dim = dim // n_heads
+        self.max_context, self.max_batch, self.fused = max_context, max_batch, fused
+        self.layers = [TransformerBlock(dim, hidden_dim, n_heads, n_kv_heads, norm_eps, max_context, linear, feed_forward, device=dev)
+                       for _ in range(n_layers)]
+        self.norm = RMSNorm(dim, norm_eps, device=dev)
+        self.tok_embeddings = embedding(vocab_size, dim, device=dev)
+        if tied_output:
+            # output.weight is the embedding table itself (Llama-3.2 1B/3B; for quantised embeddings the reference
+            # ties them as well, jsgrad/models/llama3.ts:55-58)
+            if embedding is Embedding:
+                self.output = Linear(dim, vocab_size, False, weight=self.tok_embeddings.weight)
+            else:
+                self.output = linear(dim, vocab_size, False, weight=self.tok_embeddings.weight, scale=self.tok_embeddings.scale)
+        else:
+            self.output = Linear(dim, vocab_size, False, device=dev) if embedding is Embedding else linear(dim, vocab_size, False, device=dev)
+        self.freqs_cis = precompute_freqs_cis(self.head_dim, self.max_context * 2, rope_theta, device=dev)
+        self._kv = KVCache(dev, n_layers, n_heads, self.n_kv_heads, self.head_dim, max_context, max_batch, page_size, n_split)
+        for i, layer in enumerate(self.layers):
+            layer.attention._kv, layer.attention._layer = self._kv, i
+        self._ws: dict[int, _Workspace] = {}
+        self._jit_enabled = jit
+        self._forward_jit: dict[int, TinyJit] = {}
+        self._loop_graph: dict[int, CUDAGraph] = {}
+
+    # ------------------------------------------------------------------------------------------ internals
+    def _workspace(self, B: int) -> _Workspace:
+        if B > self.max_batch:
+            raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
+        if B not in self._ws:
+            qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+            self._ws[B] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim, self.vocab_size)
+        return self._ws[B]
+
+    def _step(self, ws: _Workspace, advance: bool = False) -> None:
+        """One token per row: reads ws.tokens / ws.pos, writes ws.logits and ws.next_tokens.  With `advance` the step
+        also feeds its own output back (tokens <- next, pos += 1) so that it can be replayed with no host input."""
+        dev, B = self.dev, ws.B
+        self.tok_embeddings.call(ws.tokens, out=ws.h)
+        if self.fused:
+            for layer in self.layers:
+                layer.call_fused(ws, ws.pos, self.freqs_cis)
+            out = self.output
+            dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.h.ptr, self.norm.weight.ptr, self.norm.eps,
+                     out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
+            dev.call("jg_argmax_finalize", ws.next_tokens.ptr, ws.key.ptr, B)
+        else:
+            h = ws.h
+            for layer in self.layers:
+                h = layer.call(h, ws.pos, self.freqs_cis, None)
+            self.output.call(self.norm.call(h), out=ws.logits)
+            dev.call("jg_argmax", ws.next_tokens.ptr, ws.logits.ptr, B, self.vocab_size)
+        if advance:
+            dev.call("jg_copy", ws.tokens.ptr, ws.next_tokens.ptr, 4 * B)
+            dev.call("jg_pos_advance", ws.pos.ptr, B)
+
+    # ------------------------------------------------------------------------------------------ reference API
+    def forward(self, tokens, start_pos: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 0.8,
+                alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:
+        """Transformer.forward (jsgrad/models/llama.ts:201-213), eager.  tokens: int32 [B, S] (host array or Tensor).
+        Positions are processed one at a time, each attending to the cache up to itself — what the reference's
+        additive causal mask computes for S > 1, and how its own prefill feeds prompts
+        (jsgrad/models/llama3.ts:307-311).  Returns the greedy next token of every row ([B] int32)."""
+        if temperature >= 1e-6:
+            raise NotImplementedError("only greedy decoding (temperature < 1e-6) is implemented on the CUDA device path")
+        toks = tokens.numpy() if isinstance(tokens, Tensor) else np.asarray(tokens, dtype=np.int32)
+        B, S = toks.shape
+        if start_pos + S > self.max_context:
+            raise ValueError(f"start_pos {start_pos} + {S} tokens exceeds max_context {self.max_context}")
+        ws = self._workspace(B)
+        for s in range(S):
+            ws.tokens.assign(toks[:, s])
+            ws.pos.assign(np.full((B,), start_pos + s, np.int32))
+            self._step(ws)
+        return ws.next_tokens
+
+    def call(self, tokens, start_pos: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 0.8,
+             alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:
+        """Transformer.call (jsgrad/models/llama.ts:214-220): single-token calls after position 0 go through the jit."""
+        toks = tokens.numpy() if isinstance(tokens, Tensor) else np.asarray(tokens, dtype=np.int32)
+        B, S = toks.shape
+        if S == 1 and self._jit_enabled and start_pos != 0:
+            if temperature >= 1e-6:
+                raise NotImplementedError("only greedy decoding (temperature < 1e-6) is implemented on the CUDA device path")
+            if start_pos + 1 > self.max_context:
+                raise ValueError(f"start_pos {start_pos} + 1 exceeds max_context {self.max_context}")
+            ws = self._workspace(B)
+            ws.tokens.assign(toks[:, 0])
+            ws.pos.assign(np.full((B,), start_pos, np.int32))
+            if B not in self._forward_jit:
+                self._forward_jit[B] = TinyJit(lambda: self._step(ws), self.dev)
+            self._forward_jit[B].call()
+            return ws.next_tokens
+        return self.forward(toks, start_pos, temperature, top_k, top_p, alpha_f, alpha_p)
+
+    __call__ = call
+
+    def call_host(self, tokens: np.ndarray, start_pos: int) -> np.ndarray:
+        """`call(...)` followed by reading the ids back (`.item()` in the reference's loop), for one new token per
+        row after position 0, with the copies staged through page-locked memory: per step B*8 bytes go up (tokens and
+        positions), the captured step runs, B*4 bytes come back.  tokens: int32 [B, 1] -> int32 [B]."""
+        B = tokens.shape[0]
+        if start_pos == 0 or not self._jit_enabled:
+            return self.call(tokens, start_pos).numpy()
+        if start_pos + 1 > self.max_context:
+            raise ValueError(f"start_pos {start_pos} + 1 exceeds max_context {self.max_context}")
+        ws = self._workspace(B)
+        ws.h_tokens[:] = tokens.reshape(B)
+        ws.h_pos[:] = start_pos
+        dev = self.dev
+        dev.call("jg_copyin_async", ws.tokens.ptr, ws.h_tokens.ctypes.data, 4 * B)
+        dev.call("jg_copyin_async", ws.pos.ptr, ws.h_pos.ctypes.data, 4 * B)
+        if B not in self._forward_jit:
+            self._forward_jit[B] = TinyJit(lambda: self._step(ws), self.dev)
+        self._forward_jit[B].call()
+        dev.call("jg_copyout_async", ws.h_next.ctypes.data, ws.next_tokens.ptr, 4 * B)
+        dev.synchronize()
+        return ws.h_next.copy()
+
+    # ------------------------------------------------------------------------------------------ device-resident loop
+    def decode_loop(self, first_tokens, start_pos: int, n_steps: int, collect: bool = True,
+                    resume: bool = False) -> np.ndarray | None:
+        """Greedy-decode `n_steps` tokens per row with no host round trip between steps: the captured step feeds its
+        own output back on the device.  Returns the generated ids [B, n_steps] (read back after the last step), or
+        None when `collect` is false.  With `resume` the tokens and positions already on the device (left by the
+        previous loop) are continued and `first_tokens` only gives the batch size; nothing is copied or synchronised,
+        so a caller can time a run of steps with events."""
+        toks = np.asarray(first_tokens, dtype=np.int32).reshape(-1)
+        B = toks.shape[0]
+        if start_pos + n_steps > self.max_context:
+            raise ValueError(f"start_pos {start_pos} + {n_steps} steps exceeds max_context {self.max_context}")
+        ws = self._workspace(B)
+        if not resume:
+            ws.tokens.assign(toks)
+            ws.pos.assign(np.full((B,), start_pos, np.int32))
+        if B not in self._loop_graph:
+            if resume:
+                raise ValueError("nothing to resume: run decode_loop once without `resume` first")
+            self._step(ws, advance=True)  # eager once (sizes smem attributes), then restore the inputs and capture
+            ws.tokens.assign(toks)
+            ws.pos.assign(np.full((B,), start_pos, np.int32))
+            g = CUDAGraph(self.dev)
+            with g:
+                self._step(ws, advance=True)
+            self._loop_graph[B] = g
+        g = self._loop_graph[B]
+        hist = Tensor.empty((n_steps, B), "int32", self.dev) if collect else None
+        for i in range(n_steps):
+            g.launch()
+            if collect:
+                self.dev.call("jg_copy", hist.ptr + 4 * B * i, ws.next_tokens.ptr, 4 * B)
+        return hist.numpy().T.copy() if collect else None
+
+    def last_logits(self, B: int) -> np.ndarray:
+        """fp16 logits of the last step widened to fp32 (`.float()` at jsgrad/models/llama.ts:210), [B, vocab]."""
+        return self._workspace(B).logits.numpy().astype(np.float32)

@@ -1,0 +1,123 @@
+"""Llama3 driver on the CUDA device — Python mirror of jsgrad/models/llama3.ts (MODEL_PARAMS :119-132, the Llama3
+class :170-338) for the parts on the forward path: construction per size / quantisation, weight loading into the
+device, token-at-a-time prefill and greedy generation.  Tokenizer, chat templating and checkpoint download are not
+part of this path (the workloads use seeded token ids and seeded weights).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import synth
+from .device import Device, Tensor
+from .llama import Transformer
+from .nn import Embedding, Int8Embedding, Int8Linear, Linear, load_state_dict
+
+MODEL_PARAMS = {
+    "1B": {"args": {"dim": 2048, "n_heads": 32, "n_kv_heads": 8, "n_layers": 16, "norm_eps": 1e-5, "rope_theta": 500000,
+                    "vocab_size": 128256, "hidden_dim": 8192}, "files": 1, "tied": True},
+    # not in the reference's table; Llama-3.2-3B architecture as the 3B workload states it
+    "3B": {"args": {"dim": 3072, "n_heads": 24, "n_kv_heads": 8, "n_layers": 28, "norm_eps": 1e-5, "rope_theta": 500000,
+                    "vocab_size": 128256, "hidden_dim": 8192}, "files": 1, "tied": True},
+    "8B": {"args": {"dim": 4096, "n_heads": 32, "n_kv_heads": 8, "n_layers": 32, "norm_eps": 1e-5, "rope_theta": 500000,
+                    "vocab_size": 128256, "hidden_dim": 14336}, "files": 1, "tied": False},
+    "70B": {"args": {"dim": 8192, "n_heads": 64, "n_kv_heads": 8, "n_layers": 80, "norm_eps": 1e-5, "rope_theta": 500000,
+                     "vocab_size": 128256, "hidden_dim": 28672}, "files": 8, "tied": False},
+}
+
+
+@dataclass
+class Llama3Usage:
+    """jsgrad/models/llama3.ts:159-164."""
+    input_tokens: int = 0
+    output_tokens: int = 0
+    time_to_first_token: float = 0.0
+    tokens_per_second: float = 0.0
+
+
+@dataclass
+class Llama3:
+    """``Llama3(size=..., quantize=...)`` builds the Transformer with the reference's class injection
+    (Int8Linear / Int8Embedding for 'int8', jsgrad/models/llama3.ts:190-200).  ``temperature`` defaults to 0 here:
+    only the greedy branch of `sample` runs on this device (the reference's default of 0.95 selects the stochastic
+    branch, which is outside this path)."""
+    size: str = "1B"
+    quantize: str | None = "float16"  # 'float16' | 'int8'
+    max_context: int = 8192
+    device: str | None = None
+    temperature: float = 0.0
+    max_batch: int = 1
+    page_size: int = 64
+    fused: bool = True
+    jit: bool = True
+    n_layers: int | None = None  # override the depth (reduced-depth slices of a big architecture for checks)
+    tied_output: bool | None = None
+    args: dict = field(default_factory=dict)
+    last_seen_toks: list = field(default_factory=list)
+
+    def __post_init__(self):
+        if self.quantize not in ("float16", "int8", None):
+            raise NotImplementedError(f"quantize={self.quantize!r}: only 'float16' and 'int8' are on this device path")
+        p = dict(MODEL_PARAMS[self.size]["args"])
+        p.update(self.args)
+        if self.n_layers is not None:
+            p["n_layers"] = self.n_layers
+        self.params = p
+        int8 = self.quantize == "int8"
+        self.linear = Int8Linear if int8 else Linear
+        self.embedding = Int8Embedding if int8 else Embedding
+        self.quantize_embeds = int8
+        tied = MODEL_PARAMS[self.size]["tied"] if self.tied_output is None else self.tied_output
+        self.model = Transformer(p["dim"], p["hidden_dim"], p["n_heads"], p["n_layers"], p["norm_eps"], p["vocab_size"],
+                                 self.linear, self.embedding, p["n_kv_heads"], p["rope_theta"], self.max_context, self.jit,
+                                 device=Device[self.device], max_batch=self.max_batch, page_size=self.page_size,
+                                 tied_output=tied, fused=self.fused)
+        self.usage = Llama3Usage()
+        self.start_pos = 0
+
+    # ---- weights
+    def load_state_dict(self, weights: dict[str, np.ndarray]) -> "Llama3":
+        """Host arrays -> device tensors by name, non-strict like the reference (jsgrad/models/llama3.ts:258-260)."""
+        load_state_dict(self.model, weights, strict=False)
+        return self
+
+    def load_synthetic(self, seed: int = synth.BASE_SEED) -> "Llama3":
+        synth.fill_model(self.model, seed)
+        return self
+
+    # ---- generation
+    def reset(self) -> None:
+        self.start_pos, self.last_seen_toks = 0, []
+
+    def _prefill(self, toks: np.ndarray) -> Tensor:
+        """Feed prompt tokens one position at a time (Llama3._prefill, jsgrad/models/llama3.ts:307-311); returns the
+        greedy token after the last prompt position.  toks: int32 [B, n]."""
+        out = None
+        for i in range(toks.shape[1]):
+            out = self.model.call(toks[:, i:i + 1], self.start_pos, self.temperature)
+            self.start_pos += 1
+        return out
+
+    def generate(self, prompt: np.ndarray, max_new_tokens: int) -> np.ndarray:
+        """Greedy continuation through the public per-token API: every step copies the token ids to the device, runs
+        the (graph-replayed) step and reads the chosen ids back — the `.item()` round trip of the reference's chat
+        loop (jsgrad/models/llama3.ts:284-295,334-337).  prompt: int32 [B, n] -> int32 [B, max_new_tokens]."""
+        prompt = np.asarray(prompt, dtype=np.int32)
+        if prompt.ndim == 1:
+            prompt = prompt[None, :]
+        B = prompt.shape[0]
+        st = time.perf_counter()
+        tok = self._prefill(prompt).numpy()
+        self.usage.time_to_first_token = time.perf_counter() - st
+        out = np.empty((B, max_new_tokens), np.int32)
+        st = time.perf_counter()
+        for i in range(max_new_tokens):
+            out[:, i] = tok
+            if i + 1 < max_new_tokens:
+                tok = self.model.call_host(tok.reshape(B, 1), self.start_pos)
+                self.start_pos += 1
+        self.usage.input_tokens, self.usage.output_tokens = int(prompt.size), int(out.size)
+        self.usage.tokens_per_second = out.size / max(time.perf_counter() - st, 1e-9)
+        return out

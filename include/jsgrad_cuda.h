@@ -1,0 +1,184 @@
+/*
+ * jsgrad_cuda.h — C ABI of libjsgrad_cuda.so, the native half of a `CUDA` device for jsgrad.
+ *
+ * The TypeScript half (class CUDA extends Compiled, with its Allocator / Program / graph runner) binds exactly
+ * these symbols through Deno.dlopen, the way jsgrad/runtime/ops_clang.ts:40-54 binds one generated C function
+ * and dawn/bindings.ts binds libwebgpu_dawn.  Everything crosses the boundary as plain integers and pointers:
+ *   - a device buffer is a uint64_t device address (the engine's opaque `Buf`); sub-buffers are address + offset;
+ *   - host memory is a `const void*` / `void*` (Deno 'buffer' / 'pointer');
+ *   - every function returns an int status: 0 on success, an errno-style code otherwise, with the message
+ *     available from jg_last_error() (the TypeScript side turns a non-zero status into `throw new Error(...)`,
+ *     the reference's own convention: jsgrad/runtime/ops_clang.ts:34-35,42).
+ *
+ * All kernels of one device are issued on that device's single stream, in call order (the engine awaits each
+ * device call in program order: jsgrad/engine/realize.ts:215-218, jsgrad/engine/jit.ts:214).  Only
+ * jg_copyout, jg_device_sync and jg_timer_stop block the calling thread.
+ *
+ * Built for sm_100a only.  There is no CPU fallback: if the library cannot open a CUDA device every entry point
+ * fails with JG_EIO.
+ */
+#ifndef JSGRAD_CUDA_H
+#define JSGRAD_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define JG_OK 0
+#define JG_EIO 5         /* a CUDA runtime call failed (message in jg_last_error) */
+#define JG_ENOMEM 12     /* device or pinned-host allocation failed */
+#define JG_EINVAL 22     /* rejected before any launch: bad pointer, size, alignment or unsupported shape */
+#define JG_ENOTSUP 95    /* shape outside what the kernels implement */
+#define JG_ETIMEDOUT 110 /* a bounded device-side wait gave up */
+
+typedef struct jg_dev jg_dev;         /* one opened CUDA device + its stream */
+typedef struct jg_graph jg_graph;     /* a captured, replayable list of launches */
+typedef struct jg_kvcache jg_kvcache; /* paged K/V pool of one model on one device */
+typedef struct jg_comm jg_comm;       /* tensor-parallel communicator of one rank */
+
+/* ---- Compiled: jsgrad/runtime/allocator.ts:166-191 (ctor/init/synchronize), device lookup
+ *      jsgrad/device.ts:26-35 (`new DEVICES['CUDA']('CUDA:3')`: the ordinal is parsed from the device name). */
+typedef struct {
+  char name[64];
+  int32_t sm_count;
+  int32_t cc_major, cc_minor;
+  uint64_t total_mem;
+  uint64_t l2_bytes;
+  int32_t max_smem_per_block;
+} jg_props;
+
+int jg_device_count(int32_t* out);
+int jg_device_open(int32_t ordinal, jg_dev** out);
+int jg_device_close(jg_dev* dev);
+int jg_device_sync(jg_dev* dev);
+int jg_device_props(jg_dev* dev, jg_props* out);
+const char* jg_last_error(void);
+/* Kernels launched by this library on `dev` since it was opened (launches replayed through a graph count each
+ * time the graph runs).  Bookkeeping for DEBUG-style statistics, cf. GlobalCounters.kernel_count
+ * (jsgrad/helpers/helpers.ts:556-563). */
+int jg_launch_count(jg_dev* dev, uint64_t* out);
+
+/* ---- Allocator: jsgrad/runtime/allocator.ts:28-47 (_alloc/_free/_copyin/_copyout/_offset/_transfer). */
+int jg_alloc(jg_dev* dev, size_t nbytes, uint64_t* dptr);
+int jg_free(jg_dev* dev, uint64_t dptr);
+int jg_copyin(jg_dev* dev, uint64_t dst, const void* host, size_t nbytes);  /* host buffer reusable on return */
+int jg_copyout(jg_dev* dev, void* host, uint64_t src, size_t nbytes);       /* synchronises the stream */
+int jg_transfer(jg_dev* dst_dev, uint64_t dst, jg_dev* src_dev, uint64_t src, size_t nbytes); /* peer copy */
+int jg_memset(jg_dev* dev, uint64_t dst, int32_t byte, size_t nbytes);
+int jg_copy(jg_dev* dev, uint64_t dst, uint64_t src, size_t nbytes);  /* device-to-device on dev's stream */
+/* Page-locked host staging (BufferSpec.host, jsgrad/runtime/allocator.ts:8-25): copies from/to it are truly
+ * asynchronous. */
+int jg_host_alloc(size_t nbytes, void** out);
+int jg_host_free(void* p);
+int jg_copyin_async(jg_dev* dev, uint64_t dst, const void* pinned_host, size_t nbytes);
+int jg_copyout_async(jg_dev* dev, void* pinned_host, uint64_t src, size_t nbytes);
+
+/* ---- Program.call(..., wait): jsgrad/runtime/allocator.ts:98-107, jsgrad/runtime/ops_clang.ts:51-53.
+ *      `wait=true` is start -> calls -> stop; stop blocks and returns the elapsed device time in seconds. */
+int jg_timer_start(jg_dev* dev);
+int jg_timer_stop(jg_dev* dev, double* seconds);
+
+/* ---- Compiled.graph / GraphRunner: jsgrad/engine/jit.ts:14-144 (batching of a captured kernel list) and
+ *      CapturedJit replay jsgrad/engine/jit.ts:190-217.  Between begin and end every launch on `dev` is recorded
+ *      instead of executed; launch replays the list.  Values that change between replays (tokens, positions —
+ *      the jit's `start_pos` Variable, jsgrad/models/llama.ts:217) live in device memory and are read by the
+ *      kernels at run time, so a replay needs no patching. */
+int jg_graph_begin(jg_dev* dev);
+int jg_graph_end(jg_dev* dev, jg_graph** out);
+int jg_graph_launch(jg_dev* dev, jg_graph* g);
+int jg_graph_destroy(jg_graph* g);
+
+/* ---- Kernels.  Shapes: M = rows of activations (batch x new tokens), weights are [N][K] row-major
+ *      (nn.Linear layout, jsgrad/nn/index.ts:403-412).  `scale` = 0 selects fp16 weights; otherwise `w` is int8
+ *      and `scale` is the fp16 per-output-row scale of Int8Linear (jsgrad/models/llama3.ts:27-35).
+ *      All activation tensors are fp16, densely packed. */
+
+/* Embedding.call / Int8Embedding.call: jsgrad/nn/index.ts:607-619, jsgrad/models/llama3.ts:71-77.
+ * tokens: int32[n_tok] in device memory. */
+int jg_embed(jg_dev* dev, uint64_t out, uint64_t tokens, uint64_t w, uint64_t scale, int32_t n_tok, int32_t dim,
+             int32_t vocab);
+
+/* RMSNorm.call: jsgrad/nn/index.ts:586-588. */
+int jg_rmsnorm(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, int32_t rows, int32_t dim, float eps);
+
+/* Linear.call / Int8Linear.call: jsgrad/nn/index.ts:411, jsgrad/models/llama3.ts:35; `residual` (0 = none) is
+ * the `x.add(...)` of TransformerBlock.call, jsgrad/models/llama.ts:125-126, fused as an epilogue. */
+int jg_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, uint64_t scale, uint64_t residual, int32_t M,
+              int32_t N, int32_t K);
+
+/* RMSNorm followed by Linear on the same rows (attention_norm -> wq|wk|wv, ffn_norm -> w1/w3, norm -> output:
+ * jsgrad/models/llama.ts:125-126,210) as one kernel; the norm is over K. */
+int jg_norm_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t norm_w, float eps, uint64_t w, uint64_t scale,
+                   int32_t M, int32_t N, int32_t K);
+
+/* FeedForward.call up to the elementwise product: y = silu(norm(x) W1^T) * (norm(x) W3^T),
+ * jsgrad/models/llama.ts:108-110 + jsgrad/tensor.ts:2909-2911,3210-3226.  norm_w = 0 skips the norm. */
+int jg_norm_swiglu(jg_dev* dev, uint64_t y, uint64_t x, uint64_t norm_w, float eps, uint64_t w_gate,
+                   uint64_t s_gate, uint64_t w_up, uint64_t s_up, int32_t M, int32_t N, int32_t K);
+
+/* Elementwise silu(g) * u on already-computed projections (same source lines). */
+int jg_swiglu(jg_dev* dev, uint64_t y, uint64_t g, uint64_t u, int64_t n);
+
+/* Final norm + output projection for M rows + greedy selection: writes the fp16 logits [M][V] and folds
+ * (value, lowest index) into key[M] (uint64 each, must be zero on entry); jg_argmax_finalize turns the keys into
+ * int32 token ids and re-zeroes them.  jsgrad/models/llama.ts:210-212,137; jsgrad/tensor.ts:2314-2320. */
+int jg_norm_logits_argmax(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
+                          uint64_t w, uint64_t scale, int32_t M, int32_t V, int32_t K);
+int jg_argmax_finalize(jg_dev* dev, uint64_t tokens_out, uint64_t key, int32_t M);
+/* Tensor.argmax over the last axis of fp16 [rows][n]: jsgrad/tensor.ts:2314-2320. */
+int jg_argmax(jg_dev* dev, uint64_t out_idx, uint64_t x, int32_t rows, int32_t n);
+
+/* precompute_freqs_cis cast to fp16: jsgrad/models/llama.ts:10-14,205. table: fp16 [end][head_dim/2][2]. */
+int jg_freqs_cis(jg_dev* dev, uint64_t table, int32_t head_dim, int32_t end, double theta);
+
+/* ---- KV cache (Attention.cache_kv, jsgrad/models/llama.ts:78-90) held as a paged pool: per layer
+ *      K and V are [n_pages][n_kv_heads][page_size][head_dim] fp16; block_table[b][i] names the page holding
+ *      positions [i*page_size, (i+1)*page_size) of batch row b.  The layout is private to the device. */
+typedef struct {
+  int32_t n_layers, n_kv_heads, head_dim;
+  int32_t page_size;      /* tokens per page: 16, 32 or 64 */
+  int32_t n_pages;        /* pages in the pool (shared by all batch rows) */
+  int32_t max_batch;
+  int32_t max_pages_per_seq;
+  int32_t n_heads;        /* query heads served by this cache (sizes the attention scratch) */
+  int32_t n_split;        /* context splits per (batch row, kv head) in decode attention; 0 = choose */
+} jg_kvcache_desc;
+
+int jg_kvcache_create(jg_dev* dev, const jg_kvcache_desc* desc, jg_kvcache** out);
+int jg_kvcache_destroy(jg_kvcache* kv);
+/* host int32 [max_batch][max_pages_per_seq]; the default after create is the identity mapping
+ * (row b owns pages b*max_pages_per_seq ...). */
+int jg_kvcache_set_block_table(jg_kvcache* kv, const int32_t* table);
+int jg_kvcache_bytes(jg_kvcache* kv, uint64_t* out);
+
+/* apply_rotary_emb on Q and K + cache assignment (jsgrad/models/llama.ts:23-32,87) for S=1 rows:
+ * qkv: fp16 [B][(H + 2G) * hd] = wq|wk|wv outputs; Q is rotated in place, rotated K and V go to the cache at
+ * position pos[b] (device int32[B], the `start_pos` variable).  table: [table_rows][hd/2][2] from jg_freqs_cis;
+ * a row whose position lies outside the table or the cache is skipped. */
+int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table, int32_t table_rows,
+                    uint64_t pos, int32_t B, int32_t H);
+
+/* scaled_dot_product_attention for one new token per row over positions [0, pos[b]] with repeat_kv head
+ * sharing (jsgrad/tensor.ts:3920-3934,2186-2214; jsgrad/models/llama.ts:34-39,89-96).
+ * q is read from qkv ([B][(H+2G)*hd], first H*hd of each row); out: fp16 [B][H*hd]. */
+int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos,
+                   int32_t B, int32_t H);
+
+/* pos[b] += 1 for b < B (the host-side `start_pos++` of the decode loop, jsgrad/models/llama3.ts:284-295,
+ * kept on the device so a captured step can be replayed without host input). */
+int jg_pos_advance(jg_dev* dev, uint64_t pos, int32_t B);
+
+/* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the
+ *      workloads replace by fixed distributions).  Counter-based, so any sub-range can be generated. */
+int jg_fill_normal_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float std);
+int jg_fill_uniform_i8(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n);
+int jg_fill_scale_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float base);
+int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* JSGRAD_CUDA_H */

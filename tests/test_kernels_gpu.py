@@ -1,0 +1,256 @@
+"""GPU parity of each kernel against the CPU checker, through the C ABI (via the package's ctypes binding).
+
+Bars: integer / index / elementwise-fp16 work is bit-exact (the device restates the reference's op-by-op fp16 and
+polynomial arithmetic); reductions accumulate in fp32 in a different order than the checker's sequential loop, so
+their fp16 outputs may differ by at most one fp16 unit in the last place, on a small fraction of the elements.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from denograd_b200 import ffi, synth
+from denograd_b200.device import Tensor
+from denograd_b200.llama import KVCache, precompute_freqs_cis
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def ulp_diff(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Distance in fp16 units in the last place (monotonic integer mapping of the bit patterns)."""
+    def key(x):
+        u = np.ascontiguousarray(x, dtype=np.float16).view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, -(u & 0x7FFF), u)
+    return np.abs(key(a) - key(b))
+
+
+def assert_reduction_close(got, ref, max_ulp=1, max_frac=0.03, what=""):
+    assert got.shape == ref.shape
+    assert np.isfinite(got.astype(np.float32)).all(), what
+    d = ulp_diff(got, ref)
+    # near zero an "ulp" is tiny; there fall back to an absolute bound of one ulp of the row scale
+    scale = np.maximum(np.abs(ref.astype(np.float32)).max(), 1e-6)
+    bad = (d > max_ulp) & (np.abs(got.astype(np.float32) - ref.astype(np.float32)) > scale * 2.0 ** -10)
+    assert not bad.any(), f"{what}: {bad.sum()} elements differ by more than {max_ulp} ulp (max {d.max()})"
+    assert (d > 0).mean() <= max_frac, f"{what}: {(d > 0).mean():.4f} of the elements differ"
+
+
+# ------------------------------------------------------------------------------------------------ bit-exact kernels
+def test_seeded_fills_match_cpu_generator(dev):
+    n = 100_003
+    t = Tensor.empty((n,), "float16", dev)
+    dev.call("jg_fill_normal_f16", t.ptr, 77, 5, n, 0.02)
+    assert (t.numpy().view(np.uint16) == O.synth_normal_f16(77, n, 0.02, first=5).view(np.uint16)).all()
+    q = Tensor.empty((n,), "int8", dev)
+    dev.call("jg_fill_uniform_i8", q.ptr, 78, 0, n)
+    assert (q.numpy() == O.synth_uniform_i8(78, n)).all()
+    s = Tensor.empty((n,), "float16", dev)
+    dev.call("jg_fill_scale_f16", s.ptr, 79, 11, n, synth.INT8_SCALE_BASE)
+    assert (s.numpy().view(np.uint16) == O.synth_scale_f16(79, n, synth.INT8_SCALE_BASE, first=11).view(np.uint16)).all()
+    dev.call("jg_fill_const_f16", s.ptr, n, 1.0)
+    assert (s.numpy() == 1.0).all()
+
+
+@pytest.mark.parametrize("hd,end", [(64, 512), (128, 16384)])
+def test_freqs_cis_bit_exact(dev, hd, end):
+    got = precompute_freqs_cis(hd, end, 500000.0, dev).numpy()
+    ref = O.freqs_cis(hd, end, 500000.0)
+    assert (got.view(np.uint16) == ref.view(np.uint16)).all()
+
+
+def test_embedding_gather(dev):
+    rng = np.random.default_rng(0)
+    V, d = 777, 256
+    w = rng.standard_normal((V, d)).astype(np.float16)
+    idx = np.array([[0, 776, 5], [5, 13, 400]], np.int32)
+    out = Tensor.empty((2, 3, d), "float16", dev)
+    dev.call("jg_embed", out.ptr, Tensor(idx, device=dev).ptr, Tensor(w, device=dev).ptr, 0, idx.size, d, V)
+    assert (out.numpy() == O.embed_f16(idx, w)).all()
+    wq = rng.integers(-127, 128, (V, d), dtype=np.int8)
+    s = (rng.uniform(0.5, 1.5, V) * 3e-4).astype(np.float16)
+    dev.call("jg_embed", out.ptr, Tensor(idx, device=dev).ptr, Tensor(wq, device=dev).ptr, Tensor(s, device=dev).ptr, idx.size, d, V)
+    assert (out.numpy().view(np.uint16) == O.embed_w8(idx, wq, s).view(np.uint16)).all()
+    # an index outside the table selects no row: zeros, as the reference's one-hot sum gives
+    bad = np.array([V, -1], np.int32)
+    out2 = Tensor.empty((2, d), "float16", dev)
+    dev.call("jg_embed", out2.ptr, Tensor(bad, device=dev).ptr, Tensor(w, device=dev).ptr, 0, 2, d, V)
+    assert (out2.numpy() == 0).all()
+
+
+def test_swiglu_elementwise_bit_exact(dev):
+    g = np.concatenate([np.linspace(-40, 40, 8000), [0.0, -0.0, 65504, -65504, 1e-7, 23, -23, 22.5]]).astype(np.float16)
+    u = np.resize(np.linspace(-3, 3, 97).astype(np.float16), g.shape)
+    y = Tensor.empty(g.shape, "float16", dev)
+    dev.call("jg_swiglu", y.ptr, Tensor(g, device=dev).ptr, Tensor(u, device=dev).ptr, g.size)
+    assert (y.numpy().view(np.uint16) == O.swiglu(g, u).view(np.uint16)).all()
+
+
+def test_argmax_lowest_index(dev):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((3, 128256)).astype(np.float16)
+    x[0, [70000, 90000]] = 9.0
+    x[1, :] = -1.0
+    x[2, 128255] = 11.0
+    out = Tensor.empty((3,), "int32", dev)
+    dev.call("jg_argmax", out.ptr, Tensor(x, device=dev).ptr, 3, x.shape[1])
+    assert out.numpy().tolist() == [70000, 0, 128255]
+    assert out.numpy().tolist() == [O.argmax_f16(r) for r in x]
+
+
+# ------------------------------------------------------------------------------------------------ reductions
+def test_rmsnorm(dev):
+    rng = np.random.default_rng(2)
+    for rows, d in [(1, 2048), (5, 3072), (2, 8192)]:
+        x = (rng.standard_normal((rows, d)) * 1.7).astype(np.float16)
+        w = rng.uniform(0.5, 1.5, d).astype(np.float16)
+        y = Tensor.empty((rows, d), "float16", dev)
+        dev.call("jg_rmsnorm", y.ptr, Tensor(x, device=dev).ptr, Tensor(w, device=dev).ptr, rows, d, 1e-5)
+        assert_reduction_close(y.numpy(), O.rmsnorm(x, w, 1e-5), what=f"rmsnorm {rows}x{d}")
+
+
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 7, 8])
+@pytest.mark.parametrize("int8", [False, True])
+def test_linear(dev, M, int8):
+    rng = np.random.default_rng(10 * M + int8)
+    for N, K in [(64, 256), (1027, 2048), (333, 1040), (2048, 8192)]:  # odd row counts and ragged K chunks
+        if int8 and K % 16:
+            continue
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        res = rng.standard_normal((M, N)).astype(np.float16)
+        y = Tensor.empty((M, N), "float16", dev)
+        xt = Tensor(x, device=dev)
+        if int8:
+            wq = rng.integers(-127, 128, (N, K), dtype=np.int8)
+            s = (rng.uniform(0.5, 1.5, N) * synth.INT8_SCALE_BASE).astype(np.float16)
+            wt, st = Tensor(wq, device=dev), Tensor(s, device=dev)
+            ref = O.linear_w8(x, wq, s)
+            sp = st.ptr
+        else:
+            w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+            wt, sp = Tensor(w, device=dev), 0
+            ref = O.linear_f16(x, w)
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, sp, 0, M, N, K)
+        assert_reduction_close(y.numpy(), ref, what=f"linear M{M} N{N} K{K} int8={int8}")
+        # residual epilogue: fp16 add of the rounded projection
+        rt = Tensor(res, device=dev)
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, sp, rt.ptr, M, N, K)
+        ref_r = (res.astype(np.float32) + ref.astype(np.float32)).astype(np.float16)  # exact sum, one rounding
+        assert_reduction_close(y.numpy(), ref_r, max_ulp=2, max_frac=0.05, what=f"linear+residual M{M} N{N} K{K}")
+
+
+@pytest.mark.parametrize("M,int8", [(1, False), (4, False), (1, True), (2, True)])
+def test_fused_norm_projections(dev, M, int8):
+    rng = np.random.default_rng(100 + M)
+    K, N, F = 2048, 1536, 1024
+    x = (rng.standard_normal((M, K)) * 0.8).astype(np.float16)
+    g = rng.uniform(0.5, 1.5, K).astype(np.float16)
+    xn = O.rmsnorm(x, g, 1e-5)
+
+    def mk(n):
+        if int8:
+            wq = rng.integers(-127, 128, (n, K), dtype=np.int8)
+            s = (rng.uniform(0.5, 1.5, n) * synth.INT8_SCALE_BASE).astype(np.float16)
+            return (wq, s), (Tensor(wq, device=dev), Tensor(s, device=dev))
+        w = (rng.standard_normal((n, K)) * 0.02).astype(np.float16)
+        return (w, None), (Tensor(w, device=dev), None)
+
+    def lin(h, a):
+        return O.linear_w8(a, *h) if int8 else O.linear_f16(a, h[0])
+
+    xt, gt = Tensor(x, device=dev), Tensor(g, device=dev)
+    h, (wt, st) = mk(N)
+    y = Tensor.empty((M, N), "float16", dev)
+    dev.call("jg_norm_linear", y.ptr, xt.ptr, gt.ptr, 1e-5, wt.ptr, st.ptr if st else 0, M, N, K)
+    assert_reduction_close(y.numpy(), lin(h, xn), max_ulp=2, max_frac=0.05, what="norm_linear")
+
+    h1, (w1, s1) = mk(F)
+    h3, (w3, s3) = mk(F)
+    f = Tensor.empty((M, F), "float16", dev)
+    dev.call("jg_norm_swiglu", f.ptr, xt.ptr, gt.ptr, 1e-5, w1.ptr, s1.ptr if s1 else 0, w3.ptr, s3.ptr if s3 else 0, M, F, K)
+    ref = O.swiglu(lin(h1, xn), lin(h3, xn))
+    assert_reduction_close(f.numpy(), ref, max_ulp=3, max_frac=0.08, what="norm_swiglu")
+
+    V = 5003
+    hv, (wv, sv) = mk(V)
+    logits = Tensor.empty((M, V), "float16", dev)
+    key = Tensor.zeros((M,), "uint64", dev)
+    tok = Tensor.empty((M,), "int32", dev)
+    dev.call("jg_norm_logits_argmax", logits.ptr, key.ptr, xt.ptr, gt.ptr, 1e-5, wv.ptr, sv.ptr if sv else 0, M, V, K)
+    dev.call("jg_argmax_finalize", tok.ptr, key.ptr, M)
+    got = logits.numpy()
+    assert_reduction_close(got, lin(hv, xn), max_ulp=2, max_frac=0.05, what="logits")
+    assert tok.numpy().tolist() == [O.argmax_f16(r) for r in got]  # greedy pick is the lowest-index max of its own logits
+    assert (key.numpy() == 0).all()
+
+
+# ------------------------------------------------------------------------------------------------ RoPE + attention
+@pytest.mark.parametrize("hd,H,G", [(64, 32, 8), (128, 24, 8), (128, 8, 8), (64, 4, 2), (128, 16, 2)])
+@pytest.mark.parametrize("B,T,n_split", [(1, 1, 0), (1, 97, 0), (2, 300, 3), (1, 1000, 0), (3, 65, 1)])
+def test_rope_cache_attention(dev, hd, H, G, B, T, n_split):
+    rng = np.random.default_rng(hd + H + T)
+    max_ctx = 1024
+    kv = KVCache(dev, 2, H, G, hd, max_ctx, B, page_size=64, n_split=n_split)
+    # scatter the pages: row b's i-th page is an arbitrary pool page
+    table = rng.permutation(kv.n_pages).astype(np.int32).reshape(B, kv.max_pages_per_seq)
+    kv.set_block_table(table)
+    freqs = precompute_freqs_cis(hd, 2 * max_ctx, 500000.0, dev)
+    ftab = freqs.numpy()
+    stride = (H + 2 * G) * hd
+    qkv_all = (rng.standard_normal((T, B, stride)) * 0.7).astype(np.float16)
+    layer = 1
+    k_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    v_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    qkv = Tensor.empty((B, stride), "float16", dev)
+    pos = Tensor.zeros((B,), "int32", dev)
+    q_rot = None
+    for t in range(T):
+        qkv.assign(qkv_all[t])
+        pos.assign(np.full((B,), t, np.int32))
+        dev.call("jg_rope_kvwrite", kv.handle, layer, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, B, H)
+        q_in = qkv_all[t][:, :H * hd].reshape(B, H, hd)
+        k_in = qkv_all[t][:, H * hd:(H + G) * hd].reshape(B, G, hd)
+        k_ref[:, t] = O.rope(k_in, ftab, [t] * B)
+        v_ref[:, t] = qkv_all[t][:, (H + G) * hd:].reshape(B, G, hd)
+        if t == T - 1:
+            q_rot = O.rope(q_in, ftab, [t] * B)
+            got_q = qkv.numpy()[:, :H * hd].reshape(B, H, hd)
+            assert (got_q.view(np.uint16) == q_rot.view(np.uint16)).all(), "rotated Q differs"
+    out = Tensor.empty((B, H * hd), "float16", dev)
+    dev.call("jg_attn_decode", kv.handle, layer, out.ptr, qkv.ptr, pos.ptr, B, H)
+    ref = O.attention(q_rot.reshape(B, 1, H, hd), k_ref, v_ref, T - 1).reshape(B, H * hd)
+    assert_reduction_close(out.numpy(), ref, max_ulp=2, max_frac=0.10, what=f"attention hd{hd} H{H} G{G} B{B} T{T}")
+    # a second launch reuses the scratch and tickets and must reproduce the result bit for bit
+    out2 = Tensor.empty((B, H * hd), "float16", dev)
+    dev.call("jg_attn_decode", kv.handle, layer, out2.ptr, qkv.ptr, pos.ptr, B, H)
+    assert (out2.numpy().view(np.uint16) == out.numpy().view(np.uint16)).all()
+    kv.close()
+
+
+# ------------------------------------------------------------------------------------------------ error behaviour
+def test_invalid_arguments_are_rejected_before_launch(dev):
+    x = Tensor.zeros((8, 64), "float16", dev)
+    w = Tensor.zeros((16, 64), "float16", dev)
+    y = Tensor.zeros((8, 16), "float16", dev)
+    with pytest.raises(ffi.JgError) as e:
+        dev.call("jg_linear", y.ptr, x.ptr, w.ptr + 2, 0, 0, 1, 16, 64)  # misaligned weight pointer
+    assert e.value.status == ffi.JG_EINVAL
+    with pytest.raises(ffi.JgError) as e:
+        dev.call("jg_linear", y.ptr, x.ptr, w.ptr, 0, 0, 1, 16, 60)  # K not a multiple of 8
+    assert e.value.status == ffi.JG_EINVAL
+    with pytest.raises(ffi.JgError) as e:
+        dev.call("jg_linear", y.ptr, 0, w.ptr, 0, 0, 1, 16, 64)  # null activation pointer
+    assert e.value.status == ffi.JG_EINVAL
+    with pytest.raises(ValueError):
+        Tensor.empty((0,), "float16", dev)  # "alloc size must be positve", as the reference's Allocator.alloc
+    x9 = Tensor.zeros((9, 64), "float16", dev)
+    y9 = Tensor.zeros((9, 16), "float16", dev)
+    with pytest.raises(ffi.JgError) as e:
+        dev.call("jg_linear", y9.ptr, x9.ptr, w.ptr, 0, 0, 9, 16, 64)  # more rows than the matrix-vector kernels take
+    assert e.value.status == ffi.JG_ENOTSUP
+    with pytest.raises(ffi.JgError) as e:
+        h = C.c_void_p()
+        ffi.call("jg_device_open", 99, C.byref(h))
+    assert e.value.status == ffi.JG_EINVAL
+    dev.synchronize()  # the device is still usable
+    assert (y.numpy() == 0).all()
