@@ -96,9 +96,15 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------------ workload sizes
-def arch(model: str) -> dict:
+LAYERS_OVERRIDE = 0
+
+
+def arch(model: str):
     from denograd_b200.llama3 import MODEL_PARAMS
-    return dict(MODEL_PARAMS[model]["args"]), MODEL_PARAMS[model]["tied"]
+    p = dict(MODEL_PARAMS[model]["args"])
+    if LAYERS_OVERRIDE:
+        p["n_layers"] = LAYERS_OVERRIDE
+    return p, MODEL_PARAMS[model]["tied"]
 
 
 def weight_bytes(p: dict, tied: bool, int8: bool) -> int:
@@ -196,7 +202,8 @@ def run_gpu(args) -> None:
     max_ctx = P + 2 * (K + W) + 16
     max_ctx = (max_ctx + 63) // 64 * 64
     dev_name = "CUDA" if local_rank == 0 else f"CUDA:{local_rank}"
-    llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=B, device=dev_name).load_synthetic()
+    llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=B, device=dev_name,
+                 n_layers=p["n_layers"]).load_synthetic()
     dev = llm.model.dev
     model = llm.model
 
@@ -305,10 +312,13 @@ def main() -> None:
     ap.add_argument("--quant", default="float16", choices=["float16", "int8"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0, help="reduced depth (profiling captures only; 0 = the model's own)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    global LAYERS_OVERRIDE
+    LAYERS_OVERRIDE = args.layers
     if args.impl == "reference":
         run_reference(args)
     else:

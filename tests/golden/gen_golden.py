@@ -7,7 +7,7 @@ accidental change and let GPU tests compare full-size runs without re-running mi
   python tests/golden/gen_golden.py            # tiny + C1 (about half a minute on 8 cores)
 
 Files:
-  tiny_fp16.npz / tiny_int8.npz : dim 256, 2 layers, 8 heads, 4 kv heads, vocab 1024 — ids, full logits
+  tiny_fp16.npz / tiny_int8.npz : dim 256, 2 layers, 4 heads, 2 kv heads (head_dim 64), vocab 1024 — ids, full logits
   c1_llama32_1b.npz             : Llama-3.2-1B architecture, 32-token prompt, 64 greedy tokens — ids, top-2 margins,
                                   max logit and the logits at 256 fixed vocabulary positions per step
   c1_llama32_1b_seed42.npz      : the same workload with prompt seed 42, whose greedy trajectory passes through
@@ -33,7 +33,7 @@ from tests.util import build_oracle, oracle_greedy  # noqa: E402
 from denograd_b200 import synth  # noqa: E402
 from denograd_b200.llama3 import MODEL_PARAMS  # noqa: E402
 
-TINY = {"dim": 256, "n_heads": 8, "n_kv_heads": 4, "n_layers": 2, "norm_eps": 1e-5, "rope_theta": 500000,
+TINY = {"dim": 256, "n_heads": 4, "n_kv_heads": 2, "n_layers": 2, "norm_eps": 1e-5, "rope_theta": 500000,
         "vocab_size": 1024, "hidden_dim": 512}
 C1_SAMPLE = np.linspace(0, 128255, 256).astype(np.int64)
 C1_PROMPT_SEED = 52
