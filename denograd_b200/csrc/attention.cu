@@ -73,6 +73,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_scores_kernel(const AttnArgs
   constexpr int U = 4;           // row passes in flight
   __shared__ float red[ATT_WARPS][NREP];
   __shared__ float s_m[NREP];
+  pdl_launch();
+  pdl_wait();
   const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane % LPR, rgrp = lane / LPR;
@@ -169,6 +171,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_pv_kernel(const AttnArgs a) 
   __shared__ float s_M[NREP], s_rL[NREP];
   __shared__ float part[ATT_WARPS][NREP][HD];
   __shared__ int s_last;
+  pdl_launch();
+  pdl_wait();
   const int j = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane % LPR, rgrp = lane / LPR;
@@ -282,6 +286,8 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ block_table,
                                     __half* __restrict__ k_layer, __half* __restrict__ v_layer, int B, int H, int G,
                                     int hd, int page, int page_shift, int max_pages_per_seq, int table_rows) {
+  pdl_launch();
+  pdl_wait();
   const int per_head = hd / 8;
   const int heads = H + 2 * G;
   const long long total = (long long)B * heads * per_head;
@@ -427,20 +433,18 @@ JG_API int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   const long long total = (long long)B * (H + 2 * G) * (hd / 8);
   int blocks = (int)((total + 127) / 128);
   if (blocks > dev->sm_count * 8) blocks = dev->sm_count * 8;
-  rope_kvwrite_kernel<<<blocks, 128, 0, dev->stream>>>((__half*)qkv, (const __half*)table, (const int32_t*)pos, kv->block_table,
-                                                       kv->k_pool + kv->layer_elems * layer, kv->v_pool + kv->layer_elems * layer,
-                                                       B, H, G, hd, kv->d.page_size, ilog2(kv->d.page_size), kv->d.max_pages_per_seq, table_rows);
-  return jg_after_launch(dev, "rope_kvwrite");
+  return jg_launch(dev, "rope_kvwrite", rope_kvwrite_kernel, dim3(blocks), dim3(128), 0, (__half*)qkv, (const __half*)table,
+                   (const int32_t*)pos, (const int32_t*)kv->block_table, kv->k_pool + kv->layer_elems * layer,
+                   kv->v_pool + kv->layer_elems * layer, B, H, G, hd, kv->d.page_size, ilog2(kv->d.page_size),
+                   kv->d.max_pages_per_seq, table_rows);
 }
 
 template <int HD, int NREP>
 static int launch_attn(jg_dev* dev, const AttnArgs& a, int B) {
   dim3 grid(a.n_split, a.G, B);
-  attn_scores_kernel<HD, NREP><<<grid, ATT_THREADS, 0, dev->stream>>>(a);
-  int rc = jg_after_launch(dev, "attn_scores");
+  int rc = jg_launch(dev, "attn_scores", attn_scores_kernel<HD, NREP>, grid, dim3(ATT_THREADS), 0, a);
   if (rc) return rc;
-  attn_pv_kernel<HD, NREP><<<grid, ATT_THREADS, 0, dev->stream>>>(a);
-  return jg_after_launch(dev, "attn_pv");
+  return jg_launch(dev, "attn_pv", attn_pv_kernel<HD, NREP>, grid, dim3(ATT_THREADS), 0, a);
 }
 
 JG_API int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos,

@@ -19,6 +19,7 @@ struct jg_dev {
   cudaEvent_t t0, t1;
   void* pinned_stage;  // small page-locked staging area for jg_copyin of tiny payloads
   size_t pinned_stage_bytes;
+  bool pdl;  // launch kernels with programmatic stream serialization (JG_PDL=0 turns it off)
 };
 
 struct jg_graph {
@@ -60,8 +61,37 @@ static inline int jg_after_launch(jg_dev* dev, const char* name) {
 
 static inline bool jg_aligned(uint64_t p, uint64_t a) { return p != 0 && (p % a) == 0; }
 
+#ifdef __CUDACC__
+// Every kernel of the library is launched through here.  With `dev->pdl` the launch carries the programmatic
+// stream-serialization attribute: the kernel may begin while its predecessor on the stream is still draining, and
+// must execute pdl_wait() before it touches anything the predecessor wrote (all kernels here do, at their top or,
+// for the weight-streaming kernels, right after their first weight prefetch).
+template <typename... KArgs, typename... Args>
+static inline int jg_launch(jg_dev* dev, const char* name, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev->pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+  if (e != cudaSuccess) return jg_cuda_fail(e, name, __FILE__, __LINE__);
+  return jg_after_launch(dev, name);
+}
+#endif
+
 // ------------------------------------------------------------------------------------------------ device side
 #ifdef __CUDACC__
+
+// Programmatic dependent launch: wait until the preceding kernel on the stream has completed and its writes are
+// visible (a no-op when the kernel was launched without the attribute) / allow the next kernel to start launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // 128-bit streaming load of read-only weights: bypass L1 allocation, they are read exactly once per launch.
 __device__ __forceinline__ uint4 ld_stream_128(const void* p) {

@@ -2,6 +2,7 @@
 // side of the boundary; see include/jsgrad_cuda.h for the reference interfaces each one stands in for).
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "common.cuh"
@@ -47,6 +48,8 @@ JG_API int jg_device_open(int32_t ordinal, jg_dev** out) {
     return JG_ENOTSUP;
   }
   d->sm_count = d->prop.multiProcessorCount;
+  const char* pdl = getenv("JG_PDL");
+  d->pdl = !(pdl && pdl[0] == '0');
   JG_CUDA(cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
   JG_CUDA(cudaEventCreate(&d->t0));
   JG_CUDA(cudaEventCreate(&d->t1));

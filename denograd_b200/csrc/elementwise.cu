@@ -10,6 +10,8 @@
 // Embedding.call == row gather (jsgrad/nn/index.ts:607-619): out[i,:] = W[tokens[i],:].
 __global__ void embed_f16_kernel(__half* __restrict__ out, const int32_t* __restrict__ tokens,
                                  const __half* __restrict__ w, int n_tok, int dim, int vocab) {
+  pdl_launch();
+  pdl_wait();
   const int per_row = dim / 8;
   for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < (long long)n_tok * per_row;
        it += (long long)gridDim.x * blockDim.x) {
@@ -24,6 +26,8 @@ __global__ void embed_f16_kernel(__half* __restrict__ out, const int32_t* __rest
 __global__ void embed_w8_kernel(__half* __restrict__ out, const int32_t* __restrict__ tokens,
                                 const int8_t* __restrict__ wq, const __half* __restrict__ scale, int n_tok, int dim,
                                 int vocab) {
+  pdl_launch();
+  pdl_wait();
   const int per_row = dim / 8;
   for (long long it = blockIdx.x * (long long)blockDim.x + threadIdx.x; it < (long long)n_tok * per_row;
        it += (long long)gridDim.x * blockDim.x) {
@@ -52,11 +56,10 @@ JG_API int jg_embed(jg_dev* dev, uint64_t out, uint64_t tokens, uint64_t w, uint
   int blocks = (int)((items + 255) / 256);
   if (blocks > dev->sm_count * 8) blocks = dev->sm_count * 8;
   if (scale == 0)
-    embed_f16_kernel<<<blocks, 256, 0, dev->stream>>>((__half*)out, (const int32_t*)tokens, (const __half*)w, n_tok, dim, vocab);
-  else
-    embed_w8_kernel<<<blocks, 256, 0, dev->stream>>>((__half*)out, (const int32_t*)tokens, (const int8_t*)w,
-                                                    (const __half*)scale, n_tok, dim, vocab);
-  return jg_after_launch(dev, "embed");
+    return jg_launch(dev, "embed", embed_f16_kernel, dim3(blocks), dim3(256), 0, (__half*)out, (const int32_t*)tokens,
+                     (const __half*)w, n_tok, dim, vocab);
+  return jg_launch(dev, "embed", embed_w8_kernel, dim3(blocks), dim3(256), 0, (__half*)out, (const int32_t*)tokens,
+                   (const int8_t*)w, (const __half*)scale, n_tok, dim, vocab);
 }
 
 // ------------------------------------------------------------------------------------------------ RMSNorm
@@ -188,6 +191,8 @@ JG_API int jg_argmax(jg_dev* dev, uint64_t out_idx, uint64_t x, int32_t rows, in
 }
 
 __global__ void argmax_finalize_kernel(int32_t* __restrict__ tokens, unsigned long long* __restrict__ key, int M) {
+  pdl_launch();
+  pdl_wait();
   int m = blockIdx.x * blockDim.x + threadIdx.x;
   if (m < M) {
     unsigned long long k = key[m];
@@ -200,11 +205,13 @@ JG_API int jg_argmax_finalize(jg_dev* dev, uint64_t tokens_out, uint64_t key, in
   JG_ENTER(dev);
   JG_REQUIRE(M > 0, "argmax_finalize: bad row count %d", M);
   JG_REQUIRE(jg_aligned(tokens_out, 4) && jg_aligned(key, 8), "argmax_finalize: null or misaligned pointer");
-  argmax_finalize_kernel<<<(M + 63) / 64, 64, 0, dev->stream>>>((int32_t*)tokens_out, (unsigned long long*)key, M);
-  return jg_after_launch(dev, "argmax_finalize");
+  return jg_launch(dev, "argmax_finalize", argmax_finalize_kernel, dim3((M + 63) / 64), dim3(64), 0, (int32_t*)tokens_out,
+                   (unsigned long long*)key, M);
 }
 
 __global__ void pos_advance_kernel(int32_t* pos, int B) {
+  pdl_launch();
+  pdl_wait();
   int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < B) pos[b] += 1;
 }
@@ -212,8 +219,7 @@ __global__ void pos_advance_kernel(int32_t* pos, int B) {
 JG_API int jg_pos_advance(jg_dev* dev, uint64_t pos, int32_t B) {
   JG_ENTER(dev);
   JG_REQUIRE(B > 0 && jg_aligned(pos, 4), "pos_advance: bad arguments");
-  pos_advance_kernel<<<(B + 63) / 64, 64, 0, dev->stream>>>((int32_t*)pos, B);
-  return jg_after_launch(dev, "pos_advance");
+  return jg_launch(dev, "pos_advance", pos_advance_kernel, dim3((B + 63) / 64), dim3(64), 0, (int32_t*)pos, B);
 }
 
 // ------------------------------------------------------------------------------------------------ seeded fills

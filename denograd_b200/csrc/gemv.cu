@@ -1,10 +1,18 @@
 // Weight-streaming matrix-vector kernels for decode (M = batch rows <= 8): y[m][n] = sum_k x[m][k] * W[n][k].
 //
 // The weight matrix is read exactly once per launch with 128-bit streaming loads; the activation rows live in
-// shared memory.  A warp owns RW consecutive output rows at a time and walks K with U independent 16-byte loads
-// per lane and row in flight, so that one SM keeps tens of KB outstanding towards HBM.  Products of fp16 operands
-// are exact in fp32 and are accumulated in fp32 (Tensor.dot with sum_acc_dtype: jsgrad/tensor.ts:2593-2605,
-// jsgrad/dtype.ts:243-248); only the summation order differs from a sequential loop.
+// shared memory.  Each CTA owns a contiguous run of row groups ("units": RW rows of one matrix, or one row of each of
+// the two SwiGLU matrices).  The run is split in two parts:
+//   * bulk: floor(n/8) units per warp, each warp on its own rows with RW x U independent 16-byte loads per lane in
+//     flight and no synchronisation with the other warps;
+//   * remainder (n mod 8 units): all eight warps work on the same rows, each on an interleaved eighth of K, and the
+//     partial sums meet in shared memory.  This keeps the CTAs of a launch within one unit of each other even when
+//     a matrix has only a few rows per SM (the 4096-row projections of an 8B model give 3.5 units per CTA).
+// Before the kernel waits for its predecessor (programmatic dependent launch) each warp asks for the head of its
+// span to be brought into L2 with a bulk prefetch: weights do not depend on the previous kernel, so they can travel
+// while it drains and while the activations are staged.  Products of fp16 operands are exact in fp32 and are
+// accumulated in fp32 (Tensor.dot with sum_acc_dtype: jsgrad/tensor.ts:2593-2605, jsgrad/dtype.ts:243-248); only the
+// summation order differs from a sequential loop.
 //
 // Fused around the reduction, all from the Llama block (jsgrad/models/llama.ts:108-127,210):
 //   prologue  NORM      x <- RMSNorm(x) * g            (jsgrad/nn/index.ts:586-588)
@@ -51,16 +59,56 @@ __device__ __forceinline__ void dequant16(const uint4& raw, __half2 s2, float (&
   }
 }
 
+// Ask for `bytes` (multiple of 16) starting at `p` (16-byte aligned) to be brought into L2; returns at once.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+constexpr uint32_t GEMV_PREFETCH_BYTES = 4096;  // per weight row and warp, ahead of the dependency wait
+
 template <int MT, bool W8, int EPI, bool NORM, int RW, int U>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);  // [MT][K]
+  constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
+  constexpr int NACC = NW * RW;                 // weight rows of one unit
+  constexpr int CH = W8 ? 16 : 8;               // weights per 16-byte load
+  constexpr int GU = (8 / MT) > 0 ? (8 / MT) : 1;  // units per cooperative pass (bounds the accumulators)
+  __shared__ float part[GEMV_WARPS][GU * NACC * MT];
   __shared__ float red[GEMV_WARPS];
   __shared__ float s_rs;
-  constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
-  constexpr int CH = W8 ? 16 : 8;  // weights per 16-byte load
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int K = a.K, N = a.N;
+  pdl_launch();
+
+  // ---- this CTA's contiguous run of units: [u0, u1) = bulk (nb units per warp) + remainder (< 8 units)
+  const int n_units = (N + RW - 1) / RW;
+  const int u0 = (int)((long long)blockIdx.x * n_units / gridDim.x);
+  const int u1 = (int)((long long)(blockIdx.x + 1) * n_units / gridDim.x);
+  const int nb = (u1 - u0) / GEMV_WARPS;
+  const int rem0 = u0 + nb * GEMV_WARPS;  // first unit of the remainder
+  const int KC = K / CH;                  // 16-byte chunks per weight row
+  const size_t row_bytes = W8 ? (size_t)K : (size_t)K * 2;
+  const unsigned char* wbase[NW];
+  wbase[0] = reinterpret_cast<const unsigned char*>(a.w0);
+  if (NW == 2) wbase[NW - 1] = reinterpret_cast<const unsigned char*>(a.w1);
+
+  // ---- L2 prefetch of the head of this warp's first rows (bulk) or of its K-slice of the shared rows (remainder)
+  if (lane < NACC) {
+    const int w = lane / RW, r = lane % RW;
+    if (nb > 0) {
+      const int row = min((u0 + warp * nb) * RW + r, N - 1);
+      const uint32_t bytes = (uint32_t)min((size_t)GEMV_PREFETCH_BYTES, row_bytes);
+      l2_prefetch_bulk(wbase[w] + (size_t)row * row_bytes, bytes & ~15u);
+    } else if (rem0 < u1) {
+      const int row = min(rem0 * RW + r, N - 1);
+      const size_t off = (size_t)warp * 512;  // this warp's first 512-byte piece of the row
+      if (off + 512 <= row_bytes) l2_prefetch_bulk(wbase[w] + (size_t)row * row_bytes + off, 512);
+    }
+  }
+
+  // ---- everything below reads what the previous kernel wrote
+  pdl_wait();
 
   // ---- prologue: activation rows -> shared memory (normalised when NORM); rows beyond M are zero
   for (int m = 0; m < MT; m++) {
@@ -105,126 +153,146 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
   }
   __syncthreads();
 
-  // ---- main loop: contiguous, balanced slice of row groups per warp
-  const long long gw = (long long)blockIdx.x * GEMV_WARPS + warp, GW = (long long)gridDim.x * GEMV_WARPS;
-  const int n_units = (N + RW - 1) / RW;
-  const int u_begin = (int)(gw * n_units / GW), u_end = (int)((gw + 1) * n_units / GW);
-  const int KC = K / CH;  // 16-byte chunks per weight row
-  const size_t row_bytes = W8 ? (size_t)K : (size_t)K * 2;
-  unsigned long long best[MT];
-  if (EPI == EPI_LOGITS) {
-#pragma unroll
-    for (int m = 0; m < MT; m++) best[m] = 0ull;
-  }
+  unsigned long long best = 0ull;  // LOGITS: running (value, index) key of the outputs this thread stores
 
-  for (int unit = u_begin; unit < u_end; unit++) {
-    const int r0 = unit * RW;
-    float acc[NW][RW][MT];
+  // One 16-byte chunk `c` of weight row data `wv` against the activations: acc[m] += sum_k w[k] * x[m][k].
+  auto fma_chunk = [&](float (&acc)[MT], const uint4& wv, int c, __half2 sc) {
+    if (!W8) {
 #pragma unroll
-    for (int w = 0; w < NW; w++)
-#pragma unroll
-      for (int r = 0; r < RW; r++)
-#pragma unroll
-        for (int m = 0; m < MT; m++) acc[w][r][m] = 0.f;
-
-    const unsigned char* wrow[NW][RW];
-    __half2 sc[NW][RW];
-#pragma unroll
-    for (int w = 0; w < NW; w++)
-#pragma unroll
-      for (int r = 0; r < RW; r++) {
-        const int row = (r0 + r < N) ? (r0 + r) : (N - 1);  // clamp: duplicates are never stored
-        wrow[w][r] = reinterpret_cast<const unsigned char*>(w == 0 ? a.w0 : a.w1) + (size_t)row * row_bytes;
-        if (W8) sc[w][r] = __half2half2((w == 0 ? a.s0 : a.s1)[row]);
+      for (int m = 0; m < MT; m++) {
+        float xf[8];
+        unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 8), xf);
+        acc[m] = dot8_acc(acc[m], wv, xf);
       }
+    } else {
+      float wf[16];
+      dequant16(wv, sc, wf);
+#pragma unroll
+      for (int m = 0; m < MT; m++) {
+        const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 16);
+        float lo[8], hi[8];
+        unpack8(xp[0], lo);
+        unpack8(xp[1], hi);
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[m] = fmaf(wf[k], lo[k], acc[m]);
+#pragma unroll
+        for (int k = 0; k < 8; k++) acc[m] = fmaf(wf[8 + k], hi[k], acc[m]);
+      }
+    }
+  };
+  // Final value of output (row, m) from the reduced sums of its NW matrices.
+  auto finish = [&](int row, int m, float s_a, float s_b) {
+    const size_t o = (size_t)m * N + (size_t)row;
+    __half v = __float2half_rn(s_a);
+    if (EPI == EPI_RESIDUAL) v = hadd1(a.residual[o], v);
+    if (EPI == EPI_SWIGLU) v = jg_silu_mul(v, __float2half_rn(s_b));
+    a.y[o] = v;
+    if (EPI == EPI_LOGITS) {
+      const unsigned long long k = argmax_key(v, (uint32_t)row);
+      best = k > best ? k : best;
+    }
+  };
 
+  // ---- bulk: warp-private units
+  for (int unit = u0 + warp * nb; unit < u0 + (warp + 1) * nb; unit++) {
+    float acc[NACC][MT];
+    const unsigned char* wrow[NACC];
+    __half2 sc[NACC];
+#pragma unroll
+    for (int j = 0; j < NACC; j++) {
+#pragma unroll
+      for (int m = 0; m < MT; m++) acc[j][m] = 0.f;
+      const int row = min(unit * RW + (j % RW), N - 1);  // clamp: a duplicate row is computed but never stored
+      wrow[j] = wbase[j / RW] + (size_t)row * row_bytes;
+      sc[j] = W8 ? __half2half2((j / RW == 0 ? a.s0 : a.s1)[row]) : __half2();
+    }
     for (int c0 = lane; c0 < KC; c0 += 32 * U) {
-      uint4 wv[NW][RW][U];
+      uint4 wv[NACC][U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
         const int c = c0 + 32 * u;
-        const bool ok = c < KC;
 #pragma unroll
-        for (int w = 0; w < NW; w++)
-#pragma unroll
-          for (int r = 0; r < RW; r++)
-            wv[w][r][u] = ok ? ld_stream_128(wrow[w][r] + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < NACC; j++) wv[j][u] = (c < KC) ? ld_stream_128(wrow[j] + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
       for (int u = 0; u < U; u++) {
         const int c = c0 + 32 * u;
-        if (c >= KC) break;
-        if (!W8) {
+        if (c < KC) {
 #pragma unroll
-          for (int m = 0; m < MT; m++) {
-            float xf[8];
-            unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 8), xf);
-#pragma unroll
-            for (int w = 0; w < NW; w++)
-#pragma unroll
-              for (int r = 0; r < RW; r++) acc[w][r][m] = dot8_acc(acc[w][r][m], wv[w][r][u], xf);
-          }
-        } else {
-          float wf[NW][RW][16];
-#pragma unroll
-          for (int w = 0; w < NW; w++)
-#pragma unroll
-            for (int r = 0; r < RW; r++) dequant16(wv[w][r][u], sc[w][r], wf[w][r]);
-#pragma unroll
-          for (int m = 0; m < MT; m++) {
-            float xf[16];
-            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 16);
-            {
-              float lo[8], hi[8];
-              unpack8(xp[0], lo);
-              unpack8(xp[1], hi);
-#pragma unroll
-              for (int k = 0; k < 8; k++) { xf[k] = lo[k]; xf[8 + k] = hi[k]; }
-            }
-#pragma unroll
-            for (int w = 0; w < NW; w++)
-#pragma unroll
-              for (int r = 0; r < RW; r++)
-#pragma unroll
-                for (int k = 0; k < 16; k++) acc[w][r][m] = fmaf(wf[w][r][k], xf[k], acc[w][r][m]);
-          }
+          for (int j = 0; j < NACC; j++) fma_chunk(acc[j], wv[j][u], c, sc[j]);
         }
       }
     }
-
-    // ---- reduce across the warp and apply the epilogue; lane (r*MT + m) stores output (row r0+r, m)
 #pragma unroll
-    for (int w = 0; w < NW; w++)
+    for (int j = 0; j < NACC; j++)
 #pragma unroll
-      for (int r = 0; r < RW; r++)
-#pragma unroll
-        for (int m = 0; m < MT; m++) acc[w][r][m] = warp_sum(acc[w][r][m]);
-
+      for (int m = 0; m < MT; m++) acc[j][m] = warp_sum(acc[j][m]);
 #pragma unroll
     for (int r = 0; r < RW; r++)
 #pragma unroll
-      for (int m = 0; m < MT; m++) {
-        if (lane == ((r * MT + m) & 31) && r0 + r < N && m < a.M) {
-          const size_t o = (size_t)m * N + (size_t)(r0 + r);
-          __half v = __float2half_rn(acc[0][r][m]);
-          if (EPI == EPI_RESIDUAL) v = hadd1(a.residual[o], v);
-          if (EPI == EPI_SWIGLU) v = jg_silu_mul(v, __float2half_rn(acc[NW - 1][r][m]));
-          a.y[o] = v;
-          if (EPI == EPI_LOGITS) {
-            unsigned long long k = argmax_key(v, (uint32_t)(r0 + r));
-            best[m] = k > best[m] ? k : best[m];
-          }
+      for (int m = 0; m < MT; m++)
+        if (lane == ((r * MT + m) & 31) && unit * RW + r < N && m < a.M) finish(unit * RW + r, m, acc[r][m], acc[(NW - 1) * RW + r][m]);
+  }
+
+  // ---- remainder: all warps on the same units, K split between the warps in 512-byte pieces
+  for (int g0 = rem0; g0 < u1; g0 += GU) {
+    const int gu = min(GU, u1 - g0);
+    float acc[GU * NACC][MT];
+#pragma unroll
+    for (int j = 0; j < GU * NACC; j++)
+#pragma unroll
+      for (int m = 0; m < MT; m++) acc[j][m] = 0.f;
+    for (int c = warp * 32 + lane; c < KC; c += GEMV_THREADS) {
+      uint4 wv[GU * NACC];
+#pragma unroll
+      for (int j = 0; j < GU * NACC; j++) {
+        const int unit = g0 + j / NACC, jj = j % NACC;
+        const int row = min(unit * RW + (jj % RW), N - 1);
+        wv[j] = (j / NACC < gu) ? ld_stream_128(wbase[jj / RW] + (size_t)row * row_bytes + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < GU * NACC; j++) {
+        if (j / NACC < gu) {
+          const int unit = g0 + j / NACC, jj = j % NACC;
+          const int row = min(unit * RW + (jj % RW), N - 1);
+          fma_chunk(acc[j], wv[j], c, W8 ? __half2half2((jj / RW == 0 ? a.s0 : a.s1)[row]) : __half2());
         }
       }
+    }
+#pragma unroll
+    for (int j = 0; j < GU * NACC; j++)
+#pragma unroll
+      for (int m = 0; m < MT; m++) {
+        const float v = warp_sum(acc[j][m]);
+        if (lane == 0) part[warp][j * MT + m] = v;
+      }
+    __syncthreads();
+    if (tid < gu * RW * MT) {
+      const int ul = tid / (RW * MT), r = (tid / MT) % RW, m = tid % MT;
+      const int row = (g0 + ul) * RW + r;
+      if (row < N && m < a.M) {
+        float s_a = 0.f, s_b = 0.f;
+#pragma unroll
+        for (int w = 0; w < GEMV_WARPS; w++) s_a += part[w][(ul * NACC + r) * MT + m];
+        if (NW == 2) {
+#pragma unroll
+          for (int w = 0; w < GEMV_WARPS; w++) s_b += part[w][(ul * NACC + (NW - 1) * RW + r) * MT + m];
+        }
+        finish(row, m, s_a, s_b);
+      }
+    }
+    __syncthreads();  // `part` is rewritten by the next pass
   }
 
   if (EPI == EPI_LOGITS) {
+    // every thread may have stored outputs of some batch row m (bulk: lane r*MT+m; remainder: tid % MT)
 #pragma unroll
     for (int m = 0; m < MT; m++) {
-      unsigned long long b = best[m];
+      const bool mine = ((lane % MT) == m) || ((tid % MT) == m);
+      unsigned long long b = mine ? best : 0ull;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
-        unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
         b = other > b ? other : b;
       }
       if (lane == 0 && m < a.M && b != 0ull) atomicMax(a.key + m, b);
@@ -235,33 +303,36 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
 // ------------------------------------------------------------------------------------------------ host side
 template <int MT, bool W8, int EPI, bool NORM>
 static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
-  // RW x U 16-byte loads per lane in flight; SWIGLU streams two matrices, so it takes half the rows per pass.
+  // one unit = RW rows of one matrix, or one row of each SwiGLU matrix: two weight rows either way, with U chunks
+  // of each in flight per lane in the warp-private part
   constexpr int RW = (EPI == EPI_SWIGLU) ? 1 : 2;
-  constexpr int U = (MT >= 4 || W8) ? 2 : 4;
+  constexpr int U = W8 ? (MT == 1 ? 4 : 2) : (MT == 1 ? 8 : (MT == 2 ? 4 : 2));
   auto kern = gemv_kernel<MT, W8, EPI, NORM, RW, U>;
   const size_t smem = (size_t)MT * a.K * sizeof(__half);
-  if (smem + 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) {
+  if (smem + 2048 > (size_t)dev->prop.sharedMemPerBlockOptin) {
     jg_set_error("%s: %d activation rows of K=%d need %zu B of shared memory (limit %zu)", name, MT, a.K, smem,
                  (size_t)dev->prop.sharedMemPerBlockOptin);
     return JG_ENOTSUP;
   }
-  static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per device ordinal, per instantiation
+  static int occ_for[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  static size_t occ_smem[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int slot = dev->ordinal & 7;
   if (smem > 48 * 1024 && smem > smem_set[slot]) {
-    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->prop.sharedMemPerBlockOptin - 1024));
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->prop.sharedMemPerBlockOptin - 2048));
     smem_set[slot] = dev->prop.sharedMemPerBlockOptin;
   }
-  int occ = 0;
-  JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem));
-  if (occ < 1) occ = 1;
-  if (occ > 4) occ = 4;
+  if (occ_for[slot] == 0 || occ_smem[slot] != smem) {
+    int occ = 0;
+    JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem));
+    occ_for[slot] = occ < 1 ? 1 : (occ > 4 ? 4 : occ);
+    occ_smem[slot] = smem;
+  }
   const int n_units = (a.N + RW - 1) / RW;
-  long long blocks = (long long)dev->sm_count * occ;
-  const long long max_useful = (n_units + GEMV_WARPS - 1) / GEMV_WARPS;
-  if (blocks > max_useful) blocks = max_useful;
+  long long blocks = (long long)dev->sm_count * occ_for[slot];
+  if (blocks > n_units) blocks = n_units;
   if (blocks < 1) blocks = 1;
-  kern<<<(unsigned)blocks, GEMV_THREADS, smem, dev->stream>>>(a);
-  return jg_after_launch(dev, name);
+  return jg_launch(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, a);
 }
 
 template <bool W8, int EPI, bool NORM>
