@@ -14,8 +14,12 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "transcendental.cuh"
+
+namespace cg = cooperative_groups;
 
 struct jg_kvcache {
   jg_dev* dev;
@@ -324,6 +328,240 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
   }
 }
 
+// ------------------------------------------------------------------------------------------------ fused decode attention
+// RoPE + cache write + attention of one new token per row in ONE launch, for contexts whose scores fit in shared
+// memory.  A thread-block cluster of CS CTAs serves one (batch row, kv head); CTA `rank` owns positions
+// [rank*chunk, (rank+1)*chunk).  The softmax statistics and the p.v partials cross CTAs through distributed shared
+// memory with hardware cluster barriers (no global scratch, no spinning):
+//   scores -> local max m_j and local sum l_j of exp2((s-m_j)/ln2) -> cluster: M = max m_j, L = sum l_j exp2((m_j-M)/ln2)
+//   -> p = half(exp2((s-M)/ln2) * 1/L) -> local p.v (fp32) -> each rank folds a slice of the outputs over the ranks.
+// Every probability is formed from the global max and the global sum and rounded to fp16 before it meets v, as the
+// reference's softmax does (jsgrad/tensor.ts:2186-2214); only the order in which the sum is accumulated differs.
+// Q is rotated in registers (the qkv buffer keeps the unrotated projection); the CTA that owns the newest position
+// rotates K, writes K and V to their page, and then reads them back like any other cached row.
+struct AttnFusedArgs {
+  const __half* qkv;
+  const __half* table;  // [table_rows][hd/2][2]
+  __half* k_layer;
+  __half* v_layer;
+  const int32_t* block_table;
+  const int32_t* pos;
+  __half* out;
+  int table_rows, qkv_stride, H, G, page, page_shift, max_pages_per_seq, max_ctx, chunk_cap;
+  float scale;
+};
+
+__device__ __forceinline__ uint4 rope8(const uint4& xraw, const uint4& traw) {
+  const __half* x = reinterpret_cast<const __half*>(&xraw);
+  const __half* t = reinterpret_cast<const __half*>(&traw);
+  __align__(16) __half o[8];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const __half xa = x[2 * i], xb = x[2 * i + 1], co = t[2 * i], si = t[2 * i + 1];
+    o[2 * i] = hsub1(hmul1(xa, co), hmul1(xb, si));
+    o[2 * i + 1] = hadd1(hmul1(xa, si), hmul1(xb, co));
+  }
+  return *reinterpret_cast<uint4*>(o);
+}
+
+template <int HD, int NREP>
+__global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const AttnFusedArgs a) {
+  constexpr int LPR = HD / 8;
+  constexpr int RPW = 32 / LPR;
+  constexpr int U = 8;                          // row passes in flight
+  constexpr int ROWS_IT = ATT_WARPS * RPW * U;  // positions per loop iteration of the CTA
+  extern __shared__ __align__(16) float sc[];   // [NREP][chunk_cap] raw scores
+  __shared__ float red[ATT_WARPS][NREP];
+  __shared__ float s_m[NREP], s_l[NREP], s_M[NREP], s_rL[NREP];
+  __shared__ float part[ATT_WARPS][NREP][HD];
+  __shared__ float o_part[NREP * HD];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), CS = (int)cluster.num_blocks();
+  const int g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int sub = lane % LPR, rgrp = lane / LPR;
+  pdl_launch();
+  pdl_wait();
+
+  const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);
+  const int p = T - 1;  // position of the new token
+  const int chunk = min((T + CS - 1) / CS, a.chunk_cap);  // the host sizes chunk_cap so that CS * chunk_cap >= max_ctx
+  const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
+  const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
+  const __half* xrow = a.qkv + (size_t)b * a.qkv_stride;
+  const uint4 traw = ld_128(a.table + ((size_t)min(p, a.table_rows - 1) * (HD / 2) + (size_t)sub * 4) * 2);
+
+  // ---- the owner of position p rotates K and stores the new K / V rows
+  if (t0 <= p && p < t1 && warp == 0 && lane < LPR) {
+    const uint4 kraw = ld_128(xrow + (size_t)(a.H + g) * HD + lane * 8);
+    const uint4 vraw = ld_128(xrow + (size_t)(a.H + a.G + g) * HD + lane * 8);
+    const int pg = bt_row[p >> a.page_shift], slot = p & (a.page - 1);
+    const size_t off = (((size_t)pg * a.G + g) * a.page + slot) * HD + (size_t)lane * 8;
+    *reinterpret_cast<uint4*>(a.k_layer + off) = rope8(kraw, traw);
+    *reinterpret_cast<uint4*>(a.v_layer + off) = vraw;
+  }
+  // ---- rotated query slices of the NREP heads of this group
+  float qf[NREP][8];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) unpack8(rope8(ld_128(xrow + (size_t)(g * NREP + r) * HD + sub * 8), traw), qf[r]);
+  __syncthreads();  // the new K / V rows are visible to this CTA's loads below
+
+  // ---- scores of this rank's positions -> shared memory.  The V rows of the first iteration are requested right
+  //      after its K rows, so that they travel while the softmax statistics are worked out.
+  float lmax[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) lmax[r] = -INFINITY;
+  uint4 v0[U];
+  for (int base = t0; base < t1; base += ROWS_IT) {
+    const int tb = base + warp * RPW + rgrp;
+    uint4 kv[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+      kv[u] = (t < t1) ? ld_128(kv_row(a.k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
+    }
+    if (base == t0) {
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+        const int t = tb + u * ATT_WARPS * RPW;
+        v0[u] = (t < t1) ? ld_128(kv_row(a.v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        float d = dot8_acc(0.f, kv[u], qf[r]);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+        const float s = __fmul_rn(d, a.scale);
+        if (t < t1) {
+          lmax[r] = fmaxf(lmax[r], s);
+          if (sub == (r % LPR)) sc[(size_t)r * a.chunk_cap + (t - t0)] = s;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NREP; r++) {
+    const float m = warp_max(lmax[r]);
+    if (lane == 0) red[warp][r] = m;
+  }
+  __syncthreads();
+  if (tid < NREP) {
+    float m = red[0][tid];
+    for (int w = 1; w < ATT_WARPS; w++) m = fmaxf(m, red[w][tid]);
+    s_m[tid] = m;
+  }
+  __syncthreads();
+  // ---- sum of exponentials relative to this rank's own max (combined across ranks below)
+  const float log2e = 1.4426950408889634f;
+  float lsum[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) lsum[r] = 0.f;
+  for (int t = t0 + tid; t < t1; t += ATT_THREADS) {
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+      lsum[r] = __fadd_rn(lsum[r], jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + (t - t0)], s_m[r]), log2e)));
+  }
+  __syncthreads();  // `red` is reused
+#pragma unroll
+  for (int r = 0; r < NREP; r++) {
+    const float v = warp_sum(lsum[r]);
+    if (lane == 0) red[warp][r] = v;
+  }
+  __syncthreads();
+  if (tid < NREP) {
+    float v = 0.f;
+    for (int w = 0; w < ATT_WARPS; w++) v += red[w][tid];
+    s_l[tid] = v;
+  }
+  cluster.sync();
+  // ---- global max M and normaliser L = sum_j l_j * exp2((m_j - M)/ln2) over the ranks, in rank order
+  if (tid < NREP) {
+    float M = -INFINITY;
+    for (int rk = 0; rk < CS; rk++) M = fmaxf(M, *cluster.map_shared_rank(&s_m[tid], rk));
+    float L = 0.f;
+    for (int rk = 0; rk < CS; rk++) {
+      const float mj = *cluster.map_shared_rank(&s_m[tid], rk), lj = *cluster.map_shared_rank(&s_l[tid], rk);
+      L = __fadd_rn(L, __fmul_rn(lj, jg_xexp2_f32(__fmul_rn(__fsub_rn(mj, M), log2e))));
+    }
+    s_M[tid] = M;
+    s_rL[tid] = __fdiv_rn(1.0f, L);
+  }
+  __syncthreads();
+
+  // ---- p.v over this rank's positions; lane r of each row group evaluates p = half(exp2((s-M)/ln2) * 1/L) of head
+  //      r (rounded to fp16 before it meets v, as in the reference graph) and the group shares it
+  float acc[NREP][8];
+#pragma unroll
+  for (int r = 0; r < NREP; r++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[r][i] = 0.f;
+  const int my_r = sub < NREP ? sub : 0;
+  const float myM = s_M[my_r], myrL = s_rL[my_r];
+  for (int base = t0; base < t1; base += ROWS_IT) {
+    const int tb = base + warp * RPW + rgrp;
+    uint4 vv[U];
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+      if (base == t0) vv[u] = v0[u];
+      else vv[u] = (t < t1) ? ld_128(kv_row(a.v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; u++) {
+      const int t = tb + u * ATT_WARPS * RPW;
+      const float s = (t < t1 && sub < NREP) ? sc[(size_t)my_r * a.chunk_cap + (t - t0)] : -INFINITY;
+      const float e = jg_xexp2_f32(__fmul_rn(__fsub_rn(s, myM), log2e));
+      const float pr = __half2float(__float2half_rn(__fmul_rn(e, myrL)));
+      float vf[8];
+      unpack8(vv[u], vf);
+#pragma unroll
+      for (int r = 0; r < NREP; r++) {
+        const float p_r = __shfl_sync(0xffffffffu, pr, rgrp * LPR + r);
+#pragma unroll
+        for (int i = 0; i < 8; i++) acc[r][i] = fmaf(p_r, vf[i], acc[r][i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < NREP; r++)
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+#pragma unroll
+      for (int o = 16; o >= LPR; o >>= 1) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], o);
+    }
+  if (rgrp == 0) {
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+#pragma unroll
+      for (int i = 0; i < 8; i++) part[warp][r][sub * 8 + i] = acc[r][i];
+  }
+  __syncthreads();
+  for (int idx = tid; idx < NREP * HD; idx += ATT_THREADS) {
+    const int r = idx / HD, i = idx % HD;
+    float s = 0.f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) s += part[w][r][i];
+    o_part[idx] = s;
+  }
+  cluster.sync();
+
+  // ---- each rank folds its slice of the NREP*HD outputs over the ranks, in rank order
+  const int per_rank = (NREP * HD + CS - 1) / CS;
+  for (int k = tid; k < per_rank; k += ATT_THREADS) {
+    const int idx = rank * per_rank + k;
+    if (idx < NREP * HD) {
+      float s = 0.f;
+      for (int rk = 0; rk < CS; rk++) s = __fadd_rn(s, *cluster.map_shared_rank(&o_part[idx], rk));
+      a.out[(size_t)b * a.H * HD + (size_t)g * NREP * HD + idx] = __float2half_rn(s);
+    }
+  }
+  cluster.sync();  // peers may still be reading this CTA's shared memory
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 static int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
 
@@ -472,5 +710,71 @@ JG_API int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t o
   JG_ATT_CASE(128, 1) JG_ATT_CASE(128, 2) JG_ATT_CASE(128, 3) JG_ATT_CASE(128, 4) JG_ATT_CASE(128, 8)
 #undef JG_ATT_CASE
   jg_set_error("attn_decode: head_dim %d with %d query heads per kv head not supported", hd, n_rep);
+  return JG_ENOTSUP;
+}
+
+template <int HD, int NREP>
+static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs, size_t smem) {
+  auto kern = attn_decode_fused_kernel<HD, NREP>;
+  static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int slot = dev->ordinal & 7;
+  if (smem > smem_set[slot]) {
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (cs > 8) JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    smem_set[slot] = smem;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cs, a.G, B);
+  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dev->pdl ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) return jg_cuda_fail(e, "attn_decode_fused", __FILE__, __LINE__);
+  return jg_after_launch(dev, "attn_decode_fused");
+}
+
+JG_API int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
+                                int32_t table_rows, uint64_t pos, int32_t B, int32_t H) {
+  JG_ENTER(dev);
+  JG_REQUIRE(kv != nullptr && kv->dev == dev, "attn_decode_fused: cache belongs to another device");
+  JG_REQUIRE(layer >= 0 && layer < kv->d.n_layers, "attn_decode_fused: layer %d out of range", layer);
+  JG_REQUIRE(B > 0 && B <= kv->d.max_batch && H == kv->d.n_heads, "attn_decode_fused: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
+  JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(table, 16) && jg_aligned(pos, 4), "attn_decode_fused: null or misaligned pointer");
+  JG_REQUIRE(table_rows > 0, "attn_decode_fused: empty RoPE table");  // positions beyond the table use its last row
+  const int G = kv->d.n_kv_heads, hd = kv->d.head_dim, n_rep = H / G;
+  static int cluster = -1;
+  if (cluster < 0) {
+    const char* e = getenv("JG_ATTN_CLUSTER");
+    cluster = e ? atoi(e) : 8;
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) cluster = 8;
+  }
+  const int cs = cluster;
+  const int chunk_cap = (((kv->max_ctx + cs - 1) / cs) + 3) & ~3;
+  const size_t smem = (size_t)n_rep * chunk_cap * sizeof(float);
+  if (smem + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) {
+    jg_set_error("attn_decode_fused: %d positions per CTA need %zu B of shared memory; use jg_rope_kvwrite + jg_attn_decode", chunk_cap, smem);
+    return JG_ENOTSUP;
+  }
+  AttnFusedArgs a = {};
+  a.qkv = (const __half*)qkv; a.table = (const __half*)table; a.table_rows = table_rows;
+  a.k_layer = kv->k_pool + kv->layer_elems * layer; a.v_layer = kv->v_pool + kv->layer_elems * layer;
+  a.block_table = kv->block_table; a.pos = (const int32_t*)pos; a.out = (__half*)out;
+  a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
+  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap;
+  a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));
+#define JG_ATT_CASE(HD_, NR_) if (hd == HD_ && n_rep == NR_) return launch_attn_fused<HD_, NR_>(dev, a, B, cs, smem);
+  JG_ATT_CASE(64, 1) JG_ATT_CASE(64, 2) JG_ATT_CASE(64, 3) JG_ATT_CASE(64, 4) JG_ATT_CASE(64, 8)
+  JG_ATT_CASE(128, 1) JG_ATT_CASE(128, 2) JG_ATT_CASE(128, 3) JG_ATT_CASE(128, 4) JG_ATT_CASE(128, 8)
+#undef JG_ATT_CASE
+  jg_set_error("attn_decode_fused: head_dim %d with %d query heads per kv head not supported", hd, n_rep);
   return JG_ENOTSUP;
 }

@@ -11,7 +11,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libjsgrad_cuda.so")
+LIB_PATH = os.environ.get("JG_LIB") or os.path.join(_HERE, "lib", "libjsgrad_cuda.so")
 
 JG_OK, JG_EIO, JG_ENOMEM, JG_EINVAL, JG_ENOTSUP, JG_ETIMEDOUT = 0, 5, 12, 22, 95, 110
 
@@ -76,6 +76,7 @@ SIGNATURES: dict[str, list] = {
     "jg_kvcache_bytes": [_vp, _P(_u64)],
     "jg_rope_kvwrite": [_vp, _vp, _i32, _u64, _u64, _i32, _u64, _i32, _i32],
     "jg_attn_decode": [_vp, _vp, _i32, _u64, _u64, _u64, _i32, _i32],
+    "jg_attn_decode_fused": [_vp, _vp, _i32, _u64, _u64, _u64, _i32, _u64, _i32, _i32],
     "jg_pos_advance": [_vp, _u64, _i32],
     "jg_fill_normal_f16": [_vp, _u64, _u64, _u64, _u64, _f32],
     "jg_fill_uniform_i8": [_vp, _u64, _u64, _u64, _u64],

@@ -16,6 +16,7 @@ in device memory so that the captured step serves every position.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import numpy as np
 
@@ -47,6 +48,7 @@ class KVCache:
                        n_heads, n_split)
         self.handle = C.c_void_p()
         ffi.call("jg_kvcache_create", dev.handle, C.byref(d), C.byref(self.handle))
+        self.fused_attention = os.environ.get("JG_ATTN_FUSED", "1") != "0"  # one-launch decode attention
 
     def set_block_table(self, table: np.ndarray) -> None:
         table = np.ascontiguousarray(table, dtype=np.int32)
@@ -156,8 +158,17 @@ class TransformerBlock:
         wqkv = a._wqkv
         dev.call("jg_norm_linear", ws.qkv.ptr, ws.h.ptr, self.attention_norm.weight.ptr, self.attention_norm.eps,
                  wqkv.weight.ptr, wqkv.scale_ptr, B, wqkv.out_features, d)
-        apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
-        dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
+        if a._kv.fused_attention:
+            try:  # RoPE + cache write + attention in one cluster launch
+                dev.call("jg_attn_decode_fused", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, freqs_cis.ptr,
+                         freqs_cis.shape[0], pos.ptr, B, a.n_heads)
+            except ffi.JgError as e:
+                if e.status != ffi.JG_ENOTSUP:
+                    raise
+                a._kv.fused_attention = False  # context slice too long for shared memory: use the split kernels
+        if not a._kv.fused_attention:
+            apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
+            dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
         a.wo.call(ws.attn, residual=ws.h, out=ws.h)
         dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
                  f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)

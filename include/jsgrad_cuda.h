@@ -167,6 +167,14 @@ int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, ui
 int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos,
                    int32_t B, int32_t H);
 
+/* The three steps above for one new token per row in a single launch: rotate Q and K (jsgrad/models/llama.ts:23-32),
+ * store K/V at pos[b] (:87), attend over [0, pos[b]] (jsgrad/tensor.ts:3920-3934).  A thread-block cluster shares one
+ * (row, kv head) and exchanges the softmax statistics through distributed shared memory, so no scratch memory is
+ * used; the per-CTA slice of the context must fit in shared memory (JG_ENOTSUP otherwise — use the two calls above).
+ * Unlike jg_rope_kvwrite this leaves the Q slice of `qkv` unrotated. */
+int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
+                         int32_t table_rows, uint64_t pos, int32_t B, int32_t H);
+
 /* pos[b] += 1 for b < B (the host-side `start_pos++` of the decode loop, jsgrad/models/llama3.ts:284-295,
  * kept on the device so a captured step can be replayed without host input). */
 int jg_pos_advance(jg_dev* dev, uint64_t pos, int32_t B);

@@ -234,7 +234,22 @@ def test_rope_cache_attention(dev, hd, H, G, B, T, n_split):
     out2 = Tensor.empty((B, H * hd), "float16", dev)
     dev.call("jg_attn_decode", kv.handle, layer, out2.ptr, qkv.ptr, pos.ptr, B, H)
     assert (out2.numpy().view(np.uint16) == out.numpy().view(np.uint16)).all()
+    # the one-launch cluster kernel redoes the last position from the unrotated projections: RoPE, cache write (into
+    # another layer's pages, whose earlier rows are copied from this one) and attention
+    kv2 = KVCache(dev, 1, H, G, hd, max_ctx, B, page_size=64)
+    kv2.set_block_table(table)
+    for t in range(T - 1):
+        qkv.assign(qkv_all[t])
+        pos.assign(np.full((B,), t, np.int32))
+        dev.call("jg_rope_kvwrite", kv2.handle, 0, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, B, H)
+    qkv.assign(qkv_all[T - 1])
+    pos.assign(np.full((B,), T - 1, np.int32))
+    out3 = Tensor.empty((B, H * hd), "float16", dev)
+    dev.call("jg_attn_decode_fused", kv2.handle, 0, out3.ptr, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, B, H)
+    assert_reduction_close(out3.numpy(), ref, max_ulp=2, max_frac=0.10, what=f"fused attention hd{hd} H{H} G{G} B{B} T{T}")
+    assert (qkv.numpy() == qkv_all[T - 1]).all()  # the fused kernel leaves the projections untouched
     kv.close()
+    kv2.close()
 
 
 # ------------------------------------------------------------------------------------------------ error behaviour
