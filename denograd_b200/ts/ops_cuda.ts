@@ -1,0 +1,160 @@
+// jsgrad/runtime/ops_cuda.ts — the `CUDA` device for jsgrad, backed by libjsgrad_cuda.so (hand-written sm_100a
+// kernels behind a C ABI, see include/jsgrad_cuda.h).
+//
+// Drop this file into jsgrad/runtime/ and register it in jsgrad/env/deno.ts:
+//     import { CUDA } from '../runtime/ops_cuda.ts'
+//     override DEVICES = { CLANG, WEBGPU: DAWN, WGPU: WEBGPU, WASM, JS, DISK, CLOUD, CUDA }
+//
+// It follows the shape of the reference's own devices: ops_clang.ts (Program bound through env.dlopen with
+// 'pointer' / 'i32' parameters) and ops_dawn.ts (library opened once in init(), opaque native buffers).  The engine
+// above it is unchanged: Tensor, nn.Linear, models/llama keep their API.  No Deno runtime exists where this package
+// is built and tested, so this file is kept mechanically identical to denograd_b200/ffi.py + device.py, which make
+// the same C calls and are what the test-suite drives.
+import { Allocator, type BufferSpec, Compiled, Compiler, Program, type ProgramCallArgs } from './allocator.ts'
+import type { MemoryView } from '../helpers/memoryview.ts'
+import { env } from '../env/index.ts'
+import { vars } from '../helpers/helpers.ts'
+import { Renderer } from '../renderer/index.ts'
+
+const u64 = 'u64', i32 = 'i32', f32 = 'f32', f64 = 'f64', ptr = 'pointer', buf = 'buffer', usize = 'usize'
+const fn = (parameters: readonly string[], nonblocking = false) => ({ parameters, result: 'i32', nonblocking } as const)
+
+// One entry per function of include/jsgrad_cuda.h (same order, same types).
+export const SYMBOLS = {
+  jg_device_count: fn([buf]),
+  jg_device_open: fn([i32, buf]),
+  jg_device_close: fn([ptr]),
+  jg_device_sync: fn([ptr], true),
+  jg_device_props: fn([ptr, buf]),
+  jg_last_error: { parameters: [], result: 'pointer' },
+  jg_launch_count: fn([ptr, buf]),
+  jg_alloc: fn([ptr, usize, buf]),
+  jg_free: fn([ptr, u64]),
+  jg_copyin: fn([ptr, u64, buf, usize]),
+  jg_copyout: fn([ptr, buf, u64, usize], true),
+  jg_transfer: fn([ptr, u64, ptr, u64, usize]),
+  jg_memset: fn([ptr, u64, i32, usize]),
+  jg_copy: fn([ptr, u64, u64, usize]),
+  jg_host_alloc: fn([usize, buf]),
+  jg_host_free: fn([ptr]),
+  jg_copyin_async: fn([ptr, u64, ptr, usize]),
+  jg_copyout_async: fn([ptr, ptr, u64, usize]),
+  jg_timer_start: fn([ptr]),
+  jg_timer_stop: fn([ptr, buf], true),
+  jg_graph_begin: fn([ptr]),
+  jg_graph_end: fn([ptr, buf]),
+  jg_graph_launch: fn([ptr, ptr]),
+  jg_graph_destroy: fn([ptr]),
+  jg_embed: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
+  jg_rmsnorm: fn([ptr, u64, u64, u64, i32, i32, f32]),
+  jg_linear: fn([ptr, u64, u64, u64, u64, u64, i32, i32, i32]),
+  jg_norm_linear: fn([ptr, u64, u64, u64, f32, u64, u64, i32, i32, i32]),
+  jg_norm_swiglu: fn([ptr, u64, u64, u64, f32, u64, u64, u64, u64, i32, i32, i32]),
+  jg_swiglu: fn([ptr, u64, u64, u64, 'i64']),
+  jg_norm_logits_argmax: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32]),
+  jg_argmax_finalize: fn([ptr, u64, u64, i32]),
+  jg_argmax: fn([ptr, u64, u64, i32, i32]),
+  jg_freqs_cis: fn([ptr, u64, i32, i32, f64]),
+  jg_kvcache_create: fn([ptr, buf, buf]),
+  jg_kvcache_destroy: fn([ptr]),
+  jg_kvcache_set_block_table: fn([ptr, buf]),
+  jg_kvcache_bytes: fn([ptr, buf]),
+  jg_rope_kvwrite: fn([ptr, ptr, i32, u64, u64, i32, u64, i32, i32]),
+  jg_attn_decode: fn([ptr, ptr, i32, u64, u64, u64, i32, i32]),
+  jg_attn_decode_fused: fn([ptr, ptr, i32, u64, u64, u64, i32, u64, i32, i32]),
+  jg_pos_advance: fn([ptr, u64, i32]),
+  jg_fill_normal_f16: fn([ptr, u64, u64, u64, u64, f32]),
+  jg_fill_uniform_i8: fn([ptr, u64, u64, u64, u64]),
+  jg_fill_scale_f16: fn([ptr, u64, u64, u64, u64, f32]),
+  jg_fill_const_f16: fn([ptr, u64, u64, f32]),
+} as const
+
+type Lib = { symbols: Record<keyof typeof SYMBOLS, (...a: any[]) => any> }
+let lib: Lib | undefined
+
+const check = (status: number) => {
+  if (status !== 0) throw new Error(`[jsgrad_cuda status ${status}] ${env.getCString(lib!.symbols.jg_last_error())}`)
+}
+const out64 = () => new BigUint64Array(1)
+
+/** Buf = device address (bigint).  Allocator contract: jsgrad/runtime/allocator.ts:28-47. */
+export class CUDAAllocator extends Allocator<bigint> {
+  constructor(public dev: CUDA) { // BufferXfer reads `allocator.dev` on both sides (engine/realize.ts:126)
+    super()
+  }
+  _alloc = (size: number, _options: BufferSpec) => {
+    const o = out64()
+    check(lib!.symbols.jg_alloc(this.dev.handle, BigInt(size), o))
+    return o[0]
+  }
+  _free = (opaque: bigint, _options: BufferSpec) => check(lib!.symbols.jg_free(this.dev.handle, opaque))
+  _copyin = (dest: bigint, src: MemoryView) => check(lib!.symbols.jg_copyin(this.dev.handle, dest, src.bytes, BigInt(src.byteLength)))
+  _copyout = async (dest: MemoryView, src: bigint) => check(await lib!.symbols.jg_copyout(this.dev.handle, dest.bytes, src, BigInt(dest.byteLength)))
+  override _offset = (buf: bigint, _size: number, offset: number) => buf + BigInt(offset)
+  override _transfer = (dest: bigint, src: bigint, sz: number, src_dev: CUDA, dest_dev: CUDA) =>
+    check(lib!.symbols.jg_transfer(dest_dev.handle, dest, src_dev.handle, src, BigInt(sz)))
+}
+
+/** A kernel of the library addressed by name.  `lib` bytes are the UTF-8 descriptor the renderer emitted (which entry
+ *  point, which scalar arguments); nothing is compiled at run time.  Program contract: allocator.ts:98-107. */
+export class CUDAProgram extends Program {
+  static device: CUDA
+  static override init = (name: string, lib: Uint8Array) => new CUDAProgram(name, lib)
+  override call = async (bufs: bigint[], args: ProgramCallArgs, wait = false) => {
+    const d = JSON.parse(new TextDecoder().decode(this.lib)) as { entry: keyof typeof SYMBOLS; order: (number | string)[] }
+    const dev = CUDAProgram.device
+    if (wait) check(lib!.symbols.jg_timer_start(dev.handle))
+    // `order` interleaves buffer slots (numbers), symbolic variables from args.vals ('v0', 'v1', ...) and literals
+    const argv = d.order.map((o) => typeof o === 'number' ? bufs[o] : (o.startsWith('v') ? args.vals![Number(o.slice(1))] : Number(o)))
+    check(lib!.symbols[d.entry](dev.handle, ...argv))
+    if (wait) {
+      const s = new Float64Array(1)
+      check(await lib!.symbols.jg_timer_stop(dev.handle, s))
+      return s[0]
+    }
+  }
+}
+
+/** Emits kernel descriptors instead of source text (precedent: PythonRenderer in ops_js.ts:249-268). */
+export class CUDADescriptorRenderer extends Renderer {
+  override device = 'CUDA'
+  override has_local = true
+  override render = (name: string, _uops: unknown[]) => JSON.stringify({ entry: name, order: [] })
+}
+
+/** Captured decode step replayed with one launch (GraphRunner, engine/jit.ts:71-141). */
+export class CUDAGraph {
+  handle: Deno.PointerValue = null
+  constructor(public dev: CUDA) {}
+  capture = async (body: () => Promise<void>) => {
+    check(lib!.symbols.jg_graph_begin(this.dev.handle))
+    try {
+      await body()
+    } finally {
+      const o = out64()
+      check(lib!.symbols.jg_graph_end(this.dev.handle, o))
+      this.handle = Deno.UnsafePointer.create(o[0])
+    }
+  }
+  launch = () => check(lib!.symbols.jg_graph_launch(this.dev.handle, this.handle))
+}
+
+export class CUDA extends Compiled {
+  handle: Deno.PointerValue = null
+  ordinal: number
+  constructor(device: string) {
+    super(device, undefined, new CUDADescriptorRenderer(), new Compiler(), CUDAProgram)
+    this.ordinal = device.includes(':') ? Number(device.split(':')[1]) : 0
+    this.allocator = new CUDAAllocator(this)
+    CUDAProgram.device = this
+  }
+  // awaited before every lower / run (engine/realize.ts:133,157): idempotent
+  override init = async () => {
+    if (!lib) lib = await env.dlopen(vars.get('JSGRAD_CUDA_LIB', 'libjsgrad_cuda.so')!, SYMBOLS) as unknown as Lib
+    if (this.handle) return
+    const o = out64()
+    check(lib.symbols.jg_device_open(this.ordinal, o))
+    this.handle = Deno.UnsafePointer.create(o[0])
+  }
+  override synchronize = async () => check(await lib!.symbols.jg_device_sync(this.handle))
+}

@@ -74,3 +74,18 @@ def test_device_names():
     assert Device.canonicalize("CUDA:3") == "CUDA:3"
     with pytest.raises(ValueError):
         Device.canonicalize("CLANG")
+
+
+def test_typescript_symbol_table_matches_header():
+    """The Deno.dlopen table of ts/ops_cuda.ts lists every function of the header with the same parameter count."""
+    src = open(os.path.join(ROOT, "denograd_b200", "ts", "ops_cuda.ts")).read()
+    start = src.index("export const SYMBOLS = {")
+    body = src[start:src.index("\n} as const", start)]
+    ts = {}
+    for m in re.finditer(r"(jg_\w+):\s*fn\(\[([^\]]*)\]", body):
+        ts[m.group(1)] = len([p for p in m.group(2).split(",") if p.strip()])
+    assert "jg_last_error" in body
+    declared = {k: v for k, v in header_functions().items() if k != "jg_last_error"}
+    assert set(ts) == set(declared), set(ts) ^ set(declared)
+    for name, n in declared.items():
+        assert ts[name] == n, f"{name}: header has {n} parameters, ops_cuda.ts {ts[name]}"
