@@ -778,3 +778,74 @@ JG_API int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint
   jg_set_error("attn_decode_fused: head_dim %d with %d query heads per kv head not supported", hd, n_rep);
   return JG_ENOTSUP;
 }
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// jg_attn_decode keeps its scores / split statistics / partial outputs in buffers that jg_kvcache_create obtained
+// with cudaMalloc.  Some hosts must not let a kernel library allocate: an engine whose own allocator owns every byte
+// of the device and assigns buffers before the kernels run (jsgrad's memory planner and LRU allocator work that way —
+// an allocation made behind them is invisible to their accounting and fails once they hold the whole device), or a
+// serving loop that cannot afford the device-wide synchronisation a cudaMalloc / cudaFree implies.  For those callers
+// this variant takes every input and output from the caller and keeps the scratch in a fixed array that is part of
+// the library image: each GPU that loads the library holds JG_NOALLOC_SCRATCH_BYTES of it until the process exits.
+constexpr size_t JG_NOALLOC_SCRATCH_BYTES = 8u << 20;
+static __device__ __align__(256) unsigned char g_noalloc_scratch[JG_NOALLOC_SCRATCH_BYTES];
+// In host code `g_noalloc_scratch` is only a stand-in for the symbol, not a device address: the address is looked up
+// once per device (with that device current) and cached here.
+static unsigned char* g_noalloc_scratch_addr[64] = {};
+
+static inline size_t align_up_256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+JG_API int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint64_t k_layer, uint64_t v_layer,
+                                  uint64_t block_table, uint64_t pos, int32_t B, int32_t H, int32_t G, int32_t head_dim,
+                                  int32_t page_size, int32_t max_pages_per_seq, int32_t n_split) {
+  JG_ENTER(dev);
+  JG_REQUIRE(B > 0 && H > 0 && G > 0 && H % G == 0 && max_pages_per_seq > 0, "attn_decode_noalloc: bad shape B=%d H=%d G=%d pages=%d", B, H, G, max_pages_per_seq);
+  JG_REQUIRE(head_dim == 64 || head_dim == 128, "attn_decode_noalloc: head_dim %d not supported (64 or 128)", head_dim);
+  JG_REQUIRE(page_size == 16 || page_size == 32 || page_size == 64, "attn_decode_noalloc: page_size %d not in {16,32,64}", page_size);
+  JG_REQUIRE(n_split >= 1 && n_split <= 64, "attn_decode_noalloc: n_split %d outside [1,64]", n_split);
+  JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(k_layer, 16) && jg_aligned(v_layer, 16) &&
+                 jg_aligned(block_table, 4) && jg_aligned(pos, 4), "attn_decode_noalloc: null or misaligned pointer");
+  JG_REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64, "attn_decode_noalloc: device ordinal %d out of range", dev->ordinal);
+  const int n_rep = H / G, max_ctx = max_pages_per_seq * page_size;
+  // carve the fixed array: scores | (max, sum) per split | partial outputs per split | tickets
+  const size_t sc_bytes = align_up_256((size_t)B * H * max_ctx * sizeof(float));
+  const size_t ml_bytes = align_up_256((size_t)B * H * n_split * 2 * sizeof(float));
+  const size_t po_bytes = align_up_256((size_t)B * H * n_split * head_dim * sizeof(float));
+  const size_t tk_bytes = align_up_256((size_t)B * G * sizeof(unsigned int));
+  const size_t need = sc_bytes + ml_bytes + po_bytes + tk_bytes;
+  if (need > JG_NOALLOC_SCRATCH_BYTES) {
+    jg_set_error("attn_decode_noalloc: B=%d H=%d context=%d n_split=%d need %zu bytes of scratch, the built-in array holds %zu; "
+                 "use jg_attn_decode with a jg_kvcache for larger shapes", B, H, max_ctx, n_split, need, (size_t)JG_NOALLOC_SCRATCH_BYTES);
+    return JG_EINVAL;
+  }
+  // first call on this device: resolve the device address of the array (dev is current: JG_ENTER set it)
+  if (g_noalloc_scratch_addr[dev->ordinal] == nullptr) {
+    void* p = nullptr;
+    JG_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    JG_REQUIRE(p != nullptr, "attn_decode_noalloc: the scratch symbol has no address on device %d", dev->ordinal);
+    g_noalloc_scratch_addr[dev->ordinal] = (unsigned char*)p;
+  }
+  unsigned char* base = g_noalloc_scratch_addr[dev->ordinal];
+  AttnArgs a = {};
+  a.qkv = (const __half*)qkv;
+  a.k_layer = (const __half*)k_layer;
+  a.v_layer = (const __half*)v_layer;
+  a.block_table = (const int32_t*)block_table;
+  a.pos = (const int32_t*)pos;
+  a.scores = (float*)base;
+  a.part_ml = (float*)(base + sc_bytes);
+  a.part_o = (float*)(base + sc_bytes + ml_bytes);
+  a.tickets = (unsigned int*)(base + sc_bytes + ml_bytes + po_bytes);
+  a.out = (__half*)out;
+  a.qkv_stride = (H + 2 * G) * head_dim; a.H = H; a.G = G; a.page = page_size; a.page_shift = ilog2(page_size);
+  a.max_pages_per_seq = max_pages_per_seq; a.n_split = n_split; a.max_ctx = max_ctx;
+  a.scale = (float)(1.0 / (double)(float)sqrt((double)head_dim));
+  // the array keeps whatever the last call (of any shape) left in it; only the tickets must start at zero
+  JG_CUDA(cudaMemsetAsync(a.tickets, 0, tk_bytes, dev->stream));
+#define JG_ATT_CASE(HD_, NR_) if (head_dim == HD_ && n_rep == NR_) return launch_attn<HD_, NR_>(dev, a, B);
+  JG_ATT_CASE(64, 1) JG_ATT_CASE(64, 2) JG_ATT_CASE(64, 3) JG_ATT_CASE(64, 4) JG_ATT_CASE(64, 8)
+  JG_ATT_CASE(128, 1) JG_ATT_CASE(128, 2) JG_ATT_CASE(128, 3) JG_ATT_CASE(128, 4) JG_ATT_CASE(128, 8)
+#undef JG_ATT_CASE
+  jg_set_error("attn_decode_noalloc: head_dim %d with %d query heads per kv head not supported", head_dim, n_rep);
+  return JG_ENOTSUP;
+}

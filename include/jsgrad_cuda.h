@@ -175,6 +175,22 @@ int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uin
 int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
                          int32_t table_rows, uint64_t pos, int32_t B, int32_t H);
 
+/* jg_attn_decode without any allocation by the library.  It has no counterpart in the reference; it exists for hosts
+ * that must keep a kernel library from allocating device memory: an engine whose allocator owns the whole device and
+ * places every buffer itself (jsgrad's memory planner / LRU allocator), or a loop that cannot take the device-wide
+ * synchronisation of cudaMalloc / cudaFree.  The caller passes every input and output: the layer's K and V pools
+ * ([n_pages][G][page_size][head_dim] fp16), the int32 block table [B][max_pages_per_seq], pos[B], qkv and out as in
+ * jg_attn_decode (Q already rotated, K/V already stored).  Scores, split statistics and partial outputs live in a
+ * fixed 8 MiB array inside the library image (held by every GPU that loads the library, until the process exits);
+ * shapes that need more are rejected with JG_EINVAL:
+ *     4*B*H*(max_pages_per_seq*page_size) + 4*B*H*n_split*(2 + head_dim) + 4*B*G  bytes (each part rounded to 256).
+ * The first call on a device looks up the array's device address; make that call before any stream capture begins.
+ * All calls share the array, which keeps the previous call's contents (the call clears the part that must start at
+ * zero): two calls that overlap on the GPU — different streams, or different devices' handles on one GPU — race. */
+int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint64_t k_layer, uint64_t v_layer,
+                           uint64_t block_table, uint64_t pos, int32_t B, int32_t H, int32_t G, int32_t head_dim,
+                           int32_t page_size, int32_t max_pages_per_seq, int32_t n_split);
+
 /* pos[b] += 1 for b < B (the host-side `start_pos++` of the decode loop, jsgrad/models/llama3.ts:284-295,
  * kept on the device so a captured step can be replayed without host input). */
 int jg_pos_advance(jg_dev* dev, uint64_t pos, int32_t B);
