@@ -1,0 +1,275 @@
+// Weight-streaming projection for 9..64 activation rows (batched decode, short prefill chunks):
+//   y[m][n] = epilogue( sum_k x[m][k] * W[n][k] ),  fp16 operands, fp32 accumulation on the tensor cores.
+//
+// At these row counts the projection is still bound by reading W once from HBM, but the multiply-accumulate work no
+// longer fits the CUDA cores, so the products run through mma.sync.m16n8k16 (16 weight rows x 8 activation rows per
+// instruction).  Nothing is staged or shuffled for the weights: a lane's 16-byte global load of row g (and g+8) at
+// k-offset t*8 inside a 32-wide k block *is* its A fragment for two consecutive instructions, because the k order
+// inside a block may be permuted freely as long as the B fragment uses the same permutation — and the matching B
+// fragment is the 16 bytes of activation row (n0+g) at the same k-offset, read from a shared-memory tile.
+// CTA = 8 warps = (8/KS) tiles of 16 weight rows x KS interleaved slices of every k tile; the K-slices meet in shared
+// memory at the end.  Activation k tiles stream through a double-buffered, bank-conflict-free shared-memory ring with
+// cp.async.  Products are exact; the tensor-core accumulation order differs from the reference's sequential fp32
+// sum (jsgrad/tensor.ts:2593-2605), like every other reduction on this device.
+//
+// Epilogues: STORE, RESIDUAL (fp16 add), SWIGLU (two matrices, silu(gate)*up, jsgrad/models/llama.ts:108-110),
+// LOGITS (store + per-row (value, lowest index) key, jsgrad/tensor.ts:2314-2320).
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "transcendental.cuh"
+
+enum { GS_STORE = 0, GS_RESIDUAL = 1, GS_SWIGLU = 2, GS_LOGITS = 3 };
+
+struct GemmSmallArgs {
+  const __half* x;   // [M][K]
+  const __half* w0;  // [N][K]
+  const __half* w1;  // SWIGLU: up projection
+  __half* y;         // [M][N]
+  const __half* residual;
+  unsigned long long* key;  // [M] (LOGITS)
+  int M, N, K;
+};
+
+constexpr int GS_THREADS = 256;
+constexpr int GS_WARPS = 8;
+constexpr int GS_KT = 512;                 // activation k tile (halves)
+constexpr int GS_ROW_BYTES = GS_KT * 2 + 64;  // padded row: rows g and g+1 land 4 x 16 B apart modulo 128 B
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// D (16x8, fp32) += A (16x16, fp16, row) * B (16x8, fp16, col)
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT, int KS, int EPI>
+__global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const GemmSmallArgs a) {
+  constexpr int NT = MT / 8;                 // 8-row activation tiles
+  constexpr int NW = (EPI == GS_SWIGLU) ? 2 : 1;
+  constexpr int TILES = GS_WARPS / KS;       // 16-row weight tiles per CTA
+  constexpr int KW = GS_KT / KS;             // k elements of a tile handled by one warp
+  constexpr int NBMAX = (NW == 2) ? 4 : 8;   // 32-wide k blocks whose weight fragments a lane holds at once
+  constexpr int NB = (KW / 32) < NBMAX ? (KW / 32) : NBMAX;
+  constexpr int SPT = (KW / 32) / NB;        // steps per k tile
+  static_assert(NB >= 1 && SPT >= 1 && SPT * NB * 32 == KW, "k tiling");
+  extern __shared__ __align__(16) unsigned char smem[];  // 2 x [MT][GS_ROW_BYTES] activation tiles, then K-slice partials
+  __shared__ unsigned long long s_best[GS_WARPS][8];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int tile = warp / KS, ks = warp % KS;
+  const int K = a.K, N = a.N, M = a.M;
+  const int n_kt = (K + GS_KT - 1) / GS_KT;
+  pdl_launch();
+
+  const int row0 = (blockIdx.x * TILES + tile) * 16;  // first weight row of this warp's tile
+  const bool tile_ok = row0 < N;
+  const int ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);  // clamp: duplicates are never stored
+  const __half* wa[NW];
+  const __half* wb[NW];
+  wa[0] = a.w0 + (size_t)ra * K; wb[0] = a.w0 + (size_t)rb * K;
+  if (NW == 2) { wa[NW - 1] = a.w1 + (size_t)ra * K; wb[NW - 1] = a.w1 + (size_t)rb * K; }
+
+  float acc[NW][NT][4];
+#pragma unroll
+  for (int w = 0; w < NW; w++)
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) acc[w][j][i] = 0.f;
+
+  // weights of k tile 0 are requested before the dependency wait: they do not depend on the previous kernel
+  uint4 fa[NW][NB], fb[NW][NB];
+  auto load_w = [&](int kt, int sp) {
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+      const int k = kt * GS_KT + ks * KW + (sp * NB + b) * 32 + t * 8;
+      const bool ok = tile_ok && (k + 8 <= K);
+#pragma unroll
+      for (int w = 0; w < NW; w++) {
+        fa[w][b] = ok ? ld_stream_128(wa[w] + k) : make_uint4(0, 0, 0, 0);
+        fb[w][b] = ok ? ld_stream_128(wb[w] + k) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  load_w(0, 0);
+  pdl_wait();
+
+  // activation tile loader: MT rows x GS_KT halves, 16 bytes per cp.async, zero fill past M or K
+  auto load_x = [&](int kt, int bufi) {
+    unsigned char* dst = smem + (size_t)bufi * MT * GS_ROW_BYTES;
+    for (int c = tid; c < MT * (GS_KT / 8); c += GS_THREADS) {
+      const int m = c / (GS_KT / 8), kc = c % (GS_KT / 8);
+      const int k = kt * GS_KT + kc * 8;
+      unsigned char* d = dst + (size_t)m * GS_ROW_BYTES + (size_t)kc * 16;
+      if (m < M && k + 8 <= K) cp_async_16(d, a.x + (size_t)m * K + k);
+      else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
+    }
+    cp_async_commit();
+  };
+  load_x(0, 0);
+
+  for (int kt = 0; kt < n_kt; kt++) {
+    const int cur = kt & 1;
+    if (kt + 1 < n_kt) {
+      load_x(kt + 1, cur ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const unsigned char* xs = smem + (size_t)cur * MT * GS_ROW_BYTES;
+    for (int sp = 0; sp < SPT; sp++) {
+#pragma unroll
+      for (int b = 0; b < NB; b++) {
+        // byte offset of this lane's 16 bytes inside an activation row
+        const int koff = (ks * KW + (sp * NB + b) * 32 + t * 8) * 2;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+          const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * GS_ROW_BYTES + koff);
+#pragma unroll
+          for (int w = 0; w < NW; w++) {
+            // first instruction: halves 0-3 of the chunk (k 2t,2t+1 | 2t+8,2t+9 of the permuted block), second: 4-7
+            mma_16816(acc[w][j], fa[w][b].x, fb[w][b].x, fa[w][b].y, fb[w][b].y, xv.x, xv.y);
+            mma_16816(acc[w][j], fa[w][b].z, fb[w][b].z, fa[w][b].w, fb[w][b].w, xv.z, xv.w);
+          }
+        }
+      }
+      if (sp + 1 < SPT) load_w(kt, sp + 1);
+      else if (kt + 1 < n_kt) load_w(kt + 1, 0);
+    }
+    __syncthreads();  // the buffer read above is refilled by the next iteration's cp.async
+  }
+
+  // ---- fold the K slices (fixed order) through shared memory; slice 0 of every tile keeps the result
+  if (KS > 1) {
+    float* part = reinterpret_cast<float*>(smem);  // [TILES][KS][NW*NT*4][32]; the activation tiles are dead now
+    constexpr int PER = NW * NT * 4;
+    float* mine = part + ((size_t)(tile * KS + ks) * PER) * 32;
+#pragma unroll
+    for (int w = 0; w < NW; w++)
+#pragma unroll
+      for (int j = 0; j < NT; j++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) mine[(size_t)((w * NT + j) * 4 + i) * 32 + lane] = acc[w][j][i];
+    __syncthreads();
+    if (ks == 0) {
+#pragma unroll
+      for (int w = 0; w < NW; w++)
+#pragma unroll
+        for (int j = 0; j < NT; j++)
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            float s = 0.f;
+#pragma unroll
+            for (int q = 0; q < KS; q++) s += part[((size_t)(tile * KS + q) * PER + (size_t)((w * NT + j) * 4 + i)) * 32 + lane];
+            acc[w][j][i] = s;
+          }
+    }
+  }
+
+  // ---- epilogue: accumulator i of tile j is (weight row g + 8*(i/2), activation row 8j + 2t + (i%2))
+  unsigned long long best[NT][2];
+#pragma unroll
+  for (int j = 0; j < NT; j++) { best[j][0] = 0ull; best[j][1] = 0ull; }
+  if (ks == 0 && tile_ok) {
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        const int row = row0 + g + 8 * (i >> 1), m = j * 8 + 2 * t + (i & 1);
+        if (row < N && m < M) {
+          const size_t o = (size_t)m * N + row;
+          __half v = __float2half_rn(acc[0][j][i]);
+          if (EPI == GS_RESIDUAL) v = hadd1(a.residual[o], v);
+          if (EPI == GS_SWIGLU) v = jg_silu_mul(v, __float2half_rn(acc[NW - 1][j][i]));
+          a.y[o] = v;
+          if (EPI == GS_LOGITS) {
+            const unsigned long long k = argmax_key(v, (uint32_t)row);
+            best[j][i & 1] = k > best[j][i & 1] ? k : best[j][i & 1];
+          }
+        }
+      }
+  }
+  if (EPI == GS_LOGITS) {
+    // lanes with the same t hold the same activation rows: fold over g, then one atomic per row and warp
+#pragma unroll
+    for (int j = 0; j < NT; j++)
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        unsigned long long b = best[j][e];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+          const unsigned long long other = __shfl_xor_sync(0xffffffffu, b, o);
+          b = other > b ? other : b;
+        }
+        const int m = j * 8 + 2 * t + e;
+        if (g == 0 && m < M && b != 0ull) atomicMax(a.key + m, b);
+      }
+    (void)s_best;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+template <int MT, int KS, int EPI>
+static int launch_gs(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
+  auto kern = gemm_small_kernel<MT, KS, EPI>;
+  constexpr int NW = (EPI == GS_SWIGLU) ? 2 : 1;
+  const size_t x_bytes = (size_t)2 * MT * GS_ROW_BYTES;
+  const size_t p_bytes = KS > 1 ? (size_t)GS_WARPS * NW * (MT / 8) * 4 * 32 * sizeof(float) : 0;
+  const size_t smem = x_bytes > p_bytes ? x_bytes : p_bytes;
+  static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+  const int slot = dev->ordinal & 7;
+  if (!attr_set[slot] && smem > 48 * 1024) {
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set[slot] = true;
+  }
+  const int rows_per_cta = (GS_WARPS / KS) * 16;
+  const unsigned blocks = (unsigned)((a.N + rows_per_cta - 1) / rows_per_cta);
+  return jg_launch(dev, name, kern, dim3(blocks), dim3(GS_THREADS), smem, a);
+}
+
+template <int MT, int EPI>
+static int dispatch_ks(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
+  // enough CTAs to fill the machine twice over: 16-row tiles x K slices >= 2 x 8 warps x SMs
+  const long long tiles = (a.N + 15) / 16;
+  const long long want = 2LL * GS_WARPS * dev->sm_count;
+  if (tiles >= want || a.K < 8 * 256) return launch_gs<MT, 1, EPI>(dev, a, name);
+  if (tiles * 2 >= want) return launch_gs<MT, 2, EPI>(dev, a, name);
+  if (tiles * 4 >= want) return launch_gs<MT, 4, EPI>(dev, a, name);
+  return launch_gs<MT, 8, EPI>(dev, a, name);
+}
+
+template <int EPI>
+static int dispatch_mt(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
+  if (a.M <= 16) return dispatch_ks<16, EPI>(dev, a, name);
+  if (a.M <= 32) return dispatch_ks<32, EPI>(dev, a, name);
+  if (a.M <= 64) return dispatch_ks<64, EPI>(dev, a, name);
+  jg_set_error("%s: M=%d rows is beyond the small-batch projection kernels (max 64 per call)", name, a.M);
+  return JG_ENOTSUP;
+}
+
+// Entry used by gemv.cu's public functions for 8 < M <= 64 (fp16 weights).
+int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
+                  void* key, int M, int N, int K) {
+  JG_REQUIRE(K % 8 == 0, "projection: K=%d must be a multiple of 8", K);
+  GemmSmallArgs a = {};
+  a.x = (const __half*)x; a.w0 = (const __half*)w0; a.w1 = (const __half*)w1; a.y = (__half*)y;
+  a.residual = (const __half*)residual; a.key = (unsigned long long*)key; a.M = M; a.N = N; a.K = K;
+  switch (epi) {
+    case GS_STORE: return dispatch_mt<GS_STORE>(dev, a, "linear");
+    case GS_RESIDUAL: return dispatch_mt<GS_RESIDUAL>(dev, a, "linear");
+    case GS_SWIGLU: return dispatch_mt<GS_SWIGLU>(dev, a, "norm_swiglu");
+    case GS_LOGITS: return dispatch_mt<GS_LOGITS>(dev, a, "norm_logits_argmax");
+  }
+  jg_set_error("projection: unknown epilogue %d", epi);
+  return JG_EINVAL;
+}

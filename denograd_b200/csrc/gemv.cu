@@ -335,13 +335,20 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
   return jg_launch(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, a);
 }
 
+// gemm_small.cu: tensor-core projection for 9..64 rows (fp16 weights, activations already normalised)
+int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
+                  void* key, int M, int N, int K);
+
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
   if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
   if (a.M <= 8) return launch_gemv<8, W8, EPI, NORM>(dev, a, name);
-  jg_set_error("%s: M=%d rows is beyond the matrix-vector kernels (max 8)", name, a.M);
+  if (!W8 && !NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.y, a.residual, a.key, a.M, a.N, a.K);
+  if (NORM) jg_set_error("%s: with M=%d rows (> 8) normalise first (jg_rmsnorm) and pass norm_w = 0", name, a.M);
+  else if (W8) jg_set_error("%s: M=%d rows (> 8) with int8 weights is not implemented", name, a.M);
+  else jg_set_error("%s: M=%d rows is beyond the projection kernels (max 64 per call)", name, a.M);
   return JG_ENOTSUP;
 }
 
@@ -403,10 +410,11 @@ JG_API int jg_norm_logits_argmax(jg_dev* dev, uint64_t logits, uint64_t key, uin
   JG_ENTER(dev);
   int rc = check_common("norm_logits_argmax", logits, x, w, scale, M, V, K);
   if (rc) return rc;
-  JG_REQUIRE(jg_aligned(norm_w, 16) && jg_aligned(key, 8), "norm_logits_argmax: null or misaligned pointer");
+  JG_REQUIRE((norm_w == 0 || jg_aligned(norm_w, 16)) && jg_aligned(key, 8), "norm_logits_argmax: null or misaligned pointer");
   GemvArgs a = {};
   a.x = (const __half*)x; a.norm_w = (const __half*)norm_w; a.eps = eps; a.recip_k = (float)(1.0 / (double)K);
   a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)logits; a.key = (unsigned long long*)key;
   a.M = M; a.N = V; a.K = K;
+  if (norm_w == 0) return scale ? dispatch_m<true, EPI_LOGITS, false>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, false>(dev, a, "norm_logits_argmax");
   return scale ? dispatch_m<true, EPI_LOGITS, true>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, true>(dev, a, "norm_logits_argmax");
 }

@@ -156,8 +156,13 @@ class TransformerBlock:
         a, f, dev, B = self.attention, self.feed_forward, ws.h.dev, ws.B
         d = ws.h.shape[-1]
         wqkv = a._wqkv
-        dev.call("jg_norm_linear", ws.qkv.ptr, ws.h.ptr, self.attention_norm.weight.ptr, self.attention_norm.eps,
-                 wqkv.weight.ptr, wqkv.scale_ptr, B, wqkv.out_features, d)
+        big = B > 8  # more rows than the fused-norm kernels take: normalise into ws.xn, then project on the tensor cores
+        if big:
+            self.attention_norm.call(ws.h, out=ws.xn)
+            dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, wqkv.weight.ptr, wqkv.scale_ptr, 0, B, wqkv.out_features, d)
+        else:
+            dev.call("jg_norm_linear", ws.qkv.ptr, ws.h.ptr, self.attention_norm.weight.ptr, self.attention_norm.eps,
+                     wqkv.weight.ptr, wqkv.scale_ptr, B, wqkv.out_features, d)
         if a._kv.fused_attention:
             try:  # RoPE + cache write + attention in one cluster launch
                 dev.call("jg_attn_decode_fused", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, freqs_cis.ptr,
@@ -170,8 +175,13 @@ class TransformerBlock:
             apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
             dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
         a.wo.call(ws.attn, residual=ws.h, out=ws.h)
-        dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
-                 f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
+        if big:
+            self.ffn_norm.call(ws.h, out=ws.xn)
+            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, self.ffn_norm.eps, f.w1.weight.ptr,
+                     f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
+        else:
+            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
+                     f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
         f.w2.call(ws.ffn, residual=ws.h, out=ws.h)
 
     __call__ = call
@@ -197,6 +207,7 @@ class _Workspace:
         self.tokens = Tensor.zeros((B,), "int32", dev)
         self.pos = Tensor.zeros((B,), "int32", dev)
         self.h = Tensor.empty((B, dim), "float16", dev)
+        self.xn = Tensor.empty((B, dim), "float16", dev)
         self.qkv = Tensor.empty((B, qkv_dim), "float16", dev)
         self.attn = Tensor.empty((B, q_dim), "float16", dev)
         self.ffn = Tensor.empty((B, hidden), "float16", dev)
@@ -295,8 +306,13 @@ class Transformer:
             for layer in self.layers:
                 layer.call_fused(ws, ws.pos, self.freqs_cis)
             out = self.output
-            dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.h.ptr, self.norm.weight.ptr, self.norm.eps,
-                     out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
+            if B > 8:
+                self.norm.call(ws.h, out=ws.xn)
+                dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
+                         out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
+            else:
+                dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.h.ptr, self.norm.weight.ptr, self.norm.eps,
+                         out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
             dev.call("jg_argmax_finalize", ws.next_tokens.ptr, ws.key.ptr, B)
         else:
             h = ws.h

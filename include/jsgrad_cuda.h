@@ -105,7 +105,10 @@ int jg_embed(jg_dev* dev, uint64_t out, uint64_t tokens, uint64_t w, uint64_t sc
 int jg_rmsnorm(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, int32_t rows, int32_t dim, float eps);
 
 /* Linear.call / Int8Linear.call: jsgrad/nn/index.ts:411, jsgrad/models/llama3.ts:35; `residual` (0 = none) is
- * the `x.add(...)` of TransformerBlock.call, jsgrad/models/llama.ts:125-126, fused as an epilogue. */
+ * the `x.add(...)` of TransformerBlock.call, jsgrad/models/llama.ts:125-126, fused as an epilogue.
+ * Row counts: M <= 8 streams the weights through the CUDA cores; 8 < M <= 64 through the tensor cores (fp16 weights
+ * only, and the fused-norm entry points then want norm_w = 0 with rows normalised by jg_rmsnorm first); larger M is
+ * JG_ENOTSUP (split the rows into chunks of 64). */
 int jg_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, uint64_t scale, uint64_t residual, int32_t M,
               int32_t N, int32_t K);
 
@@ -124,7 +127,8 @@ int jg_swiglu(jg_dev* dev, uint64_t y, uint64_t g, uint64_t u, int64_t n);
 
 /* Final norm + output projection for M rows + greedy selection: writes the fp16 logits [M][V] and folds
  * (value, lowest index) into key[M] (uint64 each, must be zero on entry); jg_argmax_finalize turns the keys into
- * int32 token ids and re-zeroes them.  jsgrad/models/llama.ts:210-212,137; jsgrad/tensor.ts:2314-2320. */
+ * int32 token ids and re-zeroes them.  jsgrad/models/llama.ts:210-212,137; jsgrad/tensor.ts:2314-2320.
+ * norm_w = 0 skips the norm (rows already normalised). */
 int jg_norm_logits_argmax(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
                           uint64_t w, uint64_t scale, int32_t M, int32_t V, int32_t K);
 int jg_argmax_finalize(jg_dev* dev, uint64_t tokens_out, uint64_t key, int32_t M);

@@ -194,6 +194,36 @@ def test_fused_norm_projections(dev, M, int8):
     assert (key.numpy() == 0).all()
 
 
+@pytest.mark.parametrize("M", [9, 16, 17, 32, 40, 64])
+def test_tensor_core_projection(dev, M):
+    """8 < M <= 64 rows: mma.sync path, every epilogue, ragged N / K, all K-split variants (chosen from N)."""
+    rng = np.random.default_rng(500 + M)
+    for N, K in [(64, 256), (1027, 2048), (333, 1040), (2048, 8192), (40000, 512)]:
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+        res = rng.standard_normal((M, N)).astype(np.float16)
+        xt, wt, rt = Tensor(x, device=dev), Tensor(w, device=dev), Tensor(res, device=dev)
+        y = Tensor.empty((M, N), "float16", dev)
+        ref = O.linear_f16(x, w)
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, 0, 0, M, N, K)
+        assert_reduction_close(y.numpy(), ref, max_ulp=1, max_frac=0.05, what=f"mma linear M{M} N{N} K{K}")
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, 0, rt.ptr, M, N, K)
+        ref_r = (res.astype(np.float32) + ref.astype(np.float32)).astype(np.float16)
+        assert_reduction_close(y.numpy(), ref_r, max_ulp=2, max_frac=0.06, what=f"mma linear+residual M{M} N{N} K{K}")
+        if N <= 2048:
+            w3 = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+            w3t = Tensor(w3, device=dev)
+            dev.call("jg_norm_swiglu", y.ptr, xt.ptr, 0, 1e-5, wt.ptr, 0, w3t.ptr, 0, M, N, K)
+            assert_reduction_close(y.numpy(), O.swiglu(ref, O.linear_f16(x, w3)), max_ulp=3, max_frac=0.12, what=f"mma swiglu M{M} N{N} K{K}")
+        key = Tensor.zeros((M,), "uint64", dev)
+        tok = Tensor.empty((M,), "int32", dev)
+        dev.call("jg_norm_logits_argmax", y.ptr, key.ptr, xt.ptr, 0, 1e-5, wt.ptr, 0, M, N, K)
+        dev.call("jg_argmax_finalize", tok.ptr, key.ptr, M)
+        got = y.numpy()
+        assert_reduction_close(got, ref, max_ulp=1, max_frac=0.05, what=f"mma logits M{M} N{N} K{K}")
+        assert tok.numpy().tolist() == [O.argmax_f16(r) for r in got]
+
+
 # ------------------------------------------------------------------------------------------------ RoPE + attention
 @pytest.mark.parametrize("hd,H,G", [(64, 32, 8), (128, 24, 8), (128, 8, 8), (64, 4, 2), (128, 16, 2)])
 @pytest.mark.parametrize("B,T,n_split", [(1, 1, 0), (1, 97, 0), (2, 300, 3), (1, 1000, 0), (3, 65, 1)])
@@ -268,11 +298,14 @@ def test_invalid_arguments_are_rejected_before_launch(dev):
     assert e.value.status == ffi.JG_EINVAL
     with pytest.raises(ValueError):
         Tensor.empty((0,), "float16", dev)  # "alloc size must be positve", as the reference's Allocator.alloc
-    x9 = Tensor.zeros((9, 64), "float16", dev)
-    y9 = Tensor.zeros((9, 16), "float16", dev)
+    x9 = Tensor.zeros((65, 64), "float16", dev)
+    y9 = Tensor.zeros((65, 16), "float16", dev)
     with pytest.raises(ffi.JgError) as e:
-        dev.call("jg_linear", y9.ptr, x9.ptr, w.ptr, 0, 0, 9, 16, 64)  # more rows than the matrix-vector kernels take
+        dev.call("jg_linear", y9.ptr, x9.ptr, w.ptr, 0, 0, 65, 16, 64)  # more rows than one projection call takes
     assert e.value.status == ffi.JG_ENOTSUP
+    with pytest.raises(ffi.JgError) as e:  # the fused-norm entry points want pre-normalised rows above 8
+        dev.call("jg_norm_linear", y9.ptr, x9.ptr, w.ptr, 1e-5, w.ptr, 0, 9, 16, 64)
+    assert e.value.status == ffi.JG_ENOTSUP and "normalise" in str(e.value)
     with pytest.raises(ffi.JgError) as e:
         h = C.c_void_p()
         ffi.call("jg_device_open", 99, C.byref(h))

@@ -52,6 +52,21 @@ def test_tiny_model_matches_fixture_and_live_checker(quant):
     assert np.abs(logits2 - g["logits"].astype(np.float32)).max() <= LOGIT_TOL
 
 
+def test_batch_16_goes_through_the_tensor_core_projections():
+    """More than 8 rows per step: norms run as their own kernel and the projections on the tensor cores."""
+    prompt = synth.prompt_tokens(5, TINY["vocab_size"], batch=16, seed=21)
+    llm = make("1B", args=TINY, max_context=64, max_batch=16, tied_output=True)
+    m = build_oracle(TINY, max_context=64, max_batch=16, int8=False, tied=True)
+    ref_ids, ref_logits, margins = oracle_greedy(m, prompt, 6)
+    ids, logits = greedy_with_logits(llm, prompt, 6)
+    assert np.abs(logits - ref_logits).max() <= LOGIT_TOL
+    ulp = 2.0 ** (np.floor(np.log2(np.abs(ref_logits.max(axis=2)))) - 10)
+    safe = (margins / ulp) >= 3
+    for b in range(16):
+        n = 6 if safe[:, b].all() else int(np.argmin(safe[:, b]))
+        assert (ids[b, :n] == ref_ids[b, :n]).all(), b
+
+
 def test_weights_on_device_equal_the_checkers(dev):
     """The device-side seeded fill and the CPU generator produce the same model (spot-check every tensor kind)."""
     from tests.util import synth_weight, tensor_shapes
