@@ -258,10 +258,12 @@ def run_gpu(args) -> None:
     ws = model._workspace(B)
     d, f = p["dim"], p["hidden_dim"]
 
+    big = B > 8 or (B >= 3 and not int8)
+
     def gateup(layer):
         ff = layer.feed_forward
         # above 8 rows the projection takes pre-normalised rows (ws.xn) and runs on the tensor cores
-        dev.call("jg_norm_swiglu", ws.ffn.ptr, (ws.xn if B > 8 else ws.h).ptr, 0 if B > 8 else layer.ffn_norm.weight.ptr,
+        dev.call("jg_norm_swiglu", ws.ffn.ptr, (ws.xn if big else ws.h).ptr, 0 if big else layer.ffn_norm.weight.ptr,
                  layer.ffn_norm.eps, ff.w1.weight.ptr, ff.w1.scale_ptr, ff.w3.weight.ptr, ff.w3.scale_ptr, B, f, d)
 
     for layer in model.layers:
@@ -289,7 +291,7 @@ def run_gpu(args) -> None:
                 "ms_per_step": e2e_secs / K * 1e3},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
-        "roofline": {"bound": "hbm", "kernel": ("gemm_small_kernel (gate/up + SwiGLU instantiation)" if B > 8 else "gemv_kernel (norm + gate/up + SwiGLU instantiation)"), "achieved": k_gbs,
+        "roofline": {"bound": "hbm", "kernel": ("gemm_small_kernel (gate/up + SwiGLU instantiation)" if big else "gemv_kernel (norm + gate/up + SwiGLU instantiation)"), "achieved": k_gbs,
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k_gbs / peak, "traffic": None,
                      "bytes_per_launch": k_bytes, "us_per_launch": k_secs * 1e6,
                      "step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak,

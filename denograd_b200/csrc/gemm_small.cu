@@ -52,7 +52,7 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 }
 
 template <int MT, int KS, int EPI>
-__global__ void __launch_bounds__(GS_THREADS) gemm_small_kernel(const GemmSmallArgs a) {
+__global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_kernel(const GemmSmallArgs a) {
   constexpr int NT = MT / 8;                 // 8-row activation tiles
   constexpr int NW = (EPI == GS_SWIGLU) ? 2 : 1;
   constexpr int TILES = GS_WARPS / KS;       // 16-row weight tiles per CTA

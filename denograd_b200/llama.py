@@ -156,7 +156,9 @@ class TransformerBlock:
         a, f, dev, B = self.attention, self.feed_forward, ws.h.dev, ws.B
         d = ws.h.shape[-1]
         wqkv = a._wqkv
-        big = B > 8  # more rows than the fused-norm kernels take: normalise into ws.xn, then project on the tensor cores
+        # from 3 rows on (fp16 weights) normalise into ws.xn and project on the tensor cores; the fused-norm kernels
+        # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: up to 8 rows)
+        big = B > 8 or (B >= 3 and wqkv.scale_ptr == 0)
         if big:
             self.attention_norm.call(ws.h, out=ws.xn)
             dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, wqkv.weight.ptr, wqkv.scale_ptr, 0, B, wqkv.out_features, d)
@@ -306,7 +308,7 @@ class Transformer:
             for layer in self.layers:
                 layer.call_fused(ws, ws.pos, self.freqs_cis)
             out = self.output
-            if B > 8:
+            if B > 8 or (B >= 3 and out.scale_ptr == 0):
                 self.norm.call(ws.h, out=ws.xn)
                 dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
                          out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
