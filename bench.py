@@ -177,7 +177,8 @@ def workload_config(args, p) -> dict:
                          f"{args.prompt}-token seeded prompt in the KV cache"),
             "batch": args.batch, "prompt_tokens": args.prompt, "weights": args.quant, "layers": p["n_layers"],
             "l2": "inputs larger than L2: every step streams all weights (GBs) once, no flush needed",
-            "parallelism": "tp1" if args.gpus == 1 else f"{args.gpus} independent replicas"}
+            "parallelism": f"tp{args.gpus}" + ("" if args.gpus == 1 else
+                            ": heads / FFN width / vocabulary sharded, NCCL fp32 all-reduce after wo and w2")}
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
@@ -202,8 +203,15 @@ def run_gpu(args) -> None:
     max_ctx = P + 2 * (K + W) + 16
     max_ctx = (max_ctx + 63) // 64 * 64
     dev_name = "CUDA" if local_rank == 0 else f"CUDA:{local_rank}"
+    tp = None
+    if world > 1:
+        # tensor parallel over the ranks: rank 0 makes the NCCL id, torch.distributed carries it to the others
+        from denograd_b200.multi import TensorParallel
+        box = [TensorParallel.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        tp = TensorParallel(Device[dev_name], rank, world, box[0])
     llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=B, device=dev_name,
-                 n_layers=p["n_layers"]).load_synthetic()
+                 n_layers=p["n_layers"], tp=tp).load_synthetic()
     dev = llm.model.dev
     model = llm.model
 
@@ -221,7 +229,7 @@ def run_gpu(args) -> None:
         return float(t.item())
 
     # ---- untimed set-up: the prompt goes through the model one position at a time (fills the KV cache)
-    prompt = synth.prompt_tokens(P, p["vocab_size"], batch=B, seed=synth.PROMPT_SEED + rank)
+    prompt = synth.prompt_tokens(P, p["vocab_size"], batch=B, seed=synth.PROMPT_SEED)
     first = llm._prefill(prompt).numpy()
     pos0 = llm.start_pos
 
@@ -237,7 +245,7 @@ def run_gpu(args) -> None:
         barrier()
     launches = dev.launch_count() - launches0
     secs = max_over_ranks(secs)
-    value = world * B * K / secs
+    value = B * K / secs  # one model sharded over the ranks: the job's tokens are the batch's tokens
 
     # ---- e2e: public per-token API with host buffers (pinned H2D of ids + positions, D2H of the chosen ids)
     llm.start_pos = pos0 + W + K
@@ -250,13 +258,13 @@ def run_gpu(args) -> None:
         tok = model.call_host(tok.reshape(B, 1), llm.start_pos); llm.start_pos += 1
     e2e_secs = max_over_ranks(dev.timer_stop())
     barrier()
-    e2e_value = world * B * K / e2e_secs
+    e2e_value = B * K / e2e_secs
 
     # ---- roofline of the dominant kernel, timed alone: gate/up projection (norm + two matrices + SwiGLU) of every
     #      layer in turn, so that consecutive launches never find their weights in L2
     peak, peak_kind = measured_peaks()
     ws = model._workspace(B)
-    d, f = p["dim"], p["hidden_dim"]
+    d, f = p["dim"], p["hidden_dim"] // world  # f: this rank's share of the FFN width
 
     big = B > 8 or (B >= 3 and not int8)
 
@@ -279,12 +287,12 @@ def run_gpu(args) -> None:
     k_gbs = k_bytes / k_secs / 1e9
 
     t_mid = pos0 + W + K / 2.0  # mean cached length over the timed steps
-    step_bytes = weight_bytes(p, tied, int8) + B * t_mid * kv_bytes_per_token(p) + B * d * 2
+    step_bytes = (weight_bytes(p, tied, int8) + B * t_mid * kv_bytes_per_token(p)) / world + B * d * 2  # per GPU
     step_gbs = step_bytes / (secs / K) / 1e9
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-        "ms_per_step": secs / K * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": secs / K * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16 activations, f32 accumulate, " + ("i8 weights" if int8 else "f16 weights"), "data": "synthetic",
         "config": workload_config(args, p),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 8 * B, "d2h_bytes_per_step": 4 * B,
@@ -295,7 +303,7 @@ def run_gpu(args) -> None:
                      "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k_gbs / peak, "traffic": None,
                      "bytes_per_launch": k_bytes, "us_per_launch": k_secs * 1e6,
                      "step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak,
-                              "hbm_roofline_tok_s": B * peak * 1e9 / step_bytes}},
+                              "hbm_roofline_tok_s": B * peak * 1e9 / step_bytes, "per_gpu": True}},
     }
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_sample(args.model, int8, 8, 2)

@@ -633,8 +633,11 @@ JG_API int jg_kvcache_create(jg_dev* dev, const jg_kvcache_desc* desc, jg_kvcach
   return JG_OK;
 }
 
+static void kvcache_destroy_now(void* p) { jg_kvcache_destroy((jg_kvcache*)p); }
+
 JG_API int jg_kvcache_destroy(jg_kvcache* kv) {
   if (!kv) return JG_OK;
+  if (g_jg_capturing > 0) { jg_defer(kvcache_destroy_now, kv); return JG_OK; }
   cudaSetDevice(kv->dev->ordinal);
   cudaStreamSynchronize(kv->dev->stream);
   cudaFree(kv->k_pool); cudaFree(kv->v_pool); cudaFree(kv->block_table); cudaFree(kv->scores);

@@ -29,6 +29,12 @@ struct jg_graph {
 };
 
 void jg_set_error(const char* fmt, ...);
+// Releases that may not run while a stream capture is in progress (cudaFree / cudaFreeHost / a stream synchronise
+// invalidate the capture): a host whose garbage collector finalises an object in the middle of a capture gets its
+// release queued here and carried out right after jg_graph_end.
+extern int g_jg_capturing;  // devices of this process with a capture in progress
+void jg_defer(void (*fn)(void*), void* p);
+void jg_run_deferred(void);
 int jg_cuda_fail(cudaError_t e, const char* what, const char* file, int line);
 
 #define JG_CUDA(call)                                                        \

@@ -24,6 +24,21 @@ int jg_cuda_fail(cudaError_t e, const char* what, const char* file, int line) {
 
 JG_API const char* jg_last_error(void) { return g_err; }
 
+int g_jg_capturing = 0;
+static struct { void (*fn)(void*); void* p; } g_deferred[1024];
+static int g_n_deferred = 0;
+
+void jg_defer(void (*fn)(void*), void* p) {
+  if (g_n_deferred < 1024) { g_deferred[g_n_deferred].fn = fn; g_deferred[g_n_deferred].p = p; g_n_deferred++; }
+  // a full queue leaks the object rather than break the capture
+}
+void jg_run_deferred(void) {
+  if (g_jg_capturing > 0) return;
+  const int n = g_n_deferred;
+  g_n_deferred = 0;
+  for (int i = 0; i < n; i++) g_deferred[i].fn(g_deferred[i].p);
+}
+
 JG_API int jg_device_count(int32_t* out) {
   JG_REQUIRE(out != nullptr, "null output pointer");
   int n = 0;
@@ -110,8 +125,8 @@ JG_API int jg_alloc(jg_dev* dev, size_t nbytes, uint64_t* dptr) {
 
 JG_API int jg_free(jg_dev* dev, uint64_t dptr) {
   JG_ENTER(dev);
-  JG_REQUIRE(!dev->capturing, "free while a graph is being captured");
   if (dptr == 0) return JG_OK;
+  if (g_jg_capturing > 0) { jg_defer([](void* p) { cudaFree(p); }, (void*)(uintptr_t)dptr); return JG_OK; }
   JG_CUDA(cudaStreamSynchronize(dev->stream));
   JG_CUDA(cudaFree((void*)(uintptr_t)dptr));
   return JG_OK;
@@ -195,8 +210,12 @@ JG_API int jg_host_alloc(size_t nbytes, void** out) {
   return JG_OK;
 }
 
+static void host_free_now(void* p) { cudaFreeHost(p); }
+
 JG_API int jg_host_free(void* p) {
-  if (p) JG_CUDA(cudaFreeHost(p));
+  if (!p) return JG_OK;
+  if (g_jg_capturing > 0) { jg_defer(host_free_now, p); return JG_OK; }
+  JG_CUDA(cudaFreeHost(p));
   return JG_OK;
 }
 
@@ -224,6 +243,7 @@ JG_API int jg_graph_begin(jg_dev* dev) {
   JG_REQUIRE(!dev->capturing, "graph capture already in progress");
   JG_CUDA(cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeThreadLocal));
   dev->capturing = true;
+  g_jg_capturing++;
   dev->capture_launches = 0;
   return JG_OK;
 }
@@ -233,6 +253,7 @@ JG_API int jg_graph_end(jg_dev* dev, jg_graph** out) {
   JG_REQUIRE(out != nullptr, "null output pointer");
   JG_REQUIRE(dev->capturing, "no graph capture in progress");
   dev->capturing = false;
+  g_jg_capturing--;
   cudaGraph_t g = nullptr;
   JG_CUDA(cudaStreamEndCapture(dev->stream, &g));
   cudaGraphExec_t exec = nullptr;
@@ -246,6 +267,7 @@ JG_API int jg_graph_end(jg_dev* dev, jg_graph** out) {
   gr->exec = exec;
   gr->n_kernels = dev->capture_launches;
   *out = gr;
+  jg_run_deferred();
   return JG_OK;
 }
 
@@ -258,8 +280,16 @@ JG_API int jg_graph_launch(jg_dev* dev, jg_graph* g) {
   return JG_OK;
 }
 
+static void graph_destroy_now(void* p) {
+  jg_graph* g = (jg_graph*)p;
+  if (g->exec) cudaGraphExecDestroy(g->exec);
+  if (g->graph) cudaGraphDestroy(g->graph);
+  delete g;
+}
+
 JG_API int jg_graph_destroy(jg_graph* g) {
   if (!g) return JG_OK;
+  if (g_jg_capturing > 0) { jg_defer(graph_destroy_now, g); return JG_OK; }
   if (g->exec) cudaGraphExecDestroy(g->exec);
   if (g->graph) cudaGraphDestroy(g->graph);
   delete g;

@@ -295,3 +295,57 @@ JG_API int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value)
   fill_const_f16_kernel<<<fill_blocks(dev, n), 256, 0, dev->stream>>>((__half*)dst, n, __float2half_rn(value));
   return jg_after_launch(dev, "fill_const_f16");
 }
+
+// ------------------------------------------------------------------------------------------------ tensor-parallel helpers
+// h <- h + half(p): the residual add of TransformerBlock.call (jsgrad/models/llama.ts:125-126) applied to the fp32 sum
+// of a row-parallel projection after its all-reduce: one rounding of the full sum to fp16, then the fp16 add, exactly
+// as on a single device.
+__global__ void residual_add_f32_kernel(__half* __restrict__ h, const float* __restrict__ p, long long n4) {
+  pdl_launch();
+  pdl_wait();
+  for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < n4; c += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(p)[c];
+    uint2 raw = reinterpret_cast<uint2*>(h)[c];
+    __half* hh = reinterpret_cast<__half*>(&raw);
+    hh[0] = hadd1(hh[0], __float2half_rn(v.x));
+    hh[1] = hadd1(hh[1], __float2half_rn(v.y));
+    hh[2] = hadd1(hh[2], __float2half_rn(v.z));
+    hh[3] = hadd1(hh[3], __float2half_rn(v.w));
+    reinterpret_cast<uint2*>(h)[c] = raw;
+  }
+}
+
+JG_API int jg_residual_add_f32(jg_dev* dev, uint64_t h, uint64_t p32, int64_t n) {
+  JG_ENTER(dev);
+  JG_REQUIRE(n > 0 && n % 4 == 0, "residual_add_f32: element count %lld must be a positive multiple of 4", (long long)n);
+  JG_REQUIRE(jg_aligned(h, 8) && jg_aligned(p32, 16), "residual_add_f32: null or misaligned pointer");
+  const long long n4 = n / 4;
+  int blocks = (int)((n4 + 255) / 256);
+  if (blocks > dev->sm_count * 4) blocks = dev->sm_count * 4;
+  return jg_launch(dev, "residual_add_f32", residual_add_f32_kernel, dim3(blocks), dim3(256), 0, (__half*)h, (const float*)p32, n4);
+}
+
+// Seeded normal fill of a [rows][cols] window of a [*][full_cols] tensor starting at (row0, col0): element (r, c) takes
+// generator index (row0 + r) * full_cols + col0 + c, so a shard holds exactly the values the whole tensor would.
+__global__ void fill_normal_f16_2d_kernel(__half* __restrict__ dst, unsigned long long seed, unsigned long long rows,
+                                          unsigned long long cols, unsigned long long full_cols, unsigned long long row0,
+                                          unsigned long long col0, float c) {
+  const unsigned long long n = rows * cols;
+  for (unsigned long long j = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; j < n;
+       j += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned long long r = j / cols, cc = j % cols;
+    const unsigned long long i = (row0 + r) * full_cols + col0 + cc;
+    int S = (int)(synth_sum16(synth_word(seed, 3 * i)) + synth_sum16(synth_word(seed, 3 * i + 1)) +
+                  synth_sum16(synth_word(seed, 3 * i + 2)));
+    dst[j] = __float2half_rn(__fmul_rn((float)(S - 393210), c));
+  }
+}
+
+JG_API int jg_fill_normal_f16_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
+                                 uint64_t row0, uint64_t col0, float std) {
+  JG_ENTER(dev);
+  JG_REQUIRE(rows > 0 && cols > 0 && col0 + cols <= full_cols && jg_aligned(dst, 2), "fill_normal_f16_2d: bad arguments");
+  fill_normal_f16_2d_kernel<<<fill_blocks(dev, rows * cols), 256, 0, dev->stream>>>((__half*)dst, seed, rows, cols, full_cols,
+                                                                                   row0, col0, std / 65536.0f);
+  return jg_after_launch(dev, "fill_normal_f16_2d");
+}

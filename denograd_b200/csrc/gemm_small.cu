@@ -19,7 +19,7 @@
 #include "common.cuh"
 #include "transcendental.cuh"
 
-enum { GS_STORE = 0, GS_RESIDUAL = 1, GS_SWIGLU = 2, GS_LOGITS = 3 };
+enum { GS_STORE = 0, GS_RESIDUAL = 1, GS_SWIGLU = 2, GS_LOGITS = 3, GS_PARTIAL = 4 };
 
 struct GemmSmallArgs {
   const __half* x;   // [M][K]
@@ -28,7 +28,8 @@ struct GemmSmallArgs {
   __half* y;         // [M][N]
   const __half* residual;
   unsigned long long* key;  // [M] (LOGITS)
-  int M, N, K;
+  float* y32;               // [M][N] unrounded sums (PARTIAL)
+  int M, N, K, row_offset;
 };
 
 constexpr int GS_THREADS = 256;
@@ -188,12 +189,13 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
         const int row = row0 + g + 8 * (i >> 1), m = j * 8 + 2 * t + (i & 1);
         if (row < N && m < M) {
           const size_t o = (size_t)m * N + row;
+          if (EPI == GS_PARTIAL) { a.y32[o] = acc[0][j][i]; continue; }
           __half v = __float2half_rn(acc[0][j][i]);
           if (EPI == GS_RESIDUAL) v = hadd1(a.residual[o], v);
           if (EPI == GS_SWIGLU) v = jg_silu_mul(v, __float2half_rn(acc[NW - 1][j][i]));
           a.y[o] = v;
           if (EPI == GS_LOGITS) {
-            const unsigned long long k = argmax_key(v, (uint32_t)row);
+            const unsigned long long k = argmax_key(v, (uint32_t)(row + a.row_offset));
             best[j][i & 1] = k > best[j][i & 1] ? k : best[j][i & 1];
           }
         }
@@ -259,16 +261,19 @@ static int dispatch_mt(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
 
 // Entry used by gemv.cu's public functions for 8 < M <= 64 (fp16 weights).
 int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
-                  void* key, int M, int N, int K) {
+                  void* key, int M, int N, int K, int row_offset) {
   JG_REQUIRE(K % 8 == 0, "projection: K=%d must be a multiple of 8", K);
   GemmSmallArgs a = {};
   a.x = (const __half*)x; a.w0 = (const __half*)w0; a.w1 = (const __half*)w1; a.y = (__half*)y;
   a.residual = (const __half*)residual; a.key = (unsigned long long*)key; a.M = M; a.N = N; a.K = K;
+  a.row_offset = row_offset;
+  if (epi == GS_PARTIAL) { a.y = nullptr; a.y32 = (float*)y; }
   switch (epi) {
     case GS_STORE: return dispatch_mt<GS_STORE>(dev, a, "linear");
     case GS_RESIDUAL: return dispatch_mt<GS_RESIDUAL>(dev, a, "linear");
     case GS_SWIGLU: return dispatch_mt<GS_SWIGLU>(dev, a, "norm_swiglu");
     case GS_LOGITS: return dispatch_mt<GS_LOGITS>(dev, a, "norm_logits_argmax");
+    case GS_PARTIAL: return dispatch_mt<GS_PARTIAL>(dev, a, "linear_partial");
   }
   jg_set_error("projection: unknown epilogue %d", epi);
   return JG_EINVAL;

@@ -22,7 +22,7 @@
 #include "common.cuh"
 #include "transcendental.cuh"
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3, EPI_PARTIAL = 4 };
 
 struct GemvArgs {
   const __half* x;       // [M][K]
@@ -34,6 +34,8 @@ struct GemvArgs {
   __half* y;             // [M][N]
   const __half* residual;
   unsigned long long* key;  // [M] (LOGITS)
+  float* y32;               // [M][N] unrounded fp32 sums (PARTIAL: one rank's share of a row-parallel projection)
+  int row_offset;           // LOGITS: vocabulary index of weight row 0 (vocabulary-sharded output layer)
   float eps, recip_k;
   int M, N, K;
 };
@@ -183,12 +185,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
   // Final value of output (row, m) from the reduced sums of its NW matrices.
   auto finish = [&](int row, int m, float s_a, float s_b) {
     const size_t o = (size_t)m * N + (size_t)row;
+    if (EPI == EPI_PARTIAL) { a.y32[o] = s_a; return; }
     __half v = __float2half_rn(s_a);
     if (EPI == EPI_RESIDUAL) v = hadd1(a.residual[o], v);
     if (EPI == EPI_SWIGLU) v = jg_silu_mul(v, __float2half_rn(s_b));
     a.y[o] = v;
     if (EPI == EPI_LOGITS) {
-      const unsigned long long k = argmax_key(v, (uint32_t)row);
+      const unsigned long long k = argmax_key(v, (uint32_t)(row + a.row_offset));
       best = k > best ? k : best;
     }
   };
@@ -337,7 +340,7 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
 
 // gemm_small.cu: tensor-core projection for 9..64 rows (fp16 weights, activations already normalised)
 int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
-                  void* key, int M, int N, int K);
+                  void* key, int M, int N, int K, int row_offset);
 
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
@@ -345,10 +348,10 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
   // from 3 rows on the CUDA cores cannot keep up with the weight stream: unnormalised fp16 projections go to the
   // tensor-core kernel (measured on the 8B shapes: 48 us against 69 us at 4 rows and 106 us at 8 rows)
-  if (!W8 && !NORM && a.M >= 3 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.y, a.residual, a.key, a.M, a.N, a.K);
+  if (!W8 && !NORM && a.M >= 3 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
   if (a.M <= 8) return launch_gemv<8, W8, EPI, NORM>(dev, a, name);
-  if (!W8 && !NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.y, a.residual, a.key, a.M, a.N, a.K);
+  if (!W8 && !NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (NORM) jg_set_error("%s: with M=%d rows (> 8) normalise first (jg_rmsnorm) and pass norm_w = 0", name, a.M);
   else if (W8) jg_set_error("%s: M=%d rows (> 8) with int8 weights is not implemented", name, a.M);
   else jg_set_error("%s: M=%d rows is beyond the projection kernels (max 64 per call)", name, a.M);
@@ -408,8 +411,32 @@ JG_API int jg_norm_swiglu(jg_dev* dev, uint64_t y, uint64_t x, uint64_t norm_w, 
   return s_gate ? dispatch_m<true, EPI_SWIGLU, false>(dev, a, "norm_swiglu") : dispatch_m<false, EPI_SWIGLU, false>(dev, a, "norm_swiglu");
 }
 
+static int logits_impl(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps, uint64_t w,
+                       uint64_t scale, int32_t M, int32_t V, int32_t K, int32_t row_offset);
+
 JG_API int jg_norm_logits_argmax(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
                                  uint64_t w, uint64_t scale, int32_t M, int32_t V, int32_t K) {
+  return logits_impl(dev, logits, key, x, norm_w, eps, w, scale, M, V, K, 0);
+}
+
+JG_API int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
+                                       uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset) {
+  JG_REQUIRE(row_offset >= 0, "norm_logits_argmax_shard: negative row offset");
+  return logits_impl(dev, logits, key, x, norm_w, eps, w, scale, M, V_local, K, row_offset);
+}
+
+JG_API int jg_linear_partial(jg_dev* dev, uint64_t y32, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K) {
+  JG_ENTER(dev);
+  int rc = check_common("linear_partial", y32, x, w, scale, M, N, K);
+  if (rc) return rc;
+  JG_REQUIRE(jg_aligned(y32, 4), "linear_partial: misaligned output");
+  GemvArgs a = {};
+  a.x = (const __half*)x; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y32 = (float*)y32; a.M = M; a.N = N; a.K = K;
+  return scale ? dispatch_m<true, EPI_PARTIAL, false>(dev, a, "linear_partial") : dispatch_m<false, EPI_PARTIAL, false>(dev, a, "linear_partial");
+}
+
+static int logits_impl(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps, uint64_t w,
+                       uint64_t scale, int32_t M, int32_t V, int32_t K, int32_t row_offset) {
   JG_ENTER(dev);
   int rc = check_common("norm_logits_argmax", logits, x, w, scale, M, V, K);
   if (rc) return rc;
@@ -417,7 +444,7 @@ JG_API int jg_norm_logits_argmax(jg_dev* dev, uint64_t logits, uint64_t key, uin
   GemvArgs a = {};
   a.x = (const __half*)x; a.norm_w = (const __half*)norm_w; a.eps = eps; a.recip_k = (float)(1.0 / (double)K);
   a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)logits; a.key = (unsigned long long*)key;
-  a.M = M; a.N = V; a.K = K;
+  a.M = M; a.N = V; a.K = K; a.row_offset = row_offset;
   if (norm_w == 0) return scale ? dispatch_m<true, EPI_LOGITS, false>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, false>(dev, a, "norm_logits_argmax");
   return scale ? dispatch_m<true, EPI_LOGITS, true>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, true>(dev, a, "norm_logits_argmax");
 }

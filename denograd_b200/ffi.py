@@ -83,6 +83,15 @@ SIGNATURES: dict[str, list] = {
     "jg_fill_uniform_i8": [_vp, _u64, _u64, _u64, _u64],
     "jg_fill_scale_f16": [_vp, _u64, _u64, _u64, _u64, _f32],
     "jg_fill_const_f16": [_vp, _u64, _u64, _f32],
+    "jg_fill_normal_f16_2d": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _f32],
+    "jg_comm_unique_id": [C.c_char_p, _vp],
+    "jg_comm_init": [_vp, C.c_char_p, _vp, _i32, _i32, _P(_vp)],
+    "jg_comm_destroy": [_vp],
+    "jg_allreduce_sum_f32": [_vp, _u64, _u64],
+    "jg_allreduce_max_u64": [_vp, _u64, _u64],
+    "jg_linear_partial": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
+    "jg_residual_add_f32": [_vp, _u64, _u64, _i64],
+    "jg_norm_logits_argmax_shard": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32, _i32],
 }
 
 _lib: C.CDLL | None = None

@@ -80,10 +80,12 @@ def apply_rotary_emb_kvwrite(qkv: Tensor, freqs_cis: Tensor, pos: Tensor, kv: KV
 
 
 class Attention:
-    def __init__(self, dim: int, n_heads: int, n_kv_heads: int | None, max_context: int, linear=Linear, device=None):
+    def __init__(self, dim: int, n_heads: int, n_kv_heads: int | None, max_context: int, linear=Linear, device=None,
+                 head_dim: int | None = None):
+        # under tensor parallelism n_heads / n_kv_heads are this rank's share and head_dim is given explicitly
         self.n_heads = n_heads
         self.n_kv_heads = n_kv_heads if n_kv_heads is not None else n_heads
-        self.head_dim = dim // n_heads
+        self.head_dim = head_dim if head_dim is not None else dim // n_heads
         self.n_rep = self.n_heads // self.n_kv_heads
         self.max_context = max_context
         dev = _dev(device)
@@ -139,8 +141,8 @@ class FeedForward:
 
 class TransformerBlock:
     def __init__(self, dim: int, hidden_dim: int, n_heads: int, n_kv_heads: int | None, norm_eps: float, max_context: int,
-                 linear=Linear, feed_forward=FeedForward, device=None):
-        self.attention = Attention(dim, n_heads, n_kv_heads, max_context, linear, device=device)
+                 linear=Linear, feed_forward=FeedForward, device=None, head_dim: int | None = None):
+        self.attention = Attention(dim, n_heads, n_kv_heads, max_context, linear, device=device, head_dim=head_dim)
         self.feed_forward = feed_forward(dim, hidden_dim, linear, device=device)
         self.attention_norm = RMSNorm(dim, norm_eps, device=device)
         self.ffn_norm = RMSNorm(dim, norm_eps, device=device)
@@ -150,7 +152,7 @@ class TransformerBlock:
         h = self.attention.call(self.attention_norm.call(x), pos, freqs_cis, mask, residual=x)
         return self.feed_forward.call(self.ffn_norm.call(h), residual=h)
 
-    def call_fused(self, ws: "_Workspace", pos: Tensor, freqs_cis: Tensor) -> None:
+    def call_fused(self, ws: "_Workspace", pos: Tensor, freqs_cis: Tensor, tp=None) -> None:
         """Same block on the workspace `ws` (h is updated in place) with the norms and elementwise ops folded into
         the projection kernels."""
         a, f, dev, B = self.attention, self.feed_forward, ws.h.dev, ws.B
@@ -176,7 +178,7 @@ class TransformerBlock:
         if not a._kv.fused_attention:
             apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
             dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
-        a.wo.call(ws.attn, residual=ws.h, out=ws.h)
+        self._row_parallel(a.wo, ws.attn, ws, tp)
         if big:
             self.ffn_norm.call(ws.h, out=ws.xn)
             dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, self.ffn_norm.eps, f.w1.weight.ptr,
@@ -184,7 +186,19 @@ class TransformerBlock:
         else:
             dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
                      f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
-        f.w2.call(ws.ffn, residual=ws.h, out=ws.h)
+        self._row_parallel(f.w2, ws.ffn, ws, tp)
+
+    @staticmethod
+    def _row_parallel(lin, x: Tensor, ws: "_Workspace", tp) -> None:
+        """h <- h + lin(x).  On one device the add is the projection's epilogue; under tensor parallelism `lin` holds a
+        K-slice, so its fp32 partial sums are all-reduced first and rounded + added afterwards."""
+        if tp is None:
+            lin.call(x, residual=ws.h, out=ws.h)
+            return
+        dev = ws.h.dev
+        dev.call("jg_linear_partial", ws.part32.ptr, x.ptr, lin.weight.ptr, lin.scale_ptr, ws.B, lin.out_features, lin.in_features)
+        tp.all_reduce_sum(ws.part32)
+        dev.call("jg_residual_add_f32", ws.h.ptr, ws.part32.ptr, ws.part32.numel())
 
     __call__ = call
 
@@ -216,6 +230,7 @@ class _Workspace:
         self.logits = Tensor.empty((B, vocab), "float16", dev)
         self.key = Tensor.zeros((B,), "uint64", dev)
         self.next_tokens = Tensor.zeros((B,), "int32", dev)
+        self.part32 = Tensor.empty((B, dim), "float32", dev)  # fp32 partial sums of a row-parallel projection
         # page-locked staging for the per-step token / position upload and the result read-back
         self._pinned = C.c_void_p()
         ffi.call("jg_host_alloc", 3 * 4 * B, C.byref(self._pinned))
@@ -262,17 +277,38 @@ class Transformer:
     def __init__(self, dim: int, hidden_dim: int, n_heads: int, n_layers: int, norm_eps: float, vocab_size: int,
                  linear=Linear, embedding=Embedding, n_kv_heads: int | None = None, rope_theta: float = 10000,
                  max_context: int = 1024, jit: bool = True, feed_forward=FeedForward, device=None, max_batch: int = 1,
-                 page_size: int = 64, tied_output: bool = False, fused: bool = True, n_split: int = 0):
+                 page_size: int = 64, tied_output: bool = False, fused: bool = True, n_split: int = 0, tp=None):
         dev = _dev(device)
-        self.dev, self.dim, self.hidden_dim, self.vocab_size = dev, dim, hidden_dim, vocab_size
-        self.n_heads, self.n_kv_heads = n_heads, (n_kv_heads if n_kv_heads is not None else n_heads)
+        self.dev, self.dim, self.vocab_size = dev, dim, vocab_size
         self.head_dim = dim // n_heads
+        n_kv_heads = n_kv_heads if n_kv_heads is not None else n_heads
+        self._tp = tp
+        self._shards = None
+        self.vocab_offset = 0
+        if tp is not None and not fused:
+            raise NotImplementedError("tensor parallelism runs on the fused block path")
+        if tp is not None:
+            # this rank's share (denograd_b200.multi.shard_plan): heads, kv heads, FFN width and vocabulary rows
+            from .multi import shard_plan
+            if embedding is not Embedding:
+                raise NotImplementedError("tensor parallelism is implemented for fp16 weights only")
+            full = {"dim": dim, "n_heads": n_heads, "n_kv_heads": n_kv_heads, "hidden_dim": hidden_dim,
+                    "vocab_size": vocab_size, "n_layers": n_layers}
+            self._shards = shard_plan(full, tp.rank, tp.world, tied_output)
+            n_heads, n_kv_heads, hidden_dim = n_heads // tp.world, n_kv_heads // tp.world, hidden_dim // tp.world
+            self.vocab_offset = tp.rank * (vocab_size // tp.world)
+        self.hidden_dim = hidden_dim
+        self.n_heads, self.n_kv_heads = n_heads, n_kv_heads
+        self.vocab_local = vocab_size // tp.world if tp is not None else vocab_size
         self.max_context, self.max_batch, self.fused = max_context, max_batch, fused
-        self.layers = [TransformerBlock(dim, hidden_dim, n_heads, n_kv_heads, norm_eps, max_context, linear, feed_forward, device=dev)
+        self.layers = [TransformerBlock(dim, hidden_dim, n_heads, n_kv_heads, norm_eps, max_context, linear, feed_forward,
+                                        device=dev, head_dim=self.head_dim)
                        for _ in range(n_layers)]
         self.norm = RMSNorm(dim, norm_eps, device=dev)
         self.tok_embeddings = embedding(vocab_size, dim, device=dev)
-        if tied_output:
+        if tp is not None:
+            self.output = Linear(dim, self.vocab_local, False, device=dev)  # rows [vocab_offset, +vocab_local) of the full matrix
+        elif tied_output:
             # output.weight is the embedding table itself (Llama-3.2 1B/3B; for quantised embeddings the reference
             # ties them as well, jsgrad/models/llama3.ts:55-58)
             if embedding is Embedding:
@@ -296,7 +332,7 @@ class Transformer:
             raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
         if B not in self._ws:
             qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
-            self._ws[B] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim, self.vocab_size)
+            self._ws[B] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim, self.vocab_local)
         return self._ws[B]
 
     def _step(self, ws: _Workspace, advance: bool = False) -> None:
@@ -306,15 +342,17 @@ class Transformer:
         self.tok_embeddings.call(ws.tokens, out=ws.h)
         if self.fused:
             for layer in self.layers:
-                layer.call_fused(ws, ws.pos, self.freqs_cis)
+                layer.call_fused(ws, ws.pos, self.freqs_cis, self._tp)
             out = self.output
             if B > 8 or (B >= 3 and out.scale_ptr == 0):
                 self.norm.call(ws.h, out=ws.xn)
-                dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
-                         out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
+                dev.call("jg_norm_logits_argmax_shard", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
+                         out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)
             else:
-                dev.call("jg_norm_logits_argmax", ws.logits.ptr, ws.key.ptr, ws.h.ptr, self.norm.weight.ptr, self.norm.eps,
-                         out.weight.ptr, out.scale_ptr, B, self.vocab_size, self.dim)
+                dev.call("jg_norm_logits_argmax_shard", ws.logits.ptr, ws.key.ptr, ws.h.ptr, self.norm.weight.ptr, self.norm.eps,
+                         out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)
+            if self._tp is not None:
+                self._tp.all_reduce_max(ws.key)  # best (value, lowest global index) over the vocabulary shards
             dev.call("jg_argmax_finalize", ws.next_tokens.ptr, ws.key.ptr, B)
         else:
             h = ws.h

@@ -54,6 +54,7 @@ class Llama3:
     jit: bool = True
     n_layers: int | None = None  # override the depth (reduced-depth slices of a big architecture for checks)
     tied_output: bool | None = None
+    tp: object | None = None  # denograd_b200.multi.TensorParallel: this process is one rank of a sharded model
     args: dict = field(default_factory=dict)
     last_seen_toks: list = field(default_factory=list)
 
@@ -73,7 +74,7 @@ class Llama3:
         self.model = Transformer(p["dim"], p["hidden_dim"], p["n_heads"], p["n_layers"], p["norm_eps"], p["vocab_size"],
                                  self.linear, self.embedding, p["n_kv_heads"], p["rope_theta"], self.max_context, self.jit,
                                  device=Device[self.device], max_batch=self.max_batch, page_size=self.page_size,
-                                 tied_output=tied, fused=self.fused)
+                                 tied_output=tied, fused=self.fused, tp=self.tp)
         self.usage = Llama3Usage()
         self.start_pos = 0
 

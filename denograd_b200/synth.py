@@ -59,11 +59,20 @@ def fill_tensor(name: str, t: Tensor, base_seed: int = BASE_SEED) -> None:
 
 
 def fill_model(model, base_seed: int = BASE_SEED) -> dict[str, Tensor]:
-    """Fill every weight of `model` (anything get_state_dict names except the RoPE table); tied tensors once."""
+    """Fill every weight of `model` (anything get_state_dict names except the RoPE table); tied tensors once.  A
+    tensor-parallel model holds windows of the full tensors: each is filled with the values the full tensor has there."""
     sd = get_state_dict(model)
+    shards = getattr(model, "_shards", None) or {}
     done: set[int] = set()
     for name, t in sd.items():
         if name == "freqs_cis" or t.ptr in done:
+            continue
+        if name in shards:
+            sh = shards[name]
+            assert tuple(t.shape) == (sh.rows, sh.cols), (name, t.shape, sh)
+            t.dev.call("jg_fill_normal_f16_2d", t.ptr, name_seed(sh.seed_name, base_seed), sh.rows, sh.cols, sh.cols_full,
+                       sh.row0, sh.col0, WEIGHT_STD)
+            done.add(t.ptr)
             continue
         # views of a fused allocation are filled through their own names, so each projection keeps its own stream
         fill_tensor(name, t, base_seed)

@@ -68,6 +68,15 @@ export const SYMBOLS = {
   jg_fill_uniform_i8: fn([ptr, u64, u64, u64, u64]),
   jg_fill_scale_f16: fn([ptr, u64, u64, u64, u64, f32]),
   jg_fill_const_f16: fn([ptr, u64, u64, f32]),
+  jg_fill_normal_f16_2d: fn([ptr, u64, u64, u64, u64, u64, u64, u64, f32]),
+  jg_comm_unique_id: fn([buf, buf]),
+  jg_comm_init: fn([ptr, buf, buf, i32, i32, buf]),
+  jg_comm_destroy: fn([ptr]),
+  jg_allreduce_sum_f32: fn([ptr, u64, u64]),
+  jg_allreduce_max_u64: fn([ptr, u64, u64]),
+  jg_linear_partial: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
+  jg_residual_add_f32: fn([ptr, u64, u64, 'i64']),
+  jg_norm_logits_argmax_shard: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32, i32]),
 } as const
 
 type Lib = { symbols: Record<keyof typeof SYMBOLS, (...a: any[]) => any> }

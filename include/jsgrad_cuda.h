@@ -199,12 +199,33 @@ int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint64_t k_l
  * kept on the device so a captured step can be replayed without host input). */
 int jg_pos_advance(jg_dev* dev, uint64_t pos, int32_t B);
 
+/* ---- Tensor parallelism.  The reference only declares a sharding plan (jsgrad/models/llama3.ts:239-249; its
+ *      jsgrad/multi.ts is a stub whose functions all throw), so these have no executable counterpart there.  One rank =
+ *      one process = one jg_dev.  Column-parallel projections (wq/wk/wv by heads, w1/w3, vocabulary-sharded output)
+ *      need no exchange; row-parallel ones (wo, w2) produce fp32 partial sums that are all-reduced before the single
+ *      rounding to fp16 and the residual add. */
+int jg_comm_unique_id(const char* nccl_path, void* id128);  /* rank 0 makes the 128-byte id; share it out of band */
+int jg_comm_init(jg_dev* dev, const char* nccl_path, const void* id128, int32_t rank, int32_t world, jg_comm** out);
+int jg_comm_destroy(jg_comm* comm);
+int jg_allreduce_sum_f32(jg_comm* comm, uint64_t buf, uint64_t count);  /* in place, on the device's stream */
+int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count);  /* greedy keys of a sharded vocabulary */
+/* y32[m][n] = sum_k x[m][k] W[n][k] left in fp32 (this rank's K-slice of a row-parallel Linear, nn/index.ts:411). */
+int jg_linear_partial(jg_dev* dev, uint64_t y32, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K);
+/* h <- h + half(p32): rounding + residual add of jsgrad/models/llama.ts:125-126 after the all-reduce. */
+int jg_residual_add_f32(jg_dev* dev, uint64_t h, uint64_t p32, int64_t n);
+/* jg_norm_logits_argmax over rows [row_offset, row_offset + V_local) of the output matrix: keys carry global ids. */
+int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
+                                uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset);
+
 /* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the
  *      workloads replace by fixed distributions).  Counter-based, so any sub-range can be generated. */
 int jg_fill_normal_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float std);
 int jg_fill_uniform_i8(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n);
 int jg_fill_scale_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float base);
 int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value);
+/* [rows][cols] window at (row0, col0) of a [*][full_cols] tensor: a shard gets the values the whole tensor would. */
+int jg_fill_normal_f16_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
+                          uint64_t row0, uint64_t col0, float std);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,60 @@
+"""One tensor-parallel rank (a process with one GPU) for tests/test_tp_gpu.py.
+
+usage: python tests/tp_worker.py RANK WORLD WORKDIR [int batch] [int new_tokens]
+Rank 0 creates the NCCL id and leaves it in WORKDIR/id.bin; every rank builds its shard of the TINY model, generates
+greedily, and writes WORKDIR/out_<rank>.npz (ids, local logits slice, vocabulary offset).
+"""
+import os
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from denograd_b200 import Device, synth  # noqa: E402
+from denograd_b200.llama3 import Llama3  # noqa: E402
+from denograd_b200.multi import TensorParallel  # noqa: E402
+from tests.golden.gen_golden import TINY  # noqa: E402
+
+
+def main() -> None:
+    import faulthandler
+    # a rank that stops making progress (its peer died, say) reports where it is and leaves by itself
+    faulthandler.dump_traceback_later(90, exit=True)
+    rank, world, work = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
+    batch = int(sys.argv[4]) if len(sys.argv) > 4 else 2
+    n_new = int(sys.argv[5]) if len(sys.argv) > 5 else 8
+    dev = Device[f"CUDA:{rank}"]
+    id_path = os.path.join(work, "id.bin")
+    if rank == 0:
+        uid = TensorParallel.unique_id()
+        with open(id_path + ".tmp", "wb") as f:
+            f.write(uid)
+        os.replace(id_path + ".tmp", id_path)
+    else:
+        deadline = time.time() + 120
+        while not os.path.exists(id_path):  # host-side wait with a deadline; no GPU work is pending meanwhile
+            if time.time() > deadline:
+                raise TimeoutError("rank 0 never published the NCCL id")
+            time.sleep(0.05)
+        uid = open(id_path, "rb").read()
+    tp = TensorParallel(dev, rank, world, uid)
+    llm = Llama3(size="1B", args=TINY, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
+    ids = llm.generate(prompt, n_new)
+    logits = llm.model.last_logits(batch)
+    # the graph-replayed device loop must agree with the per-token API under sharding too
+    llm2 = Llama3(size="1B", args=TINY, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    first = llm2._prefill(prompt).numpy()
+    loop = llm2.model.decode_loop(first, llm2.start_pos, n_new - 1)
+    np.savez(os.path.join(work, f"out_{rank}.npz"), ids=ids, logits=logits, offset=llm.model.vocab_offset,
+             loop=np.concatenate([first[:, None], loop], axis=1))
+    dev.synchronize()
+    # the communicator is left to process exit: NCCL waits in ncclCommDestroy for captured graphs that still hold its
+    # collectives, and the models (with their graphs) are alive here
+
+
+if __name__ == "__main__":
+    main()
