@@ -286,6 +286,9 @@ def run_gpu(args) -> None:
     k_bytes = 2 * f * d * (1 if int8 else 2) + (2 * f * 2 if int8 else 0) + B * d * 2 + d * 2 + B * f * 2
     k_gbs = k_bytes / k_secs / 1e9
 
+    # DRAM bytes of one gate/up launch from the committed ncu capture (profiles/gemv_kernel_8b_fp16_bs1.md): read +
+    # write of the 8B fp16 batch-1 shape; other shapes have no capture yet
+    traffic = 239192832 if (args.model == "8B" and not int8 and B == 1 and world == 1) else None
     t_mid = pos0 + W + K / 2.0  # mean cached length over the timed steps
     step_bytes = (weight_bytes(p, tied, int8) + B * t_mid * kv_bytes_per_token(p)) / world + B * d * 2  # per GPU
     step_gbs = step_bytes / (secs / K) / 1e9
@@ -300,7 +303,7 @@ def run_gpu(args) -> None:
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "kernel": ("gemm_small_kernel (gate/up + SwiGLU instantiation)" if big else "gemv_kernel (norm + gate/up + SwiGLU instantiation)"), "achieved": k_gbs,
-                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k_gbs / peak, "traffic": None,
+                     "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k_gbs / peak, "traffic": traffic,
                      "bytes_per_launch": k_bytes, "us_per_launch": k_secs * 1e6,
                      "step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak,
                               "hbm_roofline_tok_s": B * peak * 1e9 / step_bytes, "per_gpu": True}},
