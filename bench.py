@@ -210,7 +210,8 @@ def run_gpu(args) -> None:
         box = [TensorParallel.unique_id() if rank == 0 else None]
         dist.broadcast_object_list(box, src=0)
         tp = TensorParallel(Device[dev_name], rank, world, box[0])
-    llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=B, device=dev_name,
+    xb = 0 if (args.no_extra or int8) else 32  # batch of the extra batched-decode leg (fp16 weights only)
+    llm = Llama3(size=args.model, quantize=args.quant, max_context=max_ctx, max_batch=max(B, xb), device=dev_name,
                  n_layers=p["n_layers"], tp=tp).load_synthetic()
     dev = llm.model.dev
     model = llm.model
@@ -308,6 +309,43 @@ def run_gpu(args) -> None:
                      "step": {"bytes_per_step": step_bytes, "achieved": step_gbs, "frac": step_gbs / peak,
                               "hbm_roofline_tok_s": B * peak * 1e9 / step_bytes, "per_gpu": True}},
     }
+    # ---- extra legs of the same metric family: prompt processing (one multi-position forward) and batch-32 decode
+    if not args.no_extra:
+        extra = {}
+        flops_per_tok = 2 * (weight_bytes(p, tied, int8) // (1 if int8 else 2)) / world  # 2 flops per weight, per GPU
+        tf_peak = 1636.2
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+                tf_peak = float(json.load(fh)["bf16_tflops"])
+        except Exception:
+            pass
+        pl = prompt[:1, :P]
+        llm.reset(); llm.prefill(pl); dev.synchronize()  # warm-up (kernels' attributes, workspaces)
+        reps = 3
+        barrier()
+        dev.timer_start()
+        for _ in range(reps):
+            llm.reset()
+            llm.prefill(pl)
+        pf = max_over_ranks(dev.timer_stop()) / reps
+        extra["prefill"] = {"tok_s": P / pf, "ms": pf * 1e3, "prompt_tokens": P, "batch": 1,
+                            "tflops_per_gpu": flops_per_tok * P / pf / 1e12, "frac_of_measured_bf16_peak": flops_per_tok * P / pf / 1e12 / tf_peak,
+                            "how": "Transformer.forward over the whole prompt in 64-row chunks: mma.sync projections, weights re-streamed per chunk"}
+        if xb:
+            pb = synth.prompt_tokens(P, p["vocab_size"], batch=xb, seed=synth.PROMPT_SEED)
+            llm.reset()
+            first_b = llm.prefill(pb).numpy()
+            model.decode_loop(first_b, llm.start_pos, W, collect=False)
+            barrier()
+            kb = max(8, K // 4)
+            dev.timer_start()
+            model.decode_loop(first_b, llm.start_pos + W, kb, collect=False, resume=True)
+            sb = max_over_ranks(dev.timer_stop())
+            tb = llm.start_pos + W + kb / 2.0
+            bytes_b = (weight_bytes(p, tied, int8) + xb * tb * kv_bytes_per_token(p)) / world + xb * d * 2
+            extra["decode_bs32"] = {"tok_s": xb * kb / sb, "ms_per_step": sb / kb * 1e3, "batch": xb, "steps": kb,
+                                    "context": int(tb), "frac_of_hbm_roofline": bytes_b / (sb / kb) / 1e9 / peak}
+        line["extra"] = extra
     if rank == 0 and world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_sample(args.model, int8, 8, 2)
     if rank == 0:
@@ -328,6 +366,7 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0, help="reduced depth (profiling captures only; 0 = the model's own)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the prefill and batch-32 legs")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

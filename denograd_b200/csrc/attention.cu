@@ -289,7 +289,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_pv_kernel(const AttnArgs a) 
 __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __restrict__ table,
                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ block_table,
                                     __half* __restrict__ k_layer, __half* __restrict__ v_layer, int B, int H, int G,
-                                    int hd, int page, int page_shift, int max_pages_per_seq, int table_rows) {
+                                    int hd, int page, int page_shift, int max_pages_per_seq, int table_rows,
+                                    const int32_t* __restrict__ seq) {
   pdl_launch();
   pdl_wait();
   const int per_head = hd / 8;
@@ -321,7 +322,7 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
     } else {
       const int g = (h < H + G) ? (h - H) : (h - H - G);
       __half* layer = (h < H + G) ? k_layer : v_layer;
-      const int pg = block_table[(size_t)b * max_pages_per_seq + (p >> page_shift)];
+      const int pg = block_table[(size_t)(seq ? seq[b] : b) * max_pages_per_seq + (p >> page_shift)];
       const int slot = p & (page - 1);
       *reinterpret_cast<uint4*>(layer + (((size_t)pg * G + g) * page + slot) * hd + (size_t)c * 8) = raw;
     }
@@ -346,8 +347,10 @@ struct AttnFusedArgs {
   __half* v_layer;
   const int32_t* block_table;
   const int32_t* pos;
+  const int32_t* seq;  // row -> sequence (block-table row); null = identity.  Several rows may belong to one sequence
   __half* out;
   int table_rows, qkv_stride, H, G, page, page_shift, max_pages_per_seq, max_ctx, chunk_cap;
+  int pre;  // 1: Q is already rotated and K/V are already in the cache (multi-position calls): attend only
   float scale;
 };
 
@@ -387,12 +390,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const At
   const int p = T - 1;  // position of the new token
   const int chunk = min((T + CS - 1) / CS, a.chunk_cap);  // the host sizes chunk_cap so that CS * chunk_cap >= max_ctx
   const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
-  const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
+  const int32_t* bt_row = a.block_table + (size_t)(a.seq ? a.seq[b] : b) * a.max_pages_per_seq;
   const __half* xrow = a.qkv + (size_t)b * a.qkv_stride;
-  const uint4 traw = ld_128(a.table + ((size_t)min(p, a.table_rows - 1) * (HD / 2) + (size_t)sub * 4) * 2);
+  const uint4 traw = a.pre ? make_uint4(0, 0, 0, 0)
+                           : ld_128(a.table + ((size_t)min(p, a.table_rows - 1) * (HD / 2) + (size_t)sub * 4) * 2);
 
   // ---- the owner of position p rotates K and stores the new K / V rows
-  if (t0 <= p && p < t1 && warp == 0 && lane < LPR) {
+  if (!a.pre && t0 <= p && p < t1 && warp == 0 && lane < LPR) {
     const uint4 kraw = ld_128(xrow + (size_t)(a.H + g) * HD + lane * 8);
     const uint4 vraw = ld_128(xrow + (size_t)(a.H + a.G + g) * HD + lane * 8);
     const int pg = bt_row[p >> a.page_shift], slot = p & (a.page - 1);
@@ -403,7 +407,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const At
   // ---- rotated query slices of the NREP heads of this group
   float qf[NREP][8];
 #pragma unroll
-  for (int r = 0; r < NREP; r++) unpack8(rope8(ld_128(xrow + (size_t)(g * NREP + r) * HD + sub * 8), traw), qf[r]);
+  for (int r = 0; r < NREP; r++) {
+    const uint4 qraw = ld_128(xrow + (size_t)(g * NREP + r) * HD + sub * 8);
+    unpack8(a.pre ? qraw : rope8(qraw, traw), qf[r]);
+  }
   __syncthreads();  // the new K / V rows are visible to this CTA's loads below
 
   // ---- scores of this rank's positions -> shared memory.  The V rows of the first iteration are requested right
@@ -663,12 +670,26 @@ JG_API int jg_kvcache_bytes(jg_kvcache* kv, uint64_t* out) {
   return JG_OK;
 }
 
+static int rope_kvwrite_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table, int32_t table_rows,
+                             uint64_t pos, uint64_t seq, int32_t B, int32_t H);
+
 JG_API int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table,
                            int32_t table_rows, uint64_t pos, int32_t B, int32_t H) {
+  return rope_kvwrite_impl(dev, kv, layer, qkv, table, table_rows, pos, 0, B, H);
+}
+
+JG_API int jg_rope_kvwrite_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table,
+                                int32_t table_rows, uint64_t pos, uint64_t seq, int32_t R, int32_t H) {
+  JG_REQUIRE(jg_aligned(seq, 4), "rope_kvwrite_rows: null or misaligned row->sequence map");
+  return rope_kvwrite_impl(dev, kv, layer, qkv, table, table_rows, pos, seq, R, H);
+}
+
+static int rope_kvwrite_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table, int32_t table_rows,
+                             uint64_t pos, uint64_t seq, int32_t B, int32_t H) {
   JG_ENTER(dev);
   JG_REQUIRE(kv != nullptr && kv->dev == dev, "rope_kvwrite: cache belongs to another device");
   JG_REQUIRE(layer >= 0 && layer < kv->d.n_layers, "rope_kvwrite: layer %d out of range", layer);
-  JG_REQUIRE(B > 0 && B <= kv->d.max_batch && H == kv->d.n_heads, "rope_kvwrite: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
+  JG_REQUIRE(B > 0 && (seq != 0 || B <= kv->d.max_batch) && B <= 65535 && H == kv->d.n_heads, "rope_kvwrite: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
   JG_REQUIRE(jg_aligned(qkv, 16) && jg_aligned(table, 16) && jg_aligned(pos, 4), "rope_kvwrite: null or misaligned pointer");
   const int G = kv->d.n_kv_heads, hd = kv->d.head_dim;
   const long long total = (long long)B * (H + 2 * G) * (hd / 8);
@@ -677,7 +698,7 @@ JG_API int jg_rope_kvwrite(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   return jg_launch(dev, "rope_kvwrite", rope_kvwrite_kernel, dim3(blocks), dim3(128), 0, (__half*)qkv, (const __half*)table,
                    (const int32_t*)pos, (const int32_t*)kv->block_table, kv->k_pool + kv->layer_elems * layer,
                    kv->v_pool + kv->layer_elems * layer, B, H, G, hd, kv->d.page_size, ilog2(kv->d.page_size),
-                   kv->d.max_pages_per_seq, table_rows);
+                   kv->d.max_pages_per_seq, table_rows, (const int32_t*)seq);
 }
 
 template <int HD, int NREP>
@@ -745,14 +766,28 @@ static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs,
   return jg_after_launch(dev, "attn_decode_fused");
 }
 
+static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
+                           int32_t table_rows, uint64_t pos, uint64_t seq, int pre, int32_t B, int32_t H);
+
 JG_API int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
                                 int32_t table_rows, uint64_t pos, int32_t B, int32_t H) {
+  JG_REQUIRE(jg_aligned(table, 16) && table_rows > 0, "attn_decode_fused: null, misaligned or empty RoPE table");
+  return attn_fused_impl(dev, kv, layer, out, qkv, table, table_rows, pos, 0, 0, B, H);
+}
+
+JG_API int jg_attn_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos, uint64_t seq,
+                        int32_t R, int32_t H) {
+  JG_REQUIRE(jg_aligned(seq, 4), "attn_rows: null or misaligned row->sequence map");
+  return attn_fused_impl(dev, kv, layer, out, qkv, 0, 1, pos, seq, 1, R, H);
+}
+
+static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
+                           int32_t table_rows, uint64_t pos, uint64_t seq, int pre, int32_t B, int32_t H) {
   JG_ENTER(dev);
   JG_REQUIRE(kv != nullptr && kv->dev == dev, "attn_decode_fused: cache belongs to another device");
   JG_REQUIRE(layer >= 0 && layer < kv->d.n_layers, "attn_decode_fused: layer %d out of range", layer);
-  JG_REQUIRE(B > 0 && B <= kv->d.max_batch && H == kv->d.n_heads, "attn_decode_fused: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
-  JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(table, 16) && jg_aligned(pos, 4), "attn_decode_fused: null or misaligned pointer");
-  JG_REQUIRE(table_rows > 0, "attn_decode_fused: empty RoPE table");  // positions beyond the table use its last row
+  JG_REQUIRE(B > 0 && (seq != 0 || B <= kv->d.max_batch) && B <= 65535 && H == kv->d.n_heads, "attn_decode_fused: B=%d H=%d do not match the cache (max_batch %d, n_heads %d)", B, H, kv->d.max_batch, kv->d.n_heads);
+  JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(pos, 4), "attn_decode_fused: null or misaligned pointer");
   const int G = kv->d.n_kv_heads, hd = kv->d.head_dim, n_rep = H / G;
   static int cluster = -1;
   if (cluster < 0) {
@@ -771,6 +806,7 @@ JG_API int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint
   a.qkv = (const __half*)qkv; a.table = (const __half*)table; a.table_rows = table_rows;
   a.k_layer = kv->k_pool + kv->layer_elems * layer; a.v_layer = kv->v_pool + kv->layer_elems * layer;
   a.block_table = kv->block_table; a.pos = (const int32_t*)pos; a.out = (__half*)out;
+  a.seq = (const int32_t*)seq; a.pre = pre;
   a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
   a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap;
   a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));

@@ -20,7 +20,10 @@ struct jg_dev {
   void* pinned_stage;  // small page-locked staging area for jg_copyin of tiny payloads
   size_t pinned_stage_bytes;
   bool pdl;  // launch kernels with programmatic stream serialization (JG_PDL=0 turns it off)
+  int* err_word;    // device word written by kernels whose bounded waits gave up (0 = fine); allocated on first use
+  bool tc_pending;  // such kernels were launched since the word was last checked
 };
+int jg_check_device_errors(jg_dev* dev);  // after a stream synchronise: JG_ETIMEDOUT if a bounded wait gave up
 
 struct jg_graph {
   cudaGraph_t graph;

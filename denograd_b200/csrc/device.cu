@@ -85,10 +85,24 @@ JG_API int jg_device_close(jg_dev* dev) {
   return JG_OK;
 }
 
+int jg_check_device_errors(jg_dev* dev) {
+  if (!dev->tc_pending || dev->err_word == nullptr || dev->capturing) return JG_OK;
+  dev->tc_pending = false;
+  int code = 0;
+  JG_CUDA(cudaMemcpy(&code, dev->err_word, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code != 0) {
+    cudaMemset(dev->err_word, 0, sizeof(int));
+    jg_set_error("a device-side wait gave up (code %d: 1 = TMA producer, 2 = MMA issuer, 3 = epilogue); results of the "
+                 "tensor-core projections since the last synchronisation are invalid", code);
+    return JG_ETIMEDOUT;
+  }
+  return JG_OK;
+}
+
 JG_API int jg_device_sync(jg_dev* dev) {
   JG_ENTER(dev);
   JG_CUDA(cudaStreamSynchronize(dev->stream));
-  return JG_OK;
+  return jg_check_device_errors(dev);
 }
 
 JG_API int jg_device_props(jg_dev* dev, jg_props* out) {
@@ -152,7 +166,7 @@ JG_API int jg_copyout(jg_dev* dev, void* host, uint64_t src, size_t nbytes) {
   JG_REQUIRE(!dev->capturing, "host copy while a graph is being captured");
   JG_CUDA(cudaMemcpyAsync(host, (const void*)(uintptr_t)src, nbytes, cudaMemcpyDeviceToHost, dev->stream));
   JG_CUDA(cudaStreamSynchronize(dev->stream));
-  return JG_OK;
+  return jg_check_device_errors(dev);
 }
 
 JG_API int jg_copyin_async(jg_dev* dev, uint64_t dst, const void* pinned_host, size_t nbytes) {

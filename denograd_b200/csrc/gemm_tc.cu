@@ -1,0 +1,273 @@
+// Dense projection for many activation rows (prompt processing): Y[m][n] = epilogue( sum_k X[m][k] * W[n][k] ) on the
+// 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory, operands brought into 128-byte
+// swizzled shared memory by TMA (cp.async.bulk.tensor), one CTA per 128 weight rows x TN activation rows.
+//
+// The roles of the MMA are swapped with respect to the usual GEMM picture so that both operands are K-major exactly as
+// they lie in memory (nn.Linear keeps W as [out][in], jsgrad/nn/index.ts:403-412): A = 128 weight rows x 64 k,
+// B = TN activation rows x 64 k, D[128 lanes = weight rows][TN columns = activation rows] in fp32.
+// Warp roles: warp 0 issues the TMA loads (one lane), warp 1 owns tensor memory and issues the MMAs (one lane),
+// warps 2-5 read the accumulator back (tcgen05.ld, each warp its 32-lane quarter) and apply the epilogue.
+// Every mbarrier wait is bounded: a wait that does not complete sets an error word and the CTA winds down (tensor
+// memory is released in every case); the host reports JG_ETIMEDOUT at the next synchronisation.
+// No cluster launch and no multicast: every CTA fetches its own tiles.
+#include <cuda.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "transcendental.cuh"
+
+enum { TC_STORE = 0, TC_RESIDUAL = 1, TC_SWIGLU = 2, TC_PARTIAL = 4 };
+
+constexpr int TC_BM = 128;  // weight rows per CTA (MMA M)
+constexpr int TC_BK = 64;   // k per stage: 64 halves = one 128-byte swizzle row
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;  // polls of one mbarrier phase before giving up (~ tens of ms)
+
+struct TcArgs {
+  __half* y;
+  float* y32;
+  const __half* residual;
+  int* err;  // device word: 0 = fine, otherwise the code of the first wait that gave up
+  int M, N, K;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase with the given parity; false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+               : "memory");
+}
+// K-major operand tile in 128-byte swizzled shared memory: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
+  const uint32_t lo = ((smem_u32(tile) & 0x3FFFFu) >> 4) | (1u << 16);  // start address, leading byte offset = 1 (unused)
+  const uint32_t hi = 64u | (1u << 14) | (2u << 29);                    // stride 1024 B, descriptor version 1, SWIZZLE_128B
+  return (uint64_t)lo | ((uint64_t)hi << 32);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+template <int TN, int EPI, int STAGES>
+__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
+                                                             const __grid_constant__ CUtensorMap tm_w1,
+                                                             const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
+  constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
+  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
+  constexpr uint32_t B_BYTES = TN * TC_BK * 2;
+  constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = (NW * TN) <= 32 ? 32 : ((NW * TN) <= 64 ? 64 : ((NW * TN) <= 128 ? 128 : ((NW * TN) <= 256 ? 256 : 512)));
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_fail;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int feat0 = blockIdx.x * TC_BM, tok0 = blockIdx.y * TN;
+  const int n_kb = a.K / TC_BK;
+  pdl_launch();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_bar, 1);
+    s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // tensor memory for the accumulator(s): one warp allocates, the same warp frees
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem;
+  pdl_wait();  // X (and the residual) come from the previous kernel
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer: TMA loads of stage kb % STAGES once the MMAs that read its previous contents are done
+    for (int kb = 0; kb < n_kb; kb++) {
+      const int s = kb % STAGES;
+      if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1)) { s_fail = 1; atomicCAS(a.err, 0, 1); break; }
+      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      tma_load_2d(st, &tm_w0, kb * TC_BK, feat0, &full_bar[s]);
+      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, kb * TC_BK, feat0, &full_bar[s]);
+      tma_load_2d(st + NW * A_BYTES, &tm_x, kb * TC_BK, tok0, &full_bar[s]);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer: 4 x (128 x TN x 16) per stage and matrix, accumulating in tensor memory
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);  // f32 acc, f16 x f16, K-major both
+    bool ok = true;
+    for (int kb = 0; kb < n_kb && ok; kb++) {
+      const int s = kb % STAGES;
+      if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) { s_fail = 1; atomicCAS(a.err, 0, 2); ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+      const uint64_t bdesc = umma_desc(st + NW * A_BYTES);
+#pragma unroll
+      for (int w = 0; w < NW; w++) {
+        const uint64_t adesc = umma_desc(st + w * A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++)  // 16 halves = 32 bytes further along K inside the swizzle row: +2 (16-byte units)
+          umma_f16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading the stage
+    }
+    if (ok) umma_commit(&acc_bar);  // ... and when the whole accumulation is complete
+  } else if (warp >= 2) {
+    // ---- epilogue: warp (id % 4) may touch tensor-memory lanes [32 * (id % 4), +32); lane l is weight row feat0 + 32q + l
+    const int q = warp & 3;
+    if (mbar_wait(&acc_bar, 0)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int feat = feat0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 16) {
+        uint32_t r0[16], r1[16];
+        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r0);
+        if (NW == 2) tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + TN + c0, r1);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const int tok = tok0 + c0 + j;
+          if (tok < a.M && feat < a.N) {
+            const size_t o = (size_t)tok * a.N + feat;
+            const float acc = __uint_as_float(r0[j]);
+            if (EPI == TC_PARTIAL) { a.y32[o] = acc; continue; }
+            __half v = __float2half_rn(acc);
+            if (EPI == TC_RESIDUAL) v = hadd1(a.residual[o], v);
+            if (EPI == TC_SWIGLU) v = jg_silu_mul(v, __float2half_rn(__uint_as_float(r1[j])));
+            a.y[o] = v;
+          }
+        }
+      }
+    } else {
+      if (lane == 0) atomicCAS(a.err, 0, 3);
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                    const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static encode_tiled_fn g_encode = nullptr;
+
+static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+    if (e != cudaSuccess || fn == nullptr) {
+      jg_set_error("cuTensorMapEncodeTiled is not available from this driver");
+      return JG_ENOTSUP;
+    }
+    g_encode = (encode_tiled_fn)fn;
+  }
+  const cuuint64_t dims[2] = {cols, rows};           // innermost first
+  const cuuint64_t strides[1] = {cols * 2};          // bytes between rows
+  const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    jg_set_error("tensor map for %s (%llu x %llu) rejected: CUresult %d", what, (unsigned long long)rows, (unsigned long long)cols, (int)r);
+    return JG_EINVAL;
+  }
+  return JG_OK;
+}
+
+template <int TN, int EPI>
+static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
+  constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
+  constexpr int STAGES = (NW == 2) ? 4 : 5;
+  constexpr size_t STAGE_BYTES = NW * TC_BM * TC_BK * 2 + TN * TC_BK * 2;
+  const size_t smem = STAGES * STAGE_BYTES + 1024;
+  auto kern = gemm_tc_kernel<TN, EPI, STAGES>;
+  static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+  const int slot = dev->ordinal & 7;
+  if (!attr_set[slot]) {
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set[slot] = true;
+  }
+  CUtensorMap tw0, tw1, tx;
+  int rc = make_map(&tw0, w0, a.N, a.K, TC_BM, "weights");
+  if (rc) return rc;
+  rc = make_map(&tw1, NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
+  if (rc) return rc;
+  rc = make_map(&tx, x, a.M, a.K, TN, "activations");
+  if (rc) return rc;
+  dev->tc_pending = true;
+  dim3 grid((a.N + TC_BM - 1) / TC_BM, (a.M + TN - 1) / TN);
+  return jg_launch(dev, "gemm_tc", kern, grid, dim3(TC_THREADS), smem, tw0, tw1, tx, a);
+}
+
+// Entry used by gemv.cu's public functions for M > 64 rows (fp16 weights, N % 128 == 0, K % 64 == 0).
+int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K) {
+  if (N % TC_BM != 0 || K % TC_BK != 0) {
+    jg_set_error("projection: M=%d rows need N %% 128 == 0 and K %% 64 == 0 (N=%d, K=%d); split the rows into chunks of 64", M, N, K);
+    return JG_ENOTSUP;
+  }
+  JG_REQUIRE(((uintptr_t)x % 16) == 0 && ((uintptr_t)w0 % 16) == 0, "projection: operands must be 16-byte aligned for TMA");
+  if (dev->err_word == nullptr) {
+    JG_REQUIRE(!dev->capturing, "first tensor-core projection on a device must not be inside a graph capture");
+    JG_CUDA(cudaMalloc(&dev->err_word, sizeof(int)));
+    JG_CUDA(cudaMemsetAsync(dev->err_word, 0, sizeof(int), dev->stream));
+  }
+  TcArgs a = {};
+  a.y = (__half*)y; a.y32 = (float*)y; a.residual = (const __half*)residual; a.err = dev->err_word; a.M = M; a.N = N; a.K = K;
+  switch (epi) {
+    case TC_STORE: return launch_tc<128, TC_STORE>(dev, x, w0, w1, a);
+    case TC_RESIDUAL: return launch_tc<128, TC_RESIDUAL>(dev, x, w0, w1, a);
+    case TC_SWIGLU: return launch_tc<128, TC_SWIGLU>(dev, x, w0, w1, a);
+    case TC_PARTIAL: return launch_tc<128, TC_PARTIAL>(dev, x, w0, w1, a);
+  }
+  jg_set_error("projection: epilogue %d has no tensor-core variant for M=%d rows", epi, M);
+  return JG_ENOTSUP;
+}

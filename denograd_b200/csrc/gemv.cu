@@ -342,13 +342,18 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
 int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
                   void* key, int M, int N, int K, int row_offset);
 
+// gemm_tc.cu: tcgen05 / TMA projection for more than 64 rows (fp16 weights, N % 128 == 0, K % 64 == 0)
+int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K);
+
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
+  if (!W8 && !NORM && a.M > 64 && EPI != EPI_LOGITS)
+    return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
   if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
   // from 3 rows on the CUDA cores cannot keep up with the weight stream: unnormalised fp16 projections go to the
   // tensor-core kernel (measured on the 8B shapes: 48 us against 69 us at 4 rows and 106 us at 8 rows)
-  if (!W8 && !NORM && a.M >= 3 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
+  if (!W8 && !NORM && a.M >= 3 && a.M <= 64 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
   if (a.M <= 8) return launch_gemv<8, W8, EPI, NORM>(dev, a, name);
   if (!W8 && !NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);

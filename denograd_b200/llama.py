@@ -219,15 +219,17 @@ class _Workspace:
     jsgrad/engine/memory.ts:8-58): reused by every layer and every step, so a captured step never allocates."""
 
     def __init__(self, dev: CUDA, B: int, dim: int, qkv_dim: int, q_dim: int, hidden: int, vocab: int):
+        """`vocab` = 0 leaves out the logits (a multi-position chunk only projects its last rows, elsewhere)."""
         self.B = B
         self.tokens = Tensor.zeros((B,), "int32", dev)
         self.pos = Tensor.zeros((B,), "int32", dev)
+        self.seq = Tensor.zeros((B,), "int32", dev)  # row -> sequence, for multi-position chunks
         self.h = Tensor.empty((B, dim), "float16", dev)
         self.xn = Tensor.empty((B, dim), "float16", dev)
         self.qkv = Tensor.empty((B, qkv_dim), "float16", dev)
         self.attn = Tensor.empty((B, q_dim), "float16", dev)
         self.ffn = Tensor.empty((B, hidden), "float16", dev)
-        self.logits = Tensor.empty((B, vocab), "float16", dev)
+        self.logits = Tensor.empty((B, vocab), "float16", dev) if vocab else None
         self.key = Tensor.zeros((B,), "uint64", dev)
         self.next_tokens = Tensor.zeros((B,), "int32", dev)
         self.part32 = Tensor.empty((B, dim), "float32", dev)  # fp32 partial sums of a row-parallel projection
@@ -327,13 +329,16 @@ class Transformer:
         self._loop_graph: dict[int, CUDAGraph] = {}
 
     # ------------------------------------------------------------------------------------------ internals
-    def _workspace(self, B: int) -> _Workspace:
-        if B > self.max_batch:
+    def _workspace(self, B: int, rows: bool = False) -> _Workspace:
+        """Workspace for B activation rows; `rows` marks a multi-position chunk (more rows than sequences allowed)."""
+        if B > self.max_batch and not rows:
             raise ValueError(f"batch {B} exceeds max_batch {self.max_batch}")
-        if B not in self._ws:
+        key = B if (not rows or B <= self.max_batch) else -B  # chunks beyond the batch limit carry no logits buffer
+        if key not in self._ws:
             qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
-            self._ws[B] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim, self.vocab_local)
-        return self._ws[B]
+            self._ws[key] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim,
+                                       self.vocab_local if key > 0 else 0)
+        return self._ws[key]
 
     def _step(self, ws: _Workspace, advance: bool = False) -> None:
         """One token per row: reads ws.tokens / ws.pos, writes ws.logits and ws.next_tokens.  With `advance` the step
@@ -368,9 +373,10 @@ class Transformer:
     def forward(self, tokens, start_pos: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 0.8,
                 alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:
         """Transformer.forward (jsgrad/models/llama.ts:201-213), eager.  tokens: int32 [B, S] (host array or Tensor).
-        Positions are processed one at a time, each attending to the cache up to itself — what the reference's
-        additive causal mask computes for S > 1, and how its own prefill feeds prompts
-        (jsgrad/models/llama3.ts:307-311).  Returns the greedy next token of every row ([B] int32)."""
+        S > 1 runs in chunks of up to 512 rows (batch x positions; 64 where a projection's shape keeps it off the
+        tcgen05 kernel, 8 for int8 weights): one pass over the weights per chunk, every row
+        attending to the cache up to its own position — what the reference's additive causal mask (:208) computes.
+        Returns the greedy next token of every batch row after the last position ([B] int32)."""
         if temperature >= 1e-6:
             raise NotImplementedError("only greedy decoding (temperature < 1e-6) is implemented on the CUDA device path")
         toks = tokens.numpy() if isinstance(tokens, Tensor) else np.asarray(tokens, dtype=np.int32)
@@ -378,11 +384,65 @@ class Transformer:
         if start_pos + S > self.max_context:
             raise ValueError(f"start_pos {start_pos} + {S} tokens exceeds max_context {self.max_context}")
         ws = self._workspace(B)
+        max_rows = self._max_chunk_rows()
+        if S > 1 and self.fused and B <= max_rows and os.environ.get("JG_PREFILL", "rows") != "token":
+            sc = max(1, max_rows // B)
+            for s0 in range(0, S, sc):
+                self._forward_rows(toks[:, s0:s0 + sc], start_pos + s0, last=(s0 + sc >= S))
+            return ws.next_tokens
         for s in range(S):
             ws.tokens.assign(toks[:, s])
             ws.pos.assign(np.full((B,), start_pos + s, np.int32))
             self._step(ws)
         return ws.next_tokens
+
+    def _max_chunk_rows(self) -> int:
+        """Rows one projection call takes: 8 for int8 weights (matrix-vector kernels), 64 for fp16 (mma.sync kernel),
+        512 when every projection of a block also fits the tcgen05 kernel (out features % 128, in features % 64)."""
+        if self.output.scale_ptr != 0:
+            return 8
+        a, f = self.layers[0].attention, self.layers[0].feed_forward
+        shapes = [(a._wqkv.out_features, self.dim), (self.dim, a.n_heads * self.head_dim),
+                  (f.w1.out_features, self.dim), (self.dim, f.w1.out_features)]
+        if all(n % 128 == 0 and k % 64 == 0 for n, k in shapes):
+            return int(os.environ.get("JG_PREFILL_ROWS", "512"))
+        return 64
+
+    def _forward_rows(self, toks: np.ndarray, start_pos: int, last: bool) -> None:
+        """One chunk of a multi-position call: rows r = s * B + b (position-major), R = B * Sc.  With `last` the
+        rows of the final position also go through the final norm, the output projection and greedy selection (the
+        reference computes logits for every position and keeps the last, jsgrad/models/llama.ts:210)."""
+        B, Sc = toks.shape
+        R, dev, tp = B * Sc, self.dev, self._tp
+        ws = self._workspace(R, rows=True)
+        ws.tokens.assign(np.ascontiguousarray(toks.T).reshape(R))
+        ws.pos.assign(np.repeat(np.arange(start_pos, start_pos + Sc, dtype=np.int32), B))
+        ws.seq.assign(np.tile(np.arange(B, dtype=np.int32), Sc))
+        self.tok_embeddings.call(ws.tokens, out=ws.h)
+        d = self.dim
+        for layer in self.layers:
+            a, f = layer.attention, layer.feed_forward
+            layer.attention_norm.call(ws.h, out=ws.xn)
+            dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, a._wqkv.weight.ptr, a._wqkv.scale_ptr, 0, R, a._wqkv.out_features, d)
+            dev.call("jg_rope_kvwrite_rows", a._kv.handle, a._layer, ws.qkv.ptr, self.freqs_cis.ptr, self.freqs_cis.shape[0],
+                     ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
+            dev.call("jg_attn_rows", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
+            layer._row_parallel(a.wo, ws.attn, ws, tp)
+            layer.ffn_norm.call(ws.h, out=ws.xn)
+            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, f.w1.weight.ptr, f.w1.scale_ptr,
+                     f.w3.weight.ptr, f.w3.scale_ptr, R, f.w1.out_features, d)
+            layer._row_parallel(f.w2, ws.ffn, ws, tp)
+        if last:
+            wsb = self._workspace(B)  # logits / keys / next tokens live in the batch-sized workspace, as after a step
+            h_last = ws.h.view_rows(R - B, R)
+            xn_last = ws.xn.view_rows(R - B, R)
+            self.norm.call(h_last, out=xn_last)
+            out = self.output
+            dev.call("jg_norm_logits_argmax_shard", wsb.logits.ptr, wsb.key.ptr, xn_last.ptr, 0, self.norm.eps,
+                     out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)
+            if tp is not None:
+                tp.all_reduce_max(wsb.key)
+            dev.call("jg_argmax_finalize", wsb.next_tokens.ptr, wsb.key.ptr, B)
 
     def call(self, tokens, start_pos: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 0.8,
              alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:

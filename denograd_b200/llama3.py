@@ -101,6 +101,13 @@ class Llama3:
             self.start_pos += 1
         return out
 
+    def prefill(self, toks: np.ndarray) -> Tensor:
+        """The whole prompt in one multi-position forward (Transformer.forward with S > 1, jsgrad/models/llama.ts:
+        201-213) instead of one call per token; returns the greedy token after the last prompt position."""
+        out = self.model.forward(np.asarray(toks, dtype=np.int32), self.start_pos, self.temperature)
+        self.start_pos += toks.shape[1]
+        return out
+
     def generate(self, prompt: np.ndarray, max_new_tokens: int) -> np.ndarray:
         """Greedy continuation through the public per-token API: every step copies the token ids to the device, runs
         the (graph-replayed) step and reads the chosen ids back — the `.item()` round trip of the reference's chat

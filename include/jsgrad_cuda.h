@@ -179,6 +179,16 @@ int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uin
 int jg_attn_decode_fused(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t table,
                          int32_t table_rows, uint64_t pos, int32_t B, int32_t H);
 
+/* Several new positions per sequence in one call (Transformer.forward with S > 1, jsgrad/models/llama.ts:201-213: the
+ * additive causal mask of :208 lets row (b, s) see positions [0, start_pos + s]).  Rows are independent: row r has
+ * position pos[r] and belongs to sequence seq[r] (its block-table row).  jg_rope_kvwrite_rows rotates Q/K of all rows
+ * and stores K/V; jg_attn_rows then attends row r over [0, pos[r]] of its sequence — which includes the rows of the
+ * same call that precede it, as the mask prescribes.  R is not limited by the cache's max_batch. */
+int jg_rope_kvwrite_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qkv, uint64_t table, int32_t table_rows,
+                         uint64_t pos, uint64_t seq, int32_t R, int32_t H);
+int jg_attn_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos, uint64_t seq,
+                 int32_t R, int32_t H);
+
 /* jg_attn_decode without any allocation by the library.  It has no counterpart in the reference; it exists for hosts
  * that must keep a kernel library from allocating device memory: an engine whose allocator owns the whole device and
  * places every buffer itself (jsgrad's memory planner / LRU allocator), or a loop that cannot take the device-wide

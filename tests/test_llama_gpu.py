@@ -67,6 +67,53 @@ def test_batch_16_goes_through_the_tensor_core_projections():
         assert (ids[b, :n] == ref_ids[b, :n]).all(), b
 
 
+@pytest.mark.parametrize("quant", ["float16", "int8"])
+def test_multi_position_forward_matches_token_at_a_time_and_checker(quant):
+    """Transformer.forward with S > 1 (chunks of rows, causal inside a chunk) against the checker's masked forward."""
+    B, S, n_new = 2, 37, 6
+    prompt = synth.prompt_tokens(S, TINY["vocab_size"], batch=B, seed=41)
+    m = build_oracle(TINY, max_context=64, max_batch=B, int8=(quant == "int8"), tied=True)
+    ref_logits, ref_next = m.forward(prompt, 0)  # one masked call over all S positions
+    llm = make("1B", args=TINY, quantize=quant, max_context=64, max_batch=B, tied_output=True)
+    tok = llm.prefill(prompt).numpy()
+    assert np.abs(llm.model.last_logits(B) - ref_logits).max() <= LOGIT_TOL
+    ref_ids, _, margins = oracle_greedy(build_oracle(TINY, max_context=64, max_batch=B, int8=(quant == "int8"), tied=True), prompt, n_new)
+    ids = np.empty((B, n_new), np.int32)
+    for i in range(n_new):  # decode on top of the cache the chunked prefill wrote
+        ids[:, i] = tok
+        if i + 1 < n_new:
+            tok = llm.model.call_host(tok.reshape(B, 1), llm.start_pos)
+            llm.start_pos += 1
+    assert (ids == ref_ids).all() or (margins.min() < 4e-3)
+    # a second, later multi-position call appends to the same cache (start_pos > 0)
+    more = synth.prompt_tokens(5, TINY["vocab_size"], batch=B, seed=42)
+    llm2 = make("1B", args=TINY, quantize=quant, max_context=64, max_batch=B, tied_output=True)
+    llm2.prefill(prompt)
+    llm2.prefill(more)
+    m2 = build_oracle(TINY, max_context=64, max_batch=B, int8=(quant == "int8"), tied=True)
+    m2.forward(prompt, 0)
+    ref2, _ = m2.forward(more, S)
+    assert np.abs(llm2.model.last_logits(B) - ref2).max() <= LOGIT_TOL
+
+
+@pytest.mark.parametrize("B,S,rows", [(1, 200, 512), (3, 70, 512), (1, 200, 96)])
+def test_long_multi_position_forward_on_the_tcgen05_projections(B, S, rows, monkeypatch):
+    """Chunks of more than 64 rows run their projections on the tcgen05 kernel; `rows` caps the chunk (96 gives a
+    first chunk on tcgen05, a second that continues the cache, and a short tail on the mma.sync kernel)."""
+    monkeypatch.setenv("JG_PREFILL_ROWS", str(rows))
+    prompt = synth.prompt_tokens(S, TINY["vocab_size"], batch=B, seed=61)
+    m = build_oracle(TINY, max_context=256, max_batch=B, int8=False, tied=True)
+    ref_logits, _ = m.forward(prompt, 0)
+    llm = make("1B", args=TINY, max_context=256, max_batch=B, tied_output=True)
+    llm.prefill(prompt)
+    assert np.abs(llm.model.last_logits(B) - ref_logits).max() <= LOGIT_TOL
+    # the cache it wrote serves a following single-token step
+    nxt = synth.prompt_tokens(1, TINY["vocab_size"], batch=B, seed=62)
+    ref1, _ = m.forward(nxt, S)
+    llm.model.call(nxt, S, 0.0)
+    assert np.abs(llm.model.last_logits(B) - ref1).max() <= LOGIT_TOL
+
+
 def test_weights_on_device_equal_the_checkers(dev):
     """The device-side seeded fill and the CPU generator produce the same model (spot-check every tensor kind)."""
     from tests.util import synth_weight, tensor_shapes
@@ -146,6 +193,22 @@ def test_c1_llama32_1b_token_exact_against_fixture():
     sample = logits[:, :, C1_SAMPLE]
     assert np.abs(sample - g["sample_logits"].astype(np.float32)).max() <= LOGIT_TOL
     assert np.abs(logits.max(axis=2) - g["max_logit"]).max() <= LOGIT_TOL
+    assert (ids == g["ids"]).all(), f"first mismatch at step {int(np.argmax(ids != g['ids']))}"
+
+
+def test_c1_with_one_pass_prefill_is_token_exact_too():
+    """Same workload with the 32-token prompt fed as one multi-position forward (tensor-core projections)."""
+    g = np.load(os.path.join(GOLD, "c1_llama32_1b.npz"))
+    llm = make("1B", max_context=128)
+    tok = llm.prefill(g["prompt"]).numpy()
+    ids = np.empty((1, 64), np.int32)
+    for i in range(64):
+        ids[:, i] = tok
+        if i == 0:
+            assert np.abs(llm.model.last_logits(1)[:, C1_SAMPLE] - g["sample_logits"][0].astype(np.float32)).max() <= LOGIT_TOL
+        if i + 1 < 64:
+            tok = llm.model.call_host(tok.reshape(1, 1), llm.start_pos)
+            llm.start_pos += 1
     assert (ids == g["ids"]).all(), f"first mismatch at step {int(np.argmax(ids != g['ids']))}"
 
 
