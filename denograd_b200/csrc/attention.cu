@@ -17,25 +17,11 @@
 #include <cooperative_groups.h>
 
 #include "common.cuh"
+#include "kvcache.cuh"
 #include "transcendental.cuh"
 
 namespace cg = cooperative_groups;
 
-struct jg_kvcache {
-  jg_dev* dev;
-  jg_kvcache_desc d;
-  __half* k_pool;  // [L][n_pages][G][page][hd]
-  __half* v_pool;
-  int32_t* block_table;  // [max_batch][max_pages_per_seq]
-  float* scores;         // [max_batch][H][max_ctx]
-  float* part_ml;        // [max_batch][H][n_split][2]  (max, sum of exp relative to that max)
-  float* part_o;         // [max_batch][H][n_split][hd]
-  unsigned int* tickets; // [max_batch][G]
-  int n_split;
-  int max_ctx;
-  size_t layer_elems;  // elements of one layer of K (or V)
-  uint64_t bytes;
-};
 
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_WARPS = ATT_THREADS / 32;
@@ -62,12 +48,6 @@ __device__ __forceinline__ int attn_chunk(int T, int n_split) {
   return c < 32 ? 32 : c;
 }
 
-__device__ __forceinline__ const __half* kv_row(const __half* layer, const int32_t* bt_row, int t, int g, int G,
-                                                int page, int page_shift, int hd) {
-  const int pg = bt_row[t >> page_shift];
-  const int slot = t & (page - 1);
-  return layer + (((size_t)pg * G + g) * page + slot) * hd;
-}
 
 // ------------------------------------------------------------------------------------------------ kernel A
 template <int HD, int NREP>
@@ -570,7 +550,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const At
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-static int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }
 
 JG_API int jg_kvcache_create(jg_dev* dev, const jg_kvcache_desc* desc, jg_kvcache** out) {
   JG_ENTER(dev);
@@ -792,10 +771,19 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   static int cluster = -1;
   if (cluster < 0) {
     const char* e = getenv("JG_ATTN_CLUSTER");
-    cluster = e ? atoi(e) : 8;
-    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) cluster = 8;
+    cluster = e ? atoi(e) : 0;
+    if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) cluster = 0;
   }
-  const int cs = cluster;
+  // CTAs per (row, kv head): as many as it takes to put about two CTAs on every SM, at most 8 — one row alone is
+  // latency-bound and wants its context spread widely, many rows fill the machine by themselves and every extra
+  // CTA only adds a cluster barrier to a short loop.
+  int cs = cluster;
+  if (cs == 0) {
+    cs = 8;
+    while (cs > 1 && (long long)B * G * cs > 2LL * dev->sm_count) cs >>= 1;
+    // ... but never more positions per CTA than its shared memory can hold scores for
+    while (cs < 8 && (size_t)n_rep * ((((kv->max_ctx + cs - 1) / cs) + 3) & ~3) * sizeof(float) + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) cs <<= 1;
+  }
   const int chunk_cap = (((kv->max_ctx + cs - 1) / cs) + 3) & ~3;
   const size_t smem = (size_t)n_rep * chunk_cap * sizeof(float);
   if (smem + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) {

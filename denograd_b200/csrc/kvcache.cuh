@@ -1,0 +1,32 @@
+// The paged KV cache object shared by the attention kernels (decode in attention.cu, multi-position chunks in
+// attention_chunk.cu).  The layout is private to the device: the reference keeps one contiguous
+// [2][B][max_ctx][G][hd] tensor per layer (jsgrad/models/llama.ts:78-90); here pages of `page_size` positions are
+// addressed through a block table.
+#pragma once
+#include "common.cuh"
+
+struct jg_kvcache {
+  jg_dev* dev;
+  jg_kvcache_desc d;
+  __half* k_pool;  // [L][n_pages][G][page][hd]
+  __half* v_pool;
+  int32_t* block_table;  // [max_batch][max_pages_per_seq]
+  float* scores;         // [max_batch][H][max_ctx]
+  float* part_ml;        // [max_batch][H][n_split][2]  (max, sum of exp relative to that max)
+  float* part_o;         // [max_batch][H][n_split][hd]
+  unsigned int* tickets; // [max_batch][G]
+  int n_split;
+  int max_ctx;
+  size_t layer_elems;  // elements of one layer of K (or V)
+  uint64_t bytes;
+};
+
+// Address of the K (or V) row of position t of kv head g for the sequence whose block-table row is bt_row.
+__device__ __forceinline__ const __half* kv_row(const __half* layer, const int32_t* bt_row, int t, int g, int G,
+                                                int page, int page_shift, int hd) {
+  const int pg = bt_row[t >> page_shift];
+  const int slot = t & (page - 1);
+  return layer + (((size_t)pg * G + g) * page + slot) * hd;
+}
+
+static inline int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }

@@ -79,6 +79,7 @@ SIGNATURES: dict[str, list] = {
     "jg_attn_decode_fused": [_vp, _vp, _i32, _u64, _u64, _u64, _i32, _u64, _i32, _i32],
     "jg_rope_kvwrite_rows": [_vp, _vp, _i32, _u64, _u64, _i32, _u64, _u64, _i32, _i32],
     "jg_attn_rows": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32],
+    "jg_attn_chunk": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_attn_decode_noalloc": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32, _i32, _i32, _i32, _i32],
     "jg_pos_advance": [_vp, _u64, _i32],
     "jg_fill_normal_f16": [_vp, _u64, _u64, _u64, _u64, _f32],

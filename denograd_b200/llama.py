@@ -426,7 +426,10 @@ class Transformer:
             dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, a._wqkv.weight.ptr, a._wqkv.scale_ptr, 0, R, a._wqkv.out_features, d)
             dev.call("jg_rope_kvwrite_rows", a._kv.handle, a._layer, ws.qkv.ptr, self.freqs_cis.ptr, self.freqs_cis.shape[0],
                      ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
-            dev.call("jg_attn_rows", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
+            if Sc >= 8 and os.environ.get("JG_ATTN_CHUNK", "1") != "0":  # tensor-core attention over the regular chunk
+                dev.call("jg_attn_chunk", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, B, Sc, a.n_heads)
+            else:
+                dev.call("jg_attn_rows", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
             layer._row_parallel(a.wo, ws.attn, ws, tp)
             layer.ffn_norm.call(ws.h, out=ws.xn)
             dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, f.w1.weight.ptr, f.w1.scale_ptr,

@@ -64,6 +64,7 @@ export const SYMBOLS = {
   jg_attn_decode_fused: fn([ptr, ptr, i32, u64, u64, u64, i32, u64, i32, i32]),
   jg_rope_kvwrite_rows: fn([ptr, ptr, i32, u64, u64, i32, u64, u64, i32, i32]),
   jg_attn_rows: fn([ptr, ptr, i32, u64, u64, u64, u64, i32, i32]),
+  jg_attn_chunk: fn([ptr, ptr, i32, u64, u64, u64, u64, i32, i32, i32]),
   jg_attn_decode_noalloc: fn([ptr, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32]),
   jg_pos_advance: fn([ptr, u64, i32]),
   jg_fill_normal_f16: fn([ptr, u64, u64, u64, u64, f32]),

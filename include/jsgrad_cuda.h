@@ -189,6 +189,13 @@ int jg_rope_kvwrite_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t qk
 int jg_attn_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos, uint64_t seq,
                  int32_t R, int32_t H);
 
+/* The same attention for a regular chunk, on the tensor cores: Sc consecutive positions of each of B sequences, rows
+ * laid out position-major (row = s * B + b) with pos[s * B + b] = pos[b] + s; seq[b] names the block-table row of
+ * sequence b (0 = row b).  K and V of the chunk must already be in the cache (jg_rope_kvwrite_rows) and Q rotated.
+ * Same result as jg_attn_rows up to the summation order of the fp32 accumulations. */
+int jg_attn_chunk(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos, uint64_t seq,
+                  int32_t B, int32_t Sc, int32_t H);
+
 /* jg_attn_decode without any allocation by the library.  It has no counterpart in the reference; it exists for hosts
  * that must keep a kernel library from allocating device memory: an engine whose allocator owns the whole device and
  * places every buffer itself (jsgrad's memory planner / LRU allocator), or a loop that cannot take the device-wide

@@ -282,6 +282,52 @@ def test_rope_cache_attention(dev, hd, H, G, B, T, n_split):
     kv2.close()
 
 
+@pytest.mark.parametrize("hd,H,G", [(64, 32, 8), (128, 24, 8), (128, 8, 8), (64, 4, 2), (128, 16, 2)])
+@pytest.mark.parametrize("B,start,Sc", [(1, 0, 16), (1, 0, 200), (2, 37, 75), (3, 130, 9), (1, 500, 140)])
+def test_chunk_attention_on_tensor_cores(dev, hd, H, G, B, start, Sc):
+    """jg_rope_kvwrite_rows + jg_attn_chunk for Sc new positions after `start` cached ones, against the checker's
+    masked attention and against the row-by-row kernel."""
+    rng = np.random.default_rng(hd * 7 + H + start + Sc)
+    max_ctx = 1024
+    kv = KVCache(dev, 1, H, G, hd, max_ctx, B, page_size=64)
+    table = rng.permutation(kv.n_pages).astype(np.int32).reshape(B, kv.max_pages_per_seq)
+    kv.set_block_table(table)
+    freqs = precompute_freqs_cis(hd, 2 * max_ctx, 500000.0, dev)
+    ftab = freqs.numpy()
+    stride = (H + 2 * G) * hd
+    T = start + Sc
+    qkv_all = (rng.standard_normal((T, B, stride)) * 0.7).astype(np.float16)  # [position][sequence]
+    k_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    v_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    q_ref = np.zeros((B, T, H, hd), np.float16)
+    for t in range(T):
+        q_ref[:, t] = O.rope(qkv_all[t][:, :H * hd].reshape(B, H, hd), ftab, [t] * B)
+        k_ref[:, t] = O.rope(qkv_all[t][:, H * hd:(H + G) * hd].reshape(B, G, hd), ftab, [t] * B)
+        v_ref[:, t] = qkv_all[t][:, (H + G) * hd:].reshape(B, G, hd)
+    seq_of = np.tile(np.arange(B, dtype=np.int32), T)
+
+    def rows(t0, n):
+        q = Tensor(np.ascontiguousarray(qkv_all[t0:t0 + n].reshape(n * B, stride)), device=dev)
+        p = Tensor(np.repeat(np.arange(t0, t0 + n, dtype=np.int32), B), device=dev)
+        s = Tensor(seq_of[:n * B].copy(), device=dev)
+        dev.call("jg_rope_kvwrite_rows", kv.handle, 0, q.ptr, freqs.ptr, freqs.shape[0], p.ptr, s.ptr, n * B, H)
+        return q, p, s
+
+    if start:
+        keep = rows(0, start)  # the cached prefix
+    q, p, s = rows(start, Sc)
+    out = Tensor.zeros((Sc * B, H * hd), "float16", dev)
+    dev.call("jg_attn_chunk", kv.handle, 0, out.ptr, q.ptr, p.ptr, s.ptr, B, Sc, H)
+    got = out.numpy().reshape(Sc, B, H * hd).transpose(1, 0, 2)
+    ref = O.attention(q_ref[:, start:], k_ref, v_ref, start)
+    assert_reduction_close(got, ref, max_ulp=2, max_frac=0.12, what=f"chunk attention hd{hd} H{H} G{G} B{B} {start}+{Sc}")
+    out2 = Tensor.zeros((Sc * B, H * hd), "float16", dev)
+    dev.call("jg_attn_rows", kv.handle, 0, out2.ptr, q.ptr, p.ptr, s.ptr, Sc * B, H)
+    assert_reduction_close(out.numpy(), out2.numpy(), max_ulp=2, max_frac=0.12, what="chunk vs row-by-row attention")
+    dev.synchronize()
+    kv.close()
+
+
 # ------------------------------------------------------------------------------------------------ error behaviour
 def test_invalid_arguments_are_rejected_before_launch(dev):
     x = Tensor.zeros((8, 64), "float16", dev)
