@@ -1,15 +1,22 @@
-// Dense projection for many activation rows (prompt processing): Y[m][n] = epilogue( sum_k X[m][k] * W[n][k] ) on the
-// 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor memory, operands brought into 128-byte
-// swizzled shared memory by TMA (cp.async.bulk.tensor), one CTA per 128 weight rows x TN activation rows.
+// Dense projection on the 5th-generation tensor cores for 9 rows and more (batched decode, prompt processing):
+// Y[m][n] = epilogue( sum_k X[m][k] * W[n][k] ) with tcgen05.mma, the accumulator in tensor memory and both operands
+// brought into 128-byte swizzled shared memory by TMA (cp.async.bulk.tensor).
 //
 // The roles of the MMA are swapped with respect to the usual GEMM picture so that both operands are K-major exactly as
 // they lie in memory (nn.Linear keeps W as [out][in], jsgrad/nn/index.ts:403-412): A = 128 weight rows x 64 k,
-// B = TN activation rows x 64 k, D[128 lanes = weight rows][TN columns = activation rows] in fp32.
+// B = TN activation rows x 64 k (TN = 16 ... 256), D[128 lanes = weight rows][TN columns = activation rows] in fp32.
+// With few activation rows the kernel is a weight stream: every weight byte crosses HBM once, the pipeline is as deep
+// as shared memory allows, and the first weight tiles are requested before the kernel waits for its predecessor.
 // Warp roles: warp 0 issues the TMA loads (one lane), warp 1 owns tensor memory and issues the MMAs (one lane),
 // warps 2-5 read the accumulator back (tcgen05.ld, each warp its 32-lane quarter) and apply the epilogue.
-// Every mbarrier wait is bounded: a wait that does not complete sets an error word and the CTA winds down (tensor
-// memory is released in every case); the host reports JG_ETIMEDOUT at the next synchronisation.
-// No cluster launch and no multicast: every CTA fetches its own tiles.
+//
+// Split-K over a thread-block cluster: when the output tiles alone do not fill the GPU, the CTAs of a cluster
+// (1,1,ks) share one output tile, each accumulating a slice of K; ranks > 0 then write their accumulators into rank 0's
+// (by then idle) pipeline buffers through distributed shared memory and rank 0 adds them in rank order before the
+// epilogue.  No cluster multicast is used anywhere: every CTA fetches its own tiles.
+// Every mbarrier wait is bounded: a wait that does not complete sets an error word and the CTA winds down (cluster
+// barriers are still reached, tensor memory is released in every case); the host reports JG_ETIMEDOUT at the next
+// synchronisation.
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
@@ -87,29 +94,65 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 
-template <int TN, int EPI, int STAGES>
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&r)[16]) {
+  uint32_t u[16];
+  tmem_ld16(taddr, u);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int j = 0; j < 16; j++) r[j] = __uint_as_float(u[j]);
+}
+// Cluster-wide barrier with release / acquire semantics (orders the distributed-shared-memory traffic around it).
+__device__ __forceinline__ void cluster_barrier() {
+  __syncwarp();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Shared-memory address `local` as seen in the CTA of rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t local, uint32_t rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+template <int TN, int EPI>
+struct TcCfg {
+  static constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
+  static constexpr int NCOL = NW * TN;                 // accumulator columns
+  static constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
+  static constexpr uint32_t B_BYTES = TN * TC_BK * 2;
+  static constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (225 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
+  static constexpr uint32_t TMEM_COLS = NCOL <= 32 ? 32 : (NCOL <= 64 ? 64 : (NCOL <= 128 ? 128 : (NCOL <= 256 ? 256 : 512)));
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+  // split-K peers park their accumulators ([column][128 lanes] fp32 each) in rank 0's pipeline buffers
+  static constexpr int MAX_KS = 1 + (int)(((size_t)STAGES * STAGE_BYTES) / ((size_t)NCOL * TC_BM * 4));
+};
+
+template <int TN, int EPI>
 __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
                                                              const __grid_constant__ CUtensorMap tm_w1,
                                                              const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
-  constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
-  constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
-  constexpr uint32_t B_BYTES = TN * TC_BK * 2;
-  constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
-  constexpr uint32_t TMEM_COLS = (NW * TN) <= 32 ? 32 : ((NW * TN) <= 64 ? 64 : ((NW * TN) <= 128 ? 128 : ((NW * TN) <= 256 ? 256 : 512)));
+  using Cfg = TcCfg<TN, EPI>;
+  constexpr int NW = Cfg::NW, STAGES = Cfg::STAGES, NCOL = Cfg::NCOL;
+  constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, TMEM_COLS = Cfg::TMEM_COLS;
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
   __shared__ uint32_t s_tmem;
-  __shared__ int s_fail;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int feat0 = blockIdx.x * TC_BM, tok0 = blockIdx.y * TN;
+  const int tok0 = blockIdx.x * TN, feat0 = blockIdx.y * TC_BM;
+  const int ks = gridDim.z, rank = blockIdx.z;  // the cluster is (1,1,ks): the rank in it is blockIdx.z
   const int n_kb = a.K / TC_BK;
+  const int kb0 = (int)((long long)rank * n_kb / ks), nk = (int)((long long)(rank + 1) * n_kb / ks) - kb0;
   pdl_launch();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     mbar_init(&acc_bar, 1);
-    s_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
@@ -121,26 +164,36 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = s_tmem;
-  pdl_wait();  // X (and the residual) come from the previous kernel
+  bool acc_ok = false;
 
   if (warp == 0 && lane == 0) {
-    // ---- producer: TMA loads of stage kb % STAGES once the MMAs that read its previous contents are done
-    for (int kb = 0; kb < n_kb; kb++) {
-      const int s = kb % STAGES;
-      if (kb >= STAGES && !mbar_wait(&empty_bar[s], ((kb / STAGES) - 1) & 1)) { s_fail = 1; atomicCAS(a.err, 0, 1); break; }
+    // ---- producer.  Weights do not depend on the preceding kernel: the first tiles are requested before the wait.
+    const int pre = nk < STAGES ? nk : STAGES;
+    for (int i = 0; i < pre; i++) {
+      unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      tma_load_2d(st, &tm_w0, (kb0 + i) * TC_BK, feat0, &full_bar[i]);
+      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &full_bar[i]);
+    }
+    pdl_wait();  // X comes from the previous kernel
+    for (int i = 0; i < pre; i++)
+      tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NW * A_BYTES, &tm_x, (kb0 + i) * TC_BK, tok0, &full_bar[i]);
+    for (int i = pre; i < nk; i++) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicCAS(a.err, 0, 1); break; }
       unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      tma_load_2d(st, &tm_w0, kb * TC_BK, feat0, &full_bar[s]);
-      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, kb * TC_BK, feat0, &full_bar[s]);
-      tma_load_2d(st + NW * A_BYTES, &tm_x, kb * TC_BK, tok0, &full_bar[s]);
+      tma_load_2d(st, &tm_w0, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
+      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
+      tma_load_2d(st + NW * A_BYTES, &tm_x, (kb0 + i) * TC_BK, tok0, &full_bar[s]);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer: 4 x (128 x TN x 16) per stage and matrix, accumulating in tensor memory
     const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);  // f32 acc, f16 x f16, K-major both
     bool ok = true;
-    for (int kb = 0; kb < n_kb && ok; kb++) {
-      const int s = kb % STAGES;
-      if (!mbar_wait(&full_bar[s], (kb / STAGES) & 1)) { s_fail = 1; atomicCAS(a.err, 0, 2); ok = false; break; }
+    for (int i = 0; i < nk; i++) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 2); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
       const uint64_t bdesc = umma_desc(st + NW * A_BYTES);
@@ -149,39 +202,71 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
         const uint64_t adesc = umma_desc(st + w * A_BYTES);
 #pragma unroll
         for (int k = 0; k < TC_BK / 16; k++)  // 16 halves = 32 bytes further along K inside the swizzle row: +2 (16-byte units)
-          umma_f16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_f16(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
       }
       umma_commit(&empty_bar[s]);  // arrives when the MMAs above have finished reading the stage
     }
     if (ok) umma_commit(&acc_bar);  // ... and when the whole accumulation is complete
   } else if (warp >= 2) {
-    // ---- epilogue: warp (id % 4) may touch tensor-memory lanes [32 * (id % 4), +32); lane l is weight row feat0 + 32q + l
-    const int q = warp & 3;
-    if (mbar_wait(&acc_bar, 0)) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int feat = feat0 + q * 32 + lane;
+    pdl_wait();  // the residual is read and Y written only after the previous kernel is done with them
+    acc_ok = mbar_wait(&acc_bar, 0);
+    if (!acc_ok && lane == 0) atomicCAS(a.err, 0, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+
+  // warp (id % 4) may touch tensor-memory lanes [32 * (id % 4), +32); lane l of it is weight row feat0 + 32q + l
+  const int q = warp & 3, row = q * 32 + lane;
+  const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+  float* red = reinterpret_cast<float*>(tiles);  // rank 0: [ks-1][NCOL][128] partial accumulators of the peers
+  if (ks > 1) {
+    cluster_barrier();  // rank 0's MMAs have consumed its pipeline buffers (its epilogue warps waited for them)
+    if (rank > 0 && warp >= 2 && acc_ok) {
+      const uint32_t dst0 = map_to_rank(smem_u32(red + ((size_t)(rank - 1) * NCOL) * TC_BM + row), 0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < TN; c0 += 16) {
-        uint32_t r0[16], r1[16];
-        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + c0, r0);
-        if (NW == 2) tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + TN + c0, r1);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      for (int c0 = 0; c0 < NCOL; c0 += 16) {
+        float r0[16];
+        tmem_ld16(t_lane + c0, r0);
+#pragma unroll
+        for (int j = 0; j < 16; j++) st_cluster_f32(dst0 + (uint32_t)((c0 + j) * TC_BM * 4), r0[j]);
+      }
+    }
+    cluster_barrier();  // the peers' partial sums have landed in rank 0
+  }
+  if (rank == 0 && warp >= 2 && acc_ok) {
+    const int feat = feat0 + row;
+#pragma unroll 1
+    for (int c0 = 0; c0 < TN; c0 += 16) {
+      float r0[16], r1[16];
+      tmem_ld16(t_lane + c0, r0);
+      if (NW == 2) tmem_ld16(t_lane + TN + c0, r1);
+      for (int p = 1; p < ks; p++) {  // rank order
+        const float* pr = red + ((size_t)(p - 1) * NCOL) * TC_BM + row;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          r0[j] = __fadd_rn(r0[j], pr[(size_t)(c0 + j) * TC_BM]);
+          if (NW == 2) r1[j] = __fadd_rn(r1[j], pr[(size_t)(TN + c0 + j) * TC_BM]);
+        }
+      }
+      if (feat < a.N) {
+        __half res[16];
+        if (EPI == TC_RESIDUAL) {  // all loads first: Y may alias the residual, which would serialise load / store pairs
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            res[j] = (tok0 + c0 + j < a.M) ? a.residual[(size_t)(tok0 + c0 + j) * a.N + feat] : __float2half_rn(0.f);
+        }
 #pragma unroll
         for (int j = 0; j < 16; j++) {
           const int tok = tok0 + c0 + j;
-          if (tok < a.M && feat < a.N) {
+          if (tok < a.M) {
             const size_t o = (size_t)tok * a.N + feat;
-            const float acc = __uint_as_float(r0[j]);
-            if (EPI == TC_PARTIAL) { a.y32[o] = acc; continue; }
-            __half v = __float2half_rn(acc);
-            if (EPI == TC_RESIDUAL) v = hadd1(a.residual[o], v);
-            if (EPI == TC_SWIGLU) v = jg_silu_mul(v, __float2half_rn(__uint_as_float(r1[j])));
+            if (EPI == TC_PARTIAL) { a.y32[o] = r0[j]; continue; }
+            __half v = __float2half_rn(r0[j]);
+            if (EPI == TC_RESIDUAL) v = hadd1(res[j], v);
+            if (EPI == TC_SWIGLU) v = jg_silu_mul(v, __float2half_rn(r1[j]));
             a.y[o] = v;
           }
         }
       }
-    } else {
-      if (lane == 0) atomicCAS(a.err, 0, 3);
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -225,32 +310,71 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
 
 template <int TN, int EPI>
 static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
-  constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
-  constexpr int STAGES = (NW == 2) ? 4 : 5;
-  constexpr size_t STAGE_BYTES = NW * TC_BM * TC_BK * 2 + TN * TC_BK * 2;
-  const size_t smem = STAGES * STAGE_BYTES + 1024;
-  auto kern = gemm_tc_kernel<TN, EPI, STAGES>;
+  using Cfg = TcCfg<TN, EPI>;
+  auto kern = gemm_tc_kernel<TN, EPI>;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   const int slot = dev->ordinal & 7;
   if (!attr_set[slot]) {
-    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     attr_set[slot] = true;
   }
   CUtensorMap tw0, tw1, tx;
   int rc = make_map(&tw0, w0, a.N, a.K, TC_BM, "weights");
   if (rc) return rc;
-  rc = make_map(&tw1, NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
+  rc = make_map(&tw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
   if (rc) return rc;
   rc = make_map(&tx, x, a.M, a.K, TN, "activations");
   if (rc) return rc;
+  // split K over a cluster until the launch has CTAs for about two thirds of the SMs, keeping at least 8 k-blocks
+  // per CTA and the peers' partial sums within rank 0's pipeline buffers
+  const int tiles = ((a.M + TN - 1) / TN) * (a.N / TC_BM), n_kb = a.K / TC_BK;
+  static int ks_env = -1;
+  if (ks_env < 0) { const char* e = getenv("JG_TC_SPLITK"); ks_env = e ? atoi(e) : 0; }
+  int ks = 1;
+  while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 && n_kb / (ks + 1) >= 8) ks++;
+  if (ks_env >= 1 && ks_env <= 8 && ks_env <= Cfg::MAX_KS && n_kb / ks_env >= 1) ks = ks_env;
   dev->tc_pending = true;
-  dim3 grid((a.N + TC_BM - 1) / TC_BM, (a.M + TN - 1) / TN);
-  return jg_launch(dev, "gemm_tc", kern, grid, dim3(TC_THREADS), smem, tw0, tw1, tx, a);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a.M + TN - 1) / TN, a.N / TC_BM, ks);  // activation tiles fastest: CTAs sharing weights run together
+  cfg.blockDim = dim3(TC_THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (ks > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = 1;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = ks;
+    na++;
+  }
+  if (dev->pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw0, tw1, tx, a);
+  if (e != cudaSuccess) return jg_cuda_fail(e, "gemm_tc", __FILE__, __LINE__);
+  return jg_after_launch(dev, "gemm_tc");
 }
 
-// Entry used by gemv.cu's public functions for M > 64 rows (fp16 weights, N % 128 == 0, K % 64 == 0).
+template <int EPI>
+static int launch_tc_rows(jg_dev* dev, const void* x, const void* w0, const void* w1, const TcArgs& a) {
+  if (a.M <= 16) return launch_tc<16, EPI>(dev, x, w0, w1, a);
+  if (a.M <= 32) return launch_tc<32, EPI>(dev, x, w0, w1, a);
+  if (a.M <= 64) return launch_tc<64, EPI>(dev, x, w0, w1, a);
+  if (a.M <= 128) return launch_tc<128, EPI>(dev, x, w0, w1, a);
+  return launch_tc<256, EPI>(dev, x, w0, w1, a);
+}
+
+// Whether jg_gemm_tc takes this shape: fp16 weights, whole 128-row weight tiles and 64-wide k-blocks.
+bool jg_gemm_tc_fits(int N, int K) { return N % TC_BM == 0 && K % TC_BK == 0; }
+
+// Entry used by gemv.cu's public functions (fp16 weights, N % 128 == 0, K % 64 == 0).
 int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K) {
-  if (N % TC_BM != 0 || K % TC_BK != 0) {
+  if (!jg_gemm_tc_fits(N, K)) {
     jg_set_error("projection: M=%d rows need N %% 128 == 0 and K %% 64 == 0 (N=%d, K=%d); split the rows into chunks of 64", M, N, K);
     return JG_ENOTSUP;
   }
@@ -263,10 +387,10 @@ int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* 
   TcArgs a = {};
   a.y = (__half*)y; a.y32 = (float*)y; a.residual = (const __half*)residual; a.err = dev->err_word; a.M = M; a.N = N; a.K = K;
   switch (epi) {
-    case TC_STORE: return launch_tc<128, TC_STORE>(dev, x, w0, w1, a);
-    case TC_RESIDUAL: return launch_tc<128, TC_RESIDUAL>(dev, x, w0, w1, a);
-    case TC_SWIGLU: return launch_tc<128, TC_SWIGLU>(dev, x, w0, w1, a);
-    case TC_PARTIAL: return launch_tc<128, TC_PARTIAL>(dev, x, w0, w1, a);
+    case TC_STORE: return launch_tc_rows<TC_STORE>(dev, x, w0, w1, a);
+    case TC_RESIDUAL: return launch_tc_rows<TC_RESIDUAL>(dev, x, w0, w1, a);
+    case TC_SWIGLU: return launch_tc_rows<TC_SWIGLU>(dev, x, w0, w1, a);
+    case TC_PARTIAL: return launch_tc_rows<TC_PARTIAL>(dev, x, w0, w1, a);
   }
   jg_set_error("projection: epilogue %d has no tensor-core variant for M=%d rows", epi, M);
   return JG_ENOTSUP;

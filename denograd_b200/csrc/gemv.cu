@@ -342,12 +342,26 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
 int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
                   void* key, int M, int N, int K, int row_offset);
 
-// gemm_tc.cu: tcgen05 / TMA projection for more than 64 rows (fp16 weights, N % 128 == 0, K % 64 == 0)
+// gemm_tc.cu: tcgen05 / TMA projection (fp16 weights, N % 128 == 0, K % 64 == 0), any number of rows
 int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K);
+bool jg_gemm_tc_fits(int N, int K);
+
+// Fewest rows that go to the tcgen05 kernel when the shape allows it (JG_TC_MIN_M overrides; above 64 rows it is
+// the only kernel).
+static int tc_min_rows() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("JG_TC_MIN_M");
+    v = e ? atoi(e) : 9;
+    if (v < 1) v = 1;
+    if (v > 65) v = 65;
+  }
+  return v;
+}
 
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
-  if (!W8 && !NORM && a.M > 64 && EPI != EPI_LOGITS)
+  if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
   if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
