@@ -12,6 +12,10 @@
 // cp.async.  Products are exact; the tensor-core accumulation order differs from the reference's sequential fp32
 // sum (jsgrad/tensor.ts:2593-2605), like every other reduction on this device.
 //
+// int8 weights (Int8Linear, jsgrad/models/llama3.ts:35): a lane's 16-byte load holds 16 weights, which it turns into
+// fp16 as half(q) * scale[row] (one rounding, as the reference's dequantised matrix) for four instructions; the k block
+// is then 64 wide and the matching activation chunk 32 bytes.
+//
 // Epilogues: STORE, RESIDUAL (fp16 add), SWIGLU (two matrices, silu(gate)*up, jsgrad/models/llama.ts:108-110),
 // LOGITS (store + per-row (value, lowest index) key, jsgrad/tensor.ts:2314-2320).
 #include <stdlib.h>
@@ -23,8 +27,10 @@ enum { GS_STORE = 0, GS_RESIDUAL = 1, GS_SWIGLU = 2, GS_LOGITS = 3, GS_PARTIAL =
 
 struct GemmSmallArgs {
   const __half* x;   // [M][K]
-  const __half* w0;  // [N][K]
-  const __half* w1;  // SWIGLU: up projection
+  const void* w0;    // [N][K] fp16, or int8 with per-row scales s0
+  const void* w1;    // SWIGLU: up projection
+  const __half* s0;  // [N] (int8 weights)
+  const __half* s1;
   __half* y;         // [M][N]
   const __half* residual;
   unsigned long long* key;  // [M] (LOGITS)
@@ -36,6 +42,24 @@ constexpr int GS_THREADS = 256;
 constexpr int GS_WARPS = 8;
 constexpr int GS_KT = 512;                 // activation k tile (halves)
 constexpr int GS_ROW_BYTES = GS_KT * 2 + 64;  // padded row: rows g and g+1 land 4 x 16 B apart modulo 128 B
+constexpr int GS_ROW_BYTES_W8 = GS_KT * 2 + 16;  // int8 weights read 32 B per lane: rows g and g+1 land 16 B apart
+
+// int8 x16 (one uint4) -> eight half2 words of half(q) * s in k order, each product rounded once.  Bytes become halves
+// exactly through the 0x6400 (1024.0) exponent trick.
+__device__ __forceinline__ void dequant16_h2(const uint4& raw, __half2 s2, uint32_t (&out)[8]) {
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);  // 1024 + 128
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const uint32_t v = words[i] ^ 0x80808080u;                  // signed -> offset-binary
+    uint32_t lo = __byte_perm(v, 0x64646464u, 0x4140);          // bytes 0,1 -> halves 0x64b0, 0x64b1
+    uint32_t hi = __byte_perm(v, 0x64646464u, 0x4342);          // bytes 2,3
+    const __half2 a = __hmul2_rn(__hsub2(*reinterpret_cast<__half2*>(&lo), bias), s2);
+    const __half2 b = __hmul2_rn(__hsub2(*reinterpret_cast<__half2*>(&hi), bias), s2);
+    out[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+    out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+}
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
   const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
@@ -52,16 +76,20 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int MT, int KS, int EPI>
+template <int MT, int KS, int EPI, bool W8>
 __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_kernel(const GemmSmallArgs a) {
+  constexpr int KBLK = W8 ? 64 : 32;         // k block: 4 lanes x one 16-byte weight load each
+  constexpr int CH = KBLK / 4;               // weights per lane and block
+  constexpr int ROWB = W8 ? GS_ROW_BYTES_W8 : GS_ROW_BYTES;
+  constexpr int WB = W8 ? 1 : 2;             // bytes per weight
   constexpr int NT = MT / 8;                 // 8-row activation tiles
   constexpr int NW = (EPI == GS_SWIGLU) ? 2 : 1;
   constexpr int TILES = GS_WARPS / KS;       // 16-row weight tiles per CTA
   constexpr int KW = GS_KT / KS;             // k elements of a tile handled by one warp
-  constexpr int NBMAX = (NW == 2) ? 4 : 8;   // 32-wide k blocks whose weight fragments a lane holds at once
-  constexpr int NB = (KW / 32) < NBMAX ? (KW / 32) : NBMAX;
-  constexpr int SPT = (KW / 32) / NB;        // steps per k tile
-  static_assert(NB >= 1 && SPT >= 1 && SPT * NB * 32 == KW, "k tiling");
+  constexpr int NBMAX = (NW == 2) ? 4 : 8;   // k blocks whose weight fragments a lane holds at once
+  constexpr int NB = (KW / KBLK) < NBMAX ? (KW / KBLK) : NBMAX;
+  constexpr int SPT = (KW / KBLK) / NB;      // steps per k tile
+  static_assert(NB >= 1 && SPT >= 1 && SPT * NB * KBLK == KW, "k tiling");
   extern __shared__ __align__(16) unsigned char smem[];  // 2 x [MT][GS_ROW_BYTES] activation tiles, then K-slice partials
   __shared__ unsigned long long s_best[GS_WARPS][8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -74,10 +102,15 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
   const int row0 = (blockIdx.x * TILES + tile) * 16;  // first weight row of this warp's tile
   const bool tile_ok = row0 < N;
   const int ra = min(row0 + g, N - 1), rb = min(row0 + g + 8, N - 1);  // clamp: duplicates are never stored
-  const __half* wa[NW];
-  const __half* wb[NW];
-  wa[0] = a.w0 + (size_t)ra * K; wb[0] = a.w0 + (size_t)rb * K;
-  if (NW == 2) { wa[NW - 1] = a.w1 + (size_t)ra * K; wb[NW - 1] = a.w1 + (size_t)rb * K; }
+  const unsigned char* wa[NW];
+  const unsigned char* wb[NW];
+  wa[0] = (const unsigned char*)a.w0 + (size_t)ra * K * WB; wb[0] = (const unsigned char*)a.w0 + (size_t)rb * K * WB;
+  if (NW == 2) { wa[NW - 1] = (const unsigned char*)a.w1 + (size_t)ra * K * WB; wb[NW - 1] = (const unsigned char*)a.w1 + (size_t)rb * K * WB; }
+  __half2 sa[NW], sb[NW];  // per-row scales of int8 weights
+  if (W8) {
+    sa[0] = __half2half2(a.s0[ra]); sb[0] = __half2half2(a.s0[rb]);
+    if (NW == 2) { sa[NW - 1] = __half2half2(a.s1[ra]); sb[NW - 1] = __half2half2(a.s1[rb]); }
+  }
 
   float acc[NW][NT][4];
 #pragma unroll
@@ -92,12 +125,12 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
   auto load_w = [&](int kt, int sp) {
 #pragma unroll
     for (int b = 0; b < NB; b++) {
-      const int k = kt * GS_KT + ks * KW + (sp * NB + b) * 32 + t * 8;
-      const bool ok = tile_ok && (k + 8 <= K);
+      const int k = kt * GS_KT + ks * KW + (sp * NB + b) * KBLK + t * CH;
+      const bool ok = tile_ok && (k + CH <= K);
 #pragma unroll
       for (int w = 0; w < NW; w++) {
-        fa[w][b] = ok ? ld_stream_128(wa[w] + k) : make_uint4(0, 0, 0, 0);
-        fb[w][b] = ok ? ld_stream_128(wb[w] + k) : make_uint4(0, 0, 0, 0);
+        fa[w][b] = ok ? ld_stream_128(wa[w] + (size_t)k * WB) : make_uint4(0, 0, 0, 0);
+        fb[w][b] = ok ? ld_stream_128(wb[w] + (size_t)k * WB) : make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -106,11 +139,11 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
 
   // activation tile loader: MT rows x GS_KT halves, 16 bytes per cp.async, zero fill past M or K
   auto load_x = [&](int kt, int bufi) {
-    unsigned char* dst = smem + (size_t)bufi * MT * GS_ROW_BYTES;
+    unsigned char* dst = smem + (size_t)bufi * MT * ROWB;
     for (int c = tid; c < MT * (GS_KT / 8); c += GS_THREADS) {
       const int m = c / (GS_KT / 8), kc = c % (GS_KT / 8);
       const int k = kt * GS_KT + kc * 8;
-      unsigned char* d = dst + (size_t)m * GS_ROW_BYTES + (size_t)kc * 16;
+      unsigned char* d = dst + (size_t)m * ROWB + (size_t)kc * 16;
       if (m < M && k + 8 <= K) cp_async_16(d, a.x + (size_t)m * K + k);
       else *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
     }
@@ -127,20 +160,37 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
       cp_async_wait<0>();
     }
     __syncthreads();
-    const unsigned char* xs = smem + (size_t)cur * MT * GS_ROW_BYTES;
+    const unsigned char* xs = smem + (size_t)cur * MT * ROWB;
     for (int sp = 0; sp < SPT; sp++) {
 #pragma unroll
       for (int b = 0; b < NB; b++) {
         // byte offset of this lane's 16 bytes inside an activation row
-        const int koff = (ks * KW + (sp * NB + b) * 32 + t * 8) * 2;
+        const int koff = (ks * KW + (sp * NB + b) * KBLK + t * CH) * 2;
+        if (!W8) {
 #pragma unroll
-        for (int j = 0; j < NT; j++) {
-          const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * GS_ROW_BYTES + koff);
+          for (int j = 0; j < NT; j++) {
+            const uint4 xv = *reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * ROWB + koff);
 #pragma unroll
-          for (int w = 0; w < NW; w++) {
-            // first instruction: halves 0-3 of the chunk (k 2t,2t+1 | 2t+8,2t+9 of the permuted block), second: 4-7
-            mma_16816(acc[w][j], fa[w][b].x, fb[w][b].x, fa[w][b].y, fb[w][b].y, xv.x, xv.y);
-            mma_16816(acc[w][j], fa[w][b].z, fb[w][b].z, fa[w][b].w, fb[w][b].w, xv.z, xv.w);
+            for (int w = 0; w < NW; w++) {
+              // first instruction: halves 0-3 of the chunk (k 2t,2t+1 | 2t+8,2t+9 of the permuted block), second: 4-7
+              mma_16816(acc[w][j], fa[w][b].x, fb[w][b].x, fa[w][b].y, fb[w][b].y, xv.x, xv.y);
+              mma_16816(acc[w][j], fa[w][b].z, fb[w][b].z, fa[w][b].w, fb[w][b].w, xv.z, xv.w);
+            }
+          }
+        } else {
+          uint32_t da[NW][8], db[NW][8];  // the lane's 16 weights of rows g and g+8 as fp16 pairs
+#pragma unroll
+          for (int w = 0; w < NW; w++) { dequant16_h2(fa[w][b], sa[w], da[w]); dequant16_h2(fb[w][b], sb[w], db[w]); }
+#pragma unroll
+          for (int j = 0; j < NT; j++) {
+            const uint4* xp = reinterpret_cast<const uint4*>(xs + (size_t)(j * 8 + g) * ROWB + koff);
+            const uint4 x0 = xp[0], x1 = xp[1];
+            const uint32_t xw[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int w = 0; w < NW; w++)
+#pragma unroll
+              for (int i = 0; i < 4; i++)  // instruction i: halves 4i .. 4i+3 of the chunk
+                mma_16816(acc[w][j], da[w][2 * i], db[w][2 * i], da[w][2 * i + 1], db[w][2 * i + 1], xw[2 * i], xw[2 * i + 1]);
           }
         }
       }
@@ -221,11 +271,11 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-template <int MT, int KS, int EPI>
+template <int MT, int KS, int EPI, bool W8>
 static int launch_gs(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
-  auto kern = gemm_small_kernel<MT, KS, EPI>;
+  auto kern = gemm_small_kernel<MT, KS, EPI, W8>;
   constexpr int NW = (EPI == GS_SWIGLU) ? 2 : 1;
-  const size_t x_bytes = (size_t)2 * MT * GS_ROW_BYTES;
+  const size_t x_bytes = (size_t)2 * MT * (W8 ? GS_ROW_BYTES_W8 : GS_ROW_BYTES);
   const size_t p_bytes = KS > 1 ? (size_t)GS_WARPS * NW * (MT / 8) * 4 * 32 * sizeof(float) : 0;
   const size_t smem = x_bytes > p_bytes ? x_bytes : p_bytes;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
@@ -239,42 +289,47 @@ static int launch_gs(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
   return jg_launch(dev, name, kern, dim3(blocks), dim3(GS_THREADS), smem, a);
 }
 
-template <int MT, int EPI>
+template <int MT, int EPI, bool W8>
 static int dispatch_ks(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
   // enough CTAs to fill the machine twice over: 16-row tiles x K slices >= 2 x 8 warps x SMs
   const long long tiles = (a.N + 15) / 16;
   const long long want = 2LL * GS_WARPS * dev->sm_count;
-  if (tiles >= want || a.K < 8 * 256) return launch_gs<MT, 1, EPI>(dev, a, name);
-  if (tiles * 2 >= want) return launch_gs<MT, 2, EPI>(dev, a, name);
-  if (tiles * 4 >= want) return launch_gs<MT, 4, EPI>(dev, a, name);
-  return launch_gs<MT, 8, EPI>(dev, a, name);
+  if (tiles >= want || a.K < 8 * 256) return launch_gs<MT, 1, EPI, W8>(dev, a, name);
+  if (tiles * 2 >= want) return launch_gs<MT, 2, EPI, W8>(dev, a, name);
+  if (tiles * 4 >= want) return launch_gs<MT, 4, EPI, W8>(dev, a, name);
+  return launch_gs<MT, 8, EPI, W8>(dev, a, name);
 }
 
-template <int EPI>
+template <int EPI, bool W8>
 static int dispatch_mt(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
-  if (a.M <= 16) return dispatch_ks<16, EPI>(dev, a, name);
-  if (a.M <= 32) return dispatch_ks<32, EPI>(dev, a, name);
-  if (a.M <= 64) return dispatch_ks<64, EPI>(dev, a, name);
+  if (a.M <= 16) return dispatch_ks<16, EPI, W8>(dev, a, name);
+  if (a.M <= 32) return dispatch_ks<32, EPI, W8>(dev, a, name);
+  if (a.M <= 64) return dispatch_ks<64, EPI, W8>(dev, a, name);
   jg_set_error("%s: M=%d rows is beyond the small-batch projection kernels (max 64 per call)", name, a.M);
   return JG_ENOTSUP;
 }
 
-// Entry used by gemv.cu's public functions for 8 < M <= 64 (fp16 weights).
-int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
-                  void* key, int M, int N, int K, int row_offset) {
-  JG_REQUIRE(K % 8 == 0, "projection: K=%d must be a multiple of 8", K);
-  GemmSmallArgs a = {};
-  a.x = (const __half*)x; a.w0 = (const __half*)w0; a.w1 = (const __half*)w1; a.y = (__half*)y;
-  a.residual = (const __half*)residual; a.key = (unsigned long long*)key; a.M = M; a.N = N; a.K = K;
-  a.row_offset = row_offset;
-  if (epi == GS_PARTIAL) { a.y = nullptr; a.y32 = (float*)y; }
+template <bool W8>
+static int dispatch_epi(jg_dev* dev, int epi, const GemmSmallArgs& a) {
   switch (epi) {
-    case GS_STORE: return dispatch_mt<GS_STORE>(dev, a, "linear");
-    case GS_RESIDUAL: return dispatch_mt<GS_RESIDUAL>(dev, a, "linear");
-    case GS_SWIGLU: return dispatch_mt<GS_SWIGLU>(dev, a, "norm_swiglu");
-    case GS_LOGITS: return dispatch_mt<GS_LOGITS>(dev, a, "norm_logits_argmax");
-    case GS_PARTIAL: return dispatch_mt<GS_PARTIAL>(dev, a, "linear_partial");
+    case GS_STORE: return dispatch_mt<GS_STORE, W8>(dev, a, "linear");
+    case GS_RESIDUAL: return dispatch_mt<GS_RESIDUAL, W8>(dev, a, "linear");
+    case GS_SWIGLU: return dispatch_mt<GS_SWIGLU, W8>(dev, a, "norm_swiglu");
+    case GS_LOGITS: return dispatch_mt<GS_LOGITS, W8>(dev, a, "norm_logits_argmax");
+    case GS_PARTIAL: return dispatch_mt<GS_PARTIAL, W8>(dev, a, "linear_partial");
   }
   jg_set_error("projection: unknown epilogue %d", epi);
   return JG_EINVAL;
+}
+
+// Entry used by gemv.cu's public functions for up to 64 rows; s0 / s1 non-null = int8 weights with per-row scales.
+int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, const void* s0, const void* s1,
+                  void* y, const void* residual, void* key, int M, int N, int K, int row_offset) {
+  JG_REQUIRE(K % (s0 ? 16 : 8) == 0, "projection: K=%d must be a multiple of %d", K, s0 ? 16 : 8);
+  GemmSmallArgs a = {};
+  a.x = (const __half*)x; a.w0 = w0; a.w1 = w1; a.s0 = (const __half*)s0; a.s1 = (const __half*)s1; a.y = (__half*)y;
+  a.residual = (const __half*)residual; a.key = (unsigned long long*)key; a.M = M; a.N = N; a.K = K;
+  a.row_offset = row_offset;
+  if (epi == GS_PARTIAL) { a.y = nullptr; a.y32 = (float*)y; }
+  return s0 ? dispatch_epi<true>(dev, epi, a) : dispatch_epi<false>(dev, epi, a);
 }

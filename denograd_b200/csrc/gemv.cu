@@ -338,9 +338,9 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
   return jg_launch(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, a);
 }
 
-// gemm_small.cu: tensor-core projection for 9..64 rows (fp16 weights, activations already normalised)
-int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual,
-                  void* key, int M, int N, int K, int row_offset);
+// gemm_small.cu: mma.sync projection for up to 64 rows (fp16 or int8 weights, activations already normalised)
+int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, const void* s0, const void* s1,
+                  void* y, const void* residual, void* key, int M, int N, int K, int row_offset);
 
 // gemm_tc.cu: tcgen05 / TMA projection (fp16 weights, N % 128 == 0, K % 64 == 0), any number of rows
 int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K);
@@ -367,12 +367,12 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
   // from 3 rows on the CUDA cores cannot keep up with the weight stream: unnormalised fp16 projections go to the
   // tensor-core kernel (measured on the 8B shapes: 48 us against 69 us at 4 rows and 106 us at 8 rows)
-  if (!W8 && !NORM && a.M >= 3 && a.M <= 64 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
+  if (!W8 && !NORM && a.M >= 3 && a.M <= 64 && a.K >= 256) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.s0, a.s1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
   if (a.M <= 8) return launch_gemv<8, W8, EPI, NORM>(dev, a, name);
-  if (!W8 && !NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
+  if (!NORM && a.M <= 64) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.s0, a.s1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (NORM) jg_set_error("%s: with M=%d rows (> 8) normalise first (jg_rmsnorm) and pass norm_w = 0", name, a.M);
-  else if (W8) jg_set_error("%s: M=%d rows (> 8) with int8 weights is not implemented", name, a.M);
+  else if (W8) jg_set_error("%s: M=%d rows (> 64) with int8 weights: split the rows into chunks of 64", name, a.M);
   else jg_set_error("%s: M=%d rows is beyond the projection kernels (max 64 per call)", name, a.M);
   return JG_ENOTSUP;
 }

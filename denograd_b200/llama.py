@@ -374,7 +374,7 @@ class Transformer:
                 alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:
         """Transformer.forward (jsgrad/models/llama.ts:201-213), eager.  tokens: int32 [B, S] (host array or Tensor).
         S > 1 runs in chunks of up to 512 rows (batch x positions; 64 where a projection's shape keeps it off the
-        tcgen05 kernel, 8 for int8 weights): one pass over the weights per chunk, every row
+        tcgen05 kernel or the weights are int8): one pass over the weights per chunk, every row
         attending to the cache up to its own position — what the reference's additive causal mask (:208) computes.
         Returns the greedy next token of every batch row after the last position ([B] int32)."""
         if temperature >= 1e-6:
@@ -397,10 +397,10 @@ class Transformer:
         return ws.next_tokens
 
     def _max_chunk_rows(self) -> int:
-        """Rows one projection call takes: 8 for int8 weights (matrix-vector kernels), 64 for fp16 (mma.sync kernel),
+        """Rows one projection call takes: 64 on the mma.sync kernel (int8 weights, or fp16 shapes off the tile grid),
         512 when every projection of a block also fits the tcgen05 kernel (out features % 128, in features % 64)."""
         if self.output.scale_ptr != 0:
-            return 8
+            return 64
         a, f = self.layers[0].attention, self.layers[0].feed_forward
         shapes = [(a._wqkv.out_features, self.dim), (self.dim, a.n_heads * self.head_dim),
                   (f.w1.out_features, self.dim), (self.dim, f.w1.out_features)]

@@ -195,29 +195,44 @@ def test_fused_norm_projections(dev, M, int8):
 
 
 @pytest.mark.parametrize("M", [9, 16, 17, 32, 40, 64])
-def test_tensor_core_projection(dev, M):
-    """8 < M <= 64 rows: mma.sync path, every epilogue, ragged N / K, all K-split variants (chosen from N)."""
-    rng = np.random.default_rng(500 + M)
+@pytest.mark.parametrize("int8", [False, True])
+def test_tensor_core_projection(dev, M, int8):
+    """8 < M <= 64 rows: mma.sync path (and tcgen05 where the shape allows it), fp16 and int8 weights, every epilogue,
+    ragged N / K, all K-split variants (chosen from N)."""
+    rng = np.random.default_rng(500 + M + int8)
+
+    def mk(n, k):
+        if int8:
+            wq = rng.integers(-127, 128, (n, k), dtype=np.int8)
+            sc = (rng.uniform(0.5, 1.5, n) * synth.INT8_SCALE_BASE).astype(np.float16)
+            wt, st = Tensor(wq, device=dev), Tensor(sc, device=dev)
+            return (wt, st), st.ptr, (lambda a: O.linear_w8(a, wq, sc))
+        w = (rng.standard_normal((n, k)) * 0.02).astype(np.float16)
+        wt = Tensor(w, device=dev)
+        return (wt, None), 0, (lambda a: O.linear_f16(a, w))
+
     for N, K in [(64, 256), (1027, 2048), (333, 1040), (2048, 8192), (40000, 512)]:
         x = rng.standard_normal((M, K)).astype(np.float16)
-        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
         res = rng.standard_normal((M, N)).astype(np.float16)
-        xt, wt, rt = Tensor(x, device=dev), Tensor(w, device=dev), Tensor(res, device=dev)
+        xt, rt = Tensor(x, device=dev), Tensor(res, device=dev)
+        (wt, keep), sp, lin = mk(N, K)
         y = Tensor.empty((M, N), "float16", dev)
-        ref = O.linear_f16(x, w)
-        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, 0, 0, M, N, K)
-        assert_reduction_close(y.numpy(), ref, max_ulp=1, max_frac=0.05, what=f"mma linear M{M} N{N} K{K}")
-        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, 0, rt.ptr, M, N, K)
+        ref = lin(x)
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, sp, 0, M, N, K)
+        assert_reduction_close(y.numpy(), ref, max_ulp=1, max_frac=0.05, what=f"mma linear M{M} N{N} K{K} int8={int8}")
+        dev.call("jg_linear", y.ptr, xt.ptr, wt.ptr, sp, rt.ptr, M, N, K)
         ref_r = (res.astype(np.float32) + ref.astype(np.float32)).astype(np.float16)
         assert_reduction_close(y.numpy(), ref_r, max_ulp=2, max_frac=0.06, what=f"mma linear+residual M{M} N{N} K{K}")
+        p32 = Tensor.zeros((M, N), "float32", dev)
+        dev.call("jg_linear_partial", p32.ptr, xt.ptr, wt.ptr, sp, M, N, K)
+        assert np.abs(p32.numpy().astype(np.float16).astype(np.float32) - ref.astype(np.float32)).max() <= 2e-2
         if N <= 2048:
-            w3 = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
-            w3t = Tensor(w3, device=dev)
-            dev.call("jg_norm_swiglu", y.ptr, xt.ptr, 0, 1e-5, wt.ptr, 0, w3t.ptr, 0, M, N, K)
-            assert_reduction_close(y.numpy(), O.swiglu(ref, O.linear_f16(x, w3)), max_ulp=3, max_frac=0.12, what=f"mma swiglu M{M} N{N} K{K}")
+            (w3t, keep3), sp3, lin3 = mk(N, K)
+            dev.call("jg_norm_swiglu", y.ptr, xt.ptr, 0, 1e-5, wt.ptr, sp, w3t.ptr, sp3, M, N, K)
+            assert_reduction_close(y.numpy(), O.swiglu(ref, lin3(x)), max_ulp=3, max_frac=0.12, what=f"mma swiglu M{M} N{N} K{K}")
         key = Tensor.zeros((M,), "uint64", dev)
         tok = Tensor.empty((M,), "int32", dev)
-        dev.call("jg_norm_logits_argmax", y.ptr, key.ptr, xt.ptr, 0, 1e-5, wt.ptr, 0, M, N, K)
+        dev.call("jg_norm_logits_argmax", y.ptr, key.ptr, xt.ptr, 0, 1e-5, wt.ptr, sp, M, N, K)
         dev.call("jg_argmax_finalize", tok.ptr, key.ptr, M)
         got = y.numpy()
         assert_reduction_close(got, ref, max_ulp=1, max_frac=0.05, what=f"mma logits M{M} N{N} K{K}")

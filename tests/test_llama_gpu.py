@@ -52,11 +52,12 @@ def test_tiny_model_matches_fixture_and_live_checker(quant):
     assert np.abs(logits2 - g["logits"].astype(np.float32)).max() <= LOGIT_TOL
 
 
-def test_batch_16_goes_through_the_tensor_core_projections():
+@pytest.mark.parametrize("quant", ["float16", "int8"])
+def test_batch_16_goes_through_the_tensor_core_projections(quant):
     """More than 8 rows per step: norms run as their own kernel and the projections on the tensor cores."""
     prompt = synth.prompt_tokens(5, TINY["vocab_size"], batch=16, seed=21)
-    llm = make("1B", args=TINY, max_context=64, max_batch=16, tied_output=True)
-    m = build_oracle(TINY, max_context=64, max_batch=16, int8=False, tied=True)
+    llm = make("1B", args=TINY, quantize=quant, max_context=64, max_batch=16, tied_output=True)
+    m = build_oracle(TINY, max_context=64, max_batch=16, int8=(quant == "int8"), tied=True)
     ref_ids, ref_logits, margins = oracle_greedy(m, prompt, 6)
     ids, logits = greedy_with_logits(llm, prompt, 6)
     assert np.abs(logits - ref_logits).max() <= LOGIT_TOL
