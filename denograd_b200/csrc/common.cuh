@@ -22,6 +22,7 @@ struct jg_dev {
   bool pdl;  // launch kernels with programmatic stream serialization (JG_PDL=0 turns it off)
   int* err_word;    // device word written by kernels whose bounded waits gave up (0 = fine); allocated on first use
   bool tc_pending;  // such kernels were launched since the word was last checked
+  bool peer_pending;  // peer-memory reductions (comm.cu) were launched since their error word was last checked
 };
 int jg_check_device_errors(jg_dev* dev);  // after a stream synchronise: JG_ETIMEDOUT if a bounded wait gave up
 

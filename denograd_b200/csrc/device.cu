@@ -85,8 +85,22 @@ JG_API int jg_device_close(jg_dev* dev) {
   return JG_OK;
 }
 
+int jg_peer_error(jg_dev* dev, int* code);  // comm.cu
+
 int jg_check_device_errors(jg_dev* dev) {
-  if (!dev->tc_pending || dev->err_word == nullptr || dev->capturing) return JG_OK;
+  if (dev->capturing) return JG_OK;
+  if (dev->peer_pending) {
+    dev->peer_pending = false;
+    int pc = 0;
+    int rc = jg_peer_error(dev, &pc);
+    if (rc) return rc;
+    if (pc != 0) {
+      jg_set_error("a peer-memory reduction gave up waiting for another rank's flag; results since the last "
+                   "synchronisation are invalid");
+      return JG_ETIMEDOUT;
+    }
+  }
+  if (!dev->tc_pending || dev->err_word == nullptr) return JG_OK;
   dev->tc_pending = false;
   int code = 0;
   JG_CUDA(cudaMemcpy(&code, dev->err_word, sizeof(int), cudaMemcpyDeviceToHost));

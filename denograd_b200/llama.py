@@ -197,8 +197,7 @@ class TransformerBlock:
             return
         dev = ws.h.dev
         dev.call("jg_linear_partial", ws.part32.ptr, x.ptr, lin.weight.ptr, lin.scale_ptr, ws.B, lin.out_features, lin.in_features)
-        tp.all_reduce_sum(ws.part32)
-        dev.call("jg_residual_add_f32", ws.h.ptr, ws.part32.ptr, ws.part32.numel())
+        tp.reduce_into_residual(ws.h, ws.part32)
 
     __call__ = call
 

@@ -4,8 +4,10 @@ weight is split on (jsgrad/models/llama3.ts:239-249); `shard_plan` follows it wi
 from the workload definition (all-reduce only after the attention-output and FFN-down projections): wq/wk/wv are split
 by heads on their output axis instead of their input axis, so attention needs no exchange at all.
 
-One rank is one process with one GPU.  The only exchanges per layer are two in-place fp32 all-reduces (after `wo` and
-`w2`), plus one max-reduction of the packed greedy keys per step when the output layer is sharded over the vocabulary.
+One rank is one process with one GPU.  The only exchanges per layer are two fp32 all-reduces (after `wo` and `w2`),
+plus one max-reduction of the packed greedy keys per step when the output layer is sharded over the vocabulary.
+Small messages (a decode step's) go through one kernel per rank over NVLink peer memory that also applies the
+residual add (`open_peers`); larger ones (prompt chunks) and ranks whose memory cannot be mapped use NCCL.
 """
 from __future__ import annotations
 
@@ -67,11 +69,42 @@ def shard_plan(p: dict, rank: int, world: int, tied: bool) -> dict[str, Shard]:
     return plan
 
 
+def exchange_via_torch(mine: bytes) -> list[bytes]:
+    """All-gather of one small byte string per rank through an initialised torch.distributed process group."""
+    import torch.distributed as dist
+    out: list = [None] * dist.get_world_size()
+    dist.all_gather_object(out, mine)
+    return out
+
+
+def exchange_via_directory(path: str, rank: int, world: int, tag: str = "ipc", timeout: float = 120.0):
+    """The same through files in a directory every rank can see (host-side wait with a deadline)."""
+    import time
+
+    def exchange(mine: bytes) -> list[bytes]:
+        tmp = os.path.join(path, f"{tag}_{rank}.tmp")
+        with open(tmp, "wb") as f:
+            f.write(mine)
+        os.replace(tmp, os.path.join(path, f"{tag}_{rank}.bin"))
+        out, deadline = [], time.time() + timeout
+        for r in range(world):
+            fn = os.path.join(path, f"{tag}_{r}.bin")
+            while not os.path.exists(fn):
+                if time.time() > deadline:
+                    raise TimeoutError(f"rank {r} never published its {tag} handle")
+                time.sleep(0.02)
+            out.append(open(fn, "rb").read())
+        return out
+
+    return exchange
+
+
 class TensorParallel:
     """Rank handle: NCCL communicator bound to this process's device stream."""
 
     def __init__(self, dev: CUDA, rank: int, world: int, unique_id: bytes):
         self.dev, self.rank, self.world = dev, rank, world
+        self.peer_capacity = 0  # fp32 elements the peer-memory exchange takes; 0 until open_peers succeeded
         self.handle = C.c_void_p()
         buf = C.create_string_buffer(unique_id, 128)
         ffi.call("jg_comm_init", dev.handle, nccl_library_path().encode(), buf, rank, world, C.byref(self.handle))
@@ -85,13 +118,47 @@ class TensorParallel:
         ffi.call("jg_comm_unique_id", nccl_library_path().encode(), buf)
         return buf.raw
 
+    # ---------------------------------------------------------------- peer-memory exchange (small messages)
+    def open_peers(self, exchange) -> bool:
+        """Map every rank's exchange buffer over NVLink peer memory.  `exchange(mine: bytes) -> list[bytes]` gathers
+        one 64-byte handle per rank in rank order (e.g. `exchange_via_torch`, `exchange_via_directory`).  Returns
+        False, leaving the NCCL path in charge, when a peer's memory cannot be mapped."""
+        buf = C.create_string_buffer(64)
+        ffi.call("jg_comm_peer_export", self.handle, buf)
+        handles = exchange(buf.raw)
+        assert len(handles) == self.world and all(len(h) == 64 for h in handles)
+        try:
+            ffi.call("jg_comm_peer_open", self.handle, C.create_string_buffer(b"".join(handles), 64 * self.world))
+        except ffi.JgError as e:
+            if e.status != 95:  # anything but "not supported" is a real error
+                raise
+            return False
+        cap = C.c_uint64(0)
+        ffi.call("jg_comm_peer_capacity", self.handle, C.byref(cap))
+        # one-shot exchange: every rank sends its whole message to every peer, which pays off only while latency
+        # dominates; beyond 128 KB NCCL's bandwidth-optimal algorithms win (measured at 512 KB on two GPUs)
+        self.peer_capacity = min(int(cap.value), 32 * 1024)
+        return self.peer_capacity > 0
+
+    def reduce_into_residual(self, h: Tensor, part32: Tensor) -> None:
+        """h <- h + half(sum over ranks of part32): the peer-memory kernel when the message fits, else NCCL + add."""
+        n = part32.numel()
+        if 0 < n <= self.peer_capacity:
+            ffi.call("jg_peer_allreduce_residual", self.handle, h.ptr, part32.ptr, n)
+        else:
+            self.all_reduce_sum(part32)
+            self.dev.call("jg_residual_add_f32", h.ptr, part32.ptr, n)
+
     def all_reduce_sum(self, t: Tensor) -> None:
         assert t.dtype == "float32"
         ffi.call("jg_allreduce_sum_f32", self.handle, t.ptr, t.numel())
 
     def all_reduce_max(self, t: Tensor) -> None:
         assert t.dtype == "uint64"
-        ffi.call("jg_allreduce_max_u64", self.handle, t.ptr, t.numel())
+        if 0 < t.numel() * 2 <= self.peer_capacity and t.ptr % 16 == 0:
+            ffi.call("jg_peer_allreduce_max_u64", self.handle, t.ptr, t.numel())
+        else:
+            ffi.call("jg_allreduce_max_u64", self.handle, t.ptr, t.numel())
 
     def close(self) -> None:
         """Destroy the communicator.  Captured steps keep references to its collectives and NCCL waits for them, so

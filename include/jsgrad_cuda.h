@@ -226,6 +226,19 @@ int jg_comm_init(jg_dev* dev, const char* nccl_path, const void* id128, int32_t 
 int jg_comm_destroy(jg_comm* comm);
 int jg_allreduce_sum_f32(jg_comm* comm, uint64_t buf, uint64_t count);  /* in place, on the device's stream */
 int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count);  /* greedy keys of a sharded vocabulary */
+/* The same two exchanges as one kernel per rank over NVLink peer memory, for the small messages of a decode step
+ * (multi.ts has no counterpart: its functions throw).  jg_comm_peer_export allocates this rank's exchange buffer and
+ * returns its 64-byte CUDA IPC handle; after every rank's handle has been gathered out of band (world x 64 bytes in
+ * rank order) jg_comm_peer_open maps the peers' buffers.  jg_peer_allreduce_residual then does
+ * h[i] <- h[i] + half(sum over ranks of part32[i]) in one launch: partial sums are stored into every peer's buffer,
+ * flags raised, the peers' flags awaited (bounded: JG_ETIMEDOUT at the next synchronisation if a peer never
+ * arrives; JG_PEER_TIMEOUT_MS, default 20000), slots added in rank order.  All ranks must issue the same sequence of
+ * peer reductions.  jg_comm_peer_capacity reports the largest n (0 while the peer path is not open). */
+int jg_comm_peer_export(jg_comm* comm, void* handle64);
+int jg_comm_peer_open(jg_comm* comm, const void* handles);
+int jg_comm_peer_capacity(jg_comm* comm, uint64_t* floats);
+int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32, uint64_t n);
+int jg_peer_allreduce_max_u64(jg_comm* comm, uint64_t keys, uint64_t n);
 /* y32[m][n] = sum_k x[m][k] W[n][k] left in fp32 (this rank's K-slice of a row-parallel Linear, nn/index.ts:411). */
 int jg_linear_partial(jg_dev* dev, uint64_t y32, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K);
 /* h <- h + half(p32): rounding + residual add of jsgrad/models/llama.ts:125-126 after the all-reduce. */

@@ -1,5 +1,6 @@
-"""Tensor parallelism on real GPUs: 2 ranks (processes), NCCL all-reduce after wo and w2, sharded vocabulary.
-Skipped when fewer than 2 GPUs are visible.  NVLS is switched off for the test processes (plain ring/tree NCCL)."""
+"""Tensor parallelism on real GPUs: 2 ranks (processes), all-reduce after wo and w2 (the peer-memory kernel, and NCCL
+alone), sharded vocabulary.  Skipped when fewer than 2 GPUs are visible.  NVLS is switched off for the test processes
+(plain ring/tree NCCL); the peer-memory kernel uses plain loads and stores."""
 import ctypes
 import os
 import subprocess
@@ -25,10 +26,11 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs 2 GPUs")
-def test_two_rank_tensor_parallel_matches_the_checker():
+@pytest.mark.parametrize("peer", ["1", "0"])
+def test_two_rank_tensor_parallel_matches_the_checker(peer):
     batch, n_new, world = 2, 8, 2
     with tempfile.TemporaryDirectory() as work:
-        env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", JG_TP_PEER=peer, JG_PEER_TIMEOUT_MS="5000")
         logs = [open(os.path.join(work, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(r), str(world), work,
                                    str(batch), str(n_new)], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
@@ -42,6 +44,8 @@ def test_two_rank_tensor_parallel_matches_the_checker():
             f.close()
         assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-4000:]
         res = [np.load(os.path.join(work, f"out_{r}.npz")) for r in range(world)]
+        if peer == "1":  # the peer-memory path must really have been the one that ran
+            assert all(open(os.path.join(work, f"peer_{r}.txt")).read() == "1" for r in range(world)), "peer memory not mapped"
     m = build_oracle(TINY, max_context=64, max_batch=batch, int8=False, tied=True)
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ref_ids, ref_logits, margins = oracle_greedy(m, prompt, n_new)

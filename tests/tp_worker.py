@@ -41,6 +41,11 @@ def main() -> None:
             time.sleep(0.05)
         uid = open(id_path, "rb").read()
     tp = TensorParallel(dev, rank, world, uid)
+    if os.environ.get("JG_TP_PEER", "1") != "0":
+        from denograd_b200.multi import exchange_via_directory
+        ok = tp.open_peers(exchange_via_directory(work, rank, world))
+        with open(os.path.join(work, f"peer_{rank}.txt"), "w") as f:
+            f.write("1" if ok else "0")
     llm = Llama3(size="1B", args=TINY, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ids = llm.generate(prompt, n_new)
