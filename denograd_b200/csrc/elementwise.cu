@@ -341,6 +341,27 @@ __global__ void fill_normal_f16_2d_kernel(__half* __restrict__ dst, unsigned lon
   }
 }
 
+// The int8 counterpart: element (r, c) of the window takes generator index (row0 + r) * full_cols + col0 + c.
+__global__ void fill_uniform_i8_2d_kernel(int8_t* __restrict__ dst, unsigned long long seed, unsigned long long rows,
+                                          unsigned long long cols, unsigned long long full_cols, unsigned long long row0,
+                                          unsigned long long col0) {
+  const unsigned long long n = rows * cols;
+  for (unsigned long long j = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; j < n;
+       j += (unsigned long long)gridDim.x * blockDim.x) {
+    const unsigned long long r = j / cols, cc = j % cols;
+    const unsigned long long i = (row0 + r) * full_cols + col0 + cc;
+    dst[j] = (int8_t)((int)(((synth_word(seed, i) >> 32) * 255ull) >> 32) - 127);
+  }
+}
+
+JG_API int jg_fill_uniform_i8_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
+                                 uint64_t row0, uint64_t col0) {
+  JG_ENTER(dev);
+  JG_REQUIRE(rows > 0 && cols > 0 && col0 + cols <= full_cols && dst != 0, "fill_uniform_i8_2d: bad arguments");
+  fill_uniform_i8_2d_kernel<<<fill_blocks(dev, rows * cols), 256, 0, dev->stream>>>((int8_t*)dst, seed, rows, cols, full_cols, row0, col0);
+  return jg_after_launch(dev, "fill_uniform_i8_2d");
+}
+
 JG_API int jg_fill_normal_f16_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
                                  uint64_t row0, uint64_t col0, float std) {
   JG_ENTER(dev);

@@ -87,6 +87,7 @@ SIGNATURES: dict[str, list] = {
     "jg_fill_scale_f16": [_vp, _u64, _u64, _u64, _u64, _f32],
     "jg_fill_const_f16": [_vp, _u64, _u64, _f32],
     "jg_fill_normal_f16_2d": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _f32],
+    "jg_fill_uniform_i8_2d": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64],
     "jg_comm_unique_id": [C.c_char_p, _vp],
     "jg_comm_init": [_vp, C.c_char_p, _vp, _i32, _i32, _P(_vp)],
     "jg_comm_destroy": [_vp],

@@ -291,11 +291,9 @@ class Transformer:
         if tp is not None:
             # this rank's share (denograd_b200.multi.shard_plan): heads, kv heads, FFN width and vocabulary rows
             from .multi import shard_plan
-            if embedding is not Embedding:
-                raise NotImplementedError("tensor parallelism is implemented for fp16 weights only")
             full = {"dim": dim, "n_heads": n_heads, "n_kv_heads": n_kv_heads, "hidden_dim": hidden_dim,
                     "vocab_size": vocab_size, "n_layers": n_layers}
-            self._shards = shard_plan(full, tp.rank, tp.world, tied_output)
+            self._shards = shard_plan(full, tp.rank, tp.world, tied_output, int8=embedding is not Embedding)
             n_heads, n_kv_heads, hidden_dim = n_heads // tp.world, n_kv_heads // tp.world, hidden_dim // tp.world
             self.vocab_offset = tp.rank * (vocab_size // tp.world)
         self.hidden_dim = hidden_dim
@@ -308,7 +306,9 @@ class Transformer:
         self.norm = RMSNorm(dim, norm_eps, device=dev)
         self.tok_embeddings = embedding(vocab_size, dim, device=dev)
         if tp is not None:
-            self.output = Linear(dim, self.vocab_local, False, device=dev)  # rows [vocab_offset, +vocab_local) of the full matrix
+            # rows [vocab_offset, +vocab_local) of the full matrix (of the embedding table when tied); the embedding
+            # table itself stays whole on every rank
+            self.output = (Linear if embedding is Embedding else linear)(dim, self.vocab_local, False, device=dev)
         elif tied_output:
             # output.weight is the embedding table itself (Llama-3.2 1B/3B; for quantised embeddings the reference
             # ties them as well, jsgrad/models/llama3.ts:55-58)

@@ -43,8 +43,10 @@ class Shard:
     col0: int
 
 
-def shard_plan(p: dict, rank: int, world: int, tied: bool) -> dict[str, Shard]:
-    """Per-rank windows of every weight of architecture `p` (MODEL_PARAMS[...]['args'] layout).
+def shard_plan(p: dict, rank: int, world: int, tied: bool, int8: bool = False) -> dict[str, Shard]:
+    """Per-rank windows of every weight of architecture `p` (MODEL_PARAMS[...]['args'] layout).  With `int8` every
+    weight also has a `.scale` entry: its per-output-row scales follow the rows of the weight's window (all rows,
+    replicated, for the row-parallel wo / w2, whose windows span every output row).
 
     column-parallel (rows of the weight): wq / wk / wv by heads, w1 / w3, output by vocabulary rows;
     row-parallel (columns of the weight, all-reduce after): wo, w2; replicated: norms and the embedding table.
@@ -66,6 +68,9 @@ def shard_plan(p: dict, rank: int, world: int, tied: bool) -> dict[str, Shard]:
         plan[f"{ff}.w3.weight"] = Shard(f"{ff}.w3.weight", fl, d, d, rank * fl, 0)
         plan[f"{ff}.w2.weight"] = Shard(f"{ff}.w2.weight", d, fl, f, 0, rank * fl)
     plan["output.weight"] = Shard("tok_embeddings.weight" if tied else "output.weight", Vl, d, d, rank * Vl, 0)
+    if int8:
+        for name, sh in list(plan.items()):
+            plan[name.replace(".weight", ".scale")] = Shard(sh.seed_name.replace(".weight", ".scale"), sh.rows, 1, 1, sh.row0, 0)
     return plan
 
 

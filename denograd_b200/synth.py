@@ -69,9 +69,16 @@ def fill_model(model, base_seed: int = BASE_SEED) -> dict[str, Tensor]:
             continue
         if name in shards:
             sh = shards[name]
-            assert tuple(t.shape) == (sh.rows, sh.cols), (name, t.shape, sh)
-            t.dev.call("jg_fill_normal_f16_2d", t.ptr, name_seed(sh.seed_name, base_seed), sh.rows, sh.cols, sh.cols_full,
-                       sh.row0, sh.col0, WEIGHT_STD)
+            seed = name_seed(sh.seed_name, base_seed)
+            if name.endswith(".scale"):
+                assert t.numel() == sh.rows, (name, t.shape, sh)
+                t.dev.call("jg_fill_scale_f16", t.ptr, seed, sh.row0, sh.rows, INT8_SCALE_BASE)
+            elif t.dtype == "int8":
+                assert tuple(t.shape) == (sh.rows, sh.cols), (name, t.shape, sh)
+                t.dev.call("jg_fill_uniform_i8_2d", t.ptr, seed, sh.rows, sh.cols, sh.cols_full, sh.row0, sh.col0)
+            else:
+                assert tuple(t.shape) == (sh.rows, sh.cols), (name, t.shape, sh)
+                t.dev.call("jg_fill_normal_f16_2d", t.ptr, seed, sh.rows, sh.cols, sh.cols_full, sh.row0, sh.col0, WEIGHT_STD)
             done.add(t.ptr)
             continue
         # views of a fused allocation are filled through their own names, so each projection keeps its own stream

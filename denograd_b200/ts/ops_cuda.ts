@@ -72,6 +72,7 @@ export const SYMBOLS = {
   jg_fill_scale_f16: fn([ptr, u64, u64, u64, u64, f32]),
   jg_fill_const_f16: fn([ptr, u64, u64, f32]),
   jg_fill_normal_f16_2d: fn([ptr, u64, u64, u64, u64, u64, u64, u64, f32]),
+  jg_fill_uniform_i8_2d: fn([ptr, u64, u64, u64, u64, u64, u64, u64]),
   jg_comm_unique_id: fn([buf, buf]),
   jg_comm_init: fn([ptr, buf, buf, i32, i32, buf]),
   jg_comm_destroy: fn([ptr]),

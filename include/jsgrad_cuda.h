@@ -256,6 +256,8 @@ int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value);
 /* [rows][cols] window at (row0, col0) of a [*][full_cols] tensor: a shard gets the values the whole tensor would. */
 int jg_fill_normal_f16_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
                           uint64_t row0, uint64_t col0, float std);
+int jg_fill_uniform_i8_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t rows, uint64_t cols, uint64_t full_cols,
+                          uint64_t row0, uint64_t col0);
 
 #ifdef __cplusplus
 }

@@ -26,14 +26,14 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("peer", ["1", "0"])
-def test_two_rank_tensor_parallel_matches_the_checker(peer):
+@pytest.mark.parametrize("peer,quant", [("1", "float16"), ("0", "float16"), ("1", "int8")])
+def test_two_rank_tensor_parallel_matches_the_checker(peer, quant):
     batch, n_new, world = 2, 8, 2
     with tempfile.TemporaryDirectory() as work:
         env = dict(os.environ, NCCL_NVLS_ENABLE="0", JG_TP_PEER=peer, JG_PEER_TIMEOUT_MS="5000")
         logs = [open(os.path.join(work, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(r), str(world), work,
-                                   str(batch), str(n_new)], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
+                                   str(batch), str(n_new), quant], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
                  for r in range(world)]
         for p in procs:
             p.wait(timeout=400)  # a stuck rank ends itself after 150 s (see tp_worker.py)
@@ -46,7 +46,7 @@ def test_two_rank_tensor_parallel_matches_the_checker(peer):
         res = [np.load(os.path.join(work, f"out_{r}.npz")) for r in range(world)]
         if peer == "1":  # the peer-memory path must really have been the one that ran
             assert all(open(os.path.join(work, f"peer_{r}.txt")).read() == "1" for r in range(world)), "peer memory not mapped"
-    m = build_oracle(TINY, max_context=64, max_batch=batch, int8=False, tied=True)
+    m = build_oracle(TINY, max_context=64, max_batch=batch, int8=(quant == "int8"), tied=True)
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ref_ids, ref_logits, margins = oracle_greedy(m, prompt, n_new)
     Vl = TINY["vocab_size"] // world

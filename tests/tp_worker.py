@@ -1,6 +1,6 @@
 """One tensor-parallel rank (a process with one GPU) for tests/test_tp_gpu.py.
 
-usage: python tests/tp_worker.py RANK WORLD WORKDIR [int batch] [int new_tokens]
+usage: python tests/tp_worker.py RANK WORLD WORKDIR [int batch] [int new_tokens] [float16|int8]
 Rank 0 creates the NCCL id and leaves it in WORKDIR/id.bin; every rank builds its shard of the TINY model, generates
 greedily, and writes WORKDIR/out_<rank>.npz (ids, local logits slice, vocabulary offset).
 """
@@ -26,6 +26,7 @@ def main() -> None:
     rank, world, work = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3]
     batch = int(sys.argv[4]) if len(sys.argv) > 4 else 2
     n_new = int(sys.argv[5]) if len(sys.argv) > 5 else 8
+    quant = sys.argv[6] if len(sys.argv) > 6 else "float16"
     dev = Device[f"CUDA:{rank}"]
     id_path = os.path.join(work, "id.bin")
     if rank == 0:
@@ -46,12 +47,12 @@ def main() -> None:
         ok = tp.open_peers(exchange_via_directory(work, rank, world))
         with open(os.path.join(work, f"peer_{rank}.txt"), "w") as f:
             f.write("1" if ok else "0")
-    llm = Llama3(size="1B", args=TINY, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ids = llm.generate(prompt, n_new)
     logits = llm.model.last_logits(batch)
     # the graph-replayed device loop must agree with the per-token API under sharding too
-    llm2 = Llama3(size="1B", args=TINY, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    llm2 = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     first = llm2._prefill(prompt).numpy()
     loop = llm2.model.decode_loop(first, llm2.start_pos, n_new - 1)
     np.savez(os.path.join(work, f"out_{rank}.npz"), ids=ids, logits=logits, offset=llm.model.vocab_offset,
