@@ -549,6 +549,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const At
   cluster.sync();  // peers may still be reading this CTA's shared memory
 }
 
+#include "attention_mma.cuh"
+
 // ------------------------------------------------------------------------------------------------ host side
 
 JG_API int jg_kvcache_create(jg_dev* dev, const jg_kvcache_desc* desc, jg_kvcache** out) {
@@ -716,9 +718,9 @@ JG_API int jg_attn_decode(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t o
   return JG_ENOTSUP;
 }
 
-template <int HD, int NREP>
+template <int HD, int NREP, bool MMA>
 static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs, size_t smem) {
-  auto kern = attn_decode_fused_kernel<HD, NREP>;
+  auto kern = MMA ? attn_decode_mma_kernel<HD, NREP> : attn_decode_fused_kernel<HD, NREP>;
   static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int slot = dev->ordinal & 7;
   if (smem > smem_set[slot]) {
@@ -728,7 +730,7 @@ static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs,
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cs, a.G, B);
-  cfg.blockDim = dim3(ATT_THREADS);
+  cfg.blockDim = dim3(MMA ? AM_THREADS : ATT_THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
   cudaLaunchAttribute attr[2];
@@ -774,6 +776,15 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
     cluster = e ? atoi(e) : 0;
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) cluster = 0;
   }
+  // The tensor-core variant of the kernel (attention_mma.cuh) serves launches with 16 or more (row, kv head) pairs;
+  // below that the CUDA-core kernel's shorter dependency chain wins (8B, one row: 3.28 against 3.31 ms per step).
+  // JG_ATTN_MMA=0 / 1 forces one of them.
+  static int mma_env = -2;
+  if (mma_env == -2) { const char* e = getenv("JG_ATTN_MMA"); mma_env = e ? (atoi(e) != 0) : -1; }
+  const int use_mma = mma_env >= 0 ? mma_env : ((long long)B * G >= 16);
+  const size_t tile_bytes = use_mma ? (size_t)2 * AM_TK * (hd + 8) * sizeof(__half) : 0;
+  // scores per CTA: rows of chunk_cap floats; the tensor-core variant pads the row so that heads fall on distinct banks
+  auto cap_of = [&](int c) { const int per = (kv->max_ctx + c - 1) / c; return use_mma ? (((per + 31) & ~31) + 8) : ((per + 3) & ~3); };
   // CTAs per (row, kv head): as many as it takes to put about two CTAs on every SM, at most 8 — one row alone is
   // latency-bound and wants its context spread widely, many rows fill the machine by themselves and every extra
   // CTA only adds a cluster barrier to a short loop.
@@ -782,10 +793,10 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
     cs = 8;
     while (cs > 1 && (long long)B * G * cs > 2LL * dev->sm_count) cs >>= 1;
     // ... but never more positions per CTA than its shared memory can hold scores for
-    while (cs < 8 && (size_t)n_rep * ((((kv->max_ctx + cs - 1) / cs) + 3) & ~3) * sizeof(float) + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) cs <<= 1;
+    while (cs < 8 && (size_t)n_rep * cap_of(cs) * sizeof(float) + tile_bytes + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) cs <<= 1;
   }
-  const int chunk_cap = (((kv->max_ctx + cs - 1) / cs) + 3) & ~3;
-  const size_t smem = (size_t)n_rep * chunk_cap * sizeof(float);
+  const int chunk_cap = cap_of(cs);
+  const size_t smem = (size_t)n_rep * chunk_cap * sizeof(float) + tile_bytes;
   if (smem + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) {
     jg_set_error("attn_decode_fused: %d positions per CTA need %zu B of shared memory; use jg_rope_kvwrite + jg_attn_decode", chunk_cap, smem);
     return JG_ENOTSUP;
@@ -798,7 +809,9 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
   a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap;
   a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));
-#define JG_ATT_CASE(HD_, NR_) if (hd == HD_ && n_rep == NR_) return launch_attn_fused<HD_, NR_>(dev, a, B, cs, smem);
+#define JG_ATT_CASE(HD_, NR_)                                                                   \
+  if (hd == HD_ && n_rep == NR_)                                                                \
+    return use_mma ? launch_attn_fused<HD_, NR_, true>(dev, a, B, cs, smem) : launch_attn_fused<HD_, NR_, false>(dev, a, B, cs, smem);
   JG_ATT_CASE(64, 1) JG_ATT_CASE(64, 2) JG_ATT_CASE(64, 3) JG_ATT_CASE(64, 4) JG_ATT_CASE(64, 8)
   JG_ATT_CASE(128, 1) JG_ATT_CASE(128, 2) JG_ATT_CASE(128, 3) JG_ATT_CASE(128, 4) JG_ATT_CASE(128, 8)
 #undef JG_ATT_CASE

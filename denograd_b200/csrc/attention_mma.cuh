@@ -1,0 +1,263 @@
+// Decode attention on the tensor cores: the same one-launch cluster scheme as attn_decode_fused_kernel (RoPE, cache
+// write, scores, softmax statistics over distributed shared memory, p.v, cross-CTA fold; see attention.cu) with the two
+// context loops restated as mma.sync.m16n8k16 products over K / V tiles staged in shared memory by cp.async:
+//   scores^T [16 positions x 8 heads] = K tile [16 x hd] . q^T [hd x 8]      (heads beyond n_rep are padding)
+//   out^T    [16 dims x 8 heads]     = V^T tile [16 x 16 positions] . p^T     (V^T fragments via ldmatrix.trans)
+// With many rows in flight (batched decode over long contexts) the CUDA-core loops of the original kernel are bound by
+// their shuffle reductions, not by the KV stream; here a warp issues 8 MMAs per 16 positions and the loads are
+// asynchronous 16-byte copies.  Arithmetic: fp32 accumulation of exact fp16 products (order differs), scores scaled in
+// fp32, p = half(exp2((s - M)/ln 2) * 1/L) from the global max and sum, exactly as in the other attention kernels.
+#pragma once
+
+constexpr int AM_THREADS = 128;
+constexpr int AM_WARPS = 4;
+constexpr int AM_TK = 64;  // positions per staged tile
+
+__device__ __forceinline__ void am_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void am_cp16(void* dst, const void* src, bool valid) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;  // 0 source bytes: zero fill
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ uint32_t am_pack(float lo, float hi) {
+  const __half2 h = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+// apply_rotary_emb on one (even, odd) pair: x = (a, b), t = (cos, sin) -> (a*cos - b*sin, a*sin + b*cos), each fp16 op
+// rounded once (jsgrad/models/llama.ts:17-32)
+__device__ __forceinline__ uint32_t am_rope2(uint32_t xraw, uint32_t traw) {
+  const __half2 x = *reinterpret_cast<const __half2*>(&xraw), t = *reinterpret_cast<const __half2*>(&traw);
+  const __half xa = __low2half(x), xb = __high2half(x), co = __low2half(t), si = __high2half(t);
+  const __half2 o = __halves2half2(hsub1(hmul1(xa, co), hmul1(xb, si)), hadd1(hmul1(xa, si), hmul1(xb, co)));
+  return *reinterpret_cast<const uint32_t*>(&o);
+}
+
+template <int HD, int NREP>
+__global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnFusedArgs a) {
+  constexpr int LD = HD + 8;      // padded tile row: fragment loads and ldmatrix rows fall on distinct banks
+  constexpr int KS = HD / 16;     // k-steps of a score product
+  constexpr int MT = HD / 16;     // 16-dim m-tiles of the output
+  constexpr int MPW = (MT + AM_WARPS - 1) / AM_WARPS;
+  constexpr int LPR = HD / 8;
+  extern __shared__ __align__(16) float sc[];  // [NREP][chunk_cap] scores, later probabilities; then the K/V tiles
+  __shared__ float red[AM_WARPS][8];
+  __shared__ float s_m[NREP], s_l[NREP], s_M[NREP], s_rL[NREP];
+  __shared__ float o_part[NREP * HD];
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = (int)cluster.block_rank(), CS = (int)cluster.num_blocks();
+  const int g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int qr = lane >> 2, qc = (lane & 3) * 2;
+  __half* tiles = reinterpret_cast<__half*>(sc + (size_t)NREP * a.chunk_cap);  // [2][AM_TK][LD]
+  pdl_launch();
+  pdl_wait();
+
+  const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);
+  const int p = T - 1;  // position of the new token
+  const int chunk = min((T + CS - 1) / CS, a.chunk_cap);
+  const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
+  const int n_local = max(t1 - t0, 0);
+  const int n_tiles = (n_local + AM_TK - 1) / AM_TK;
+  const int32_t* bt_row = a.block_table + (size_t)(a.seq ? a.seq[b] : b) * a.max_pages_per_seq;
+  const __half* xrow = a.qkv + (size_t)b * a.qkv_stride;
+  const __half* trow = a.table + (size_t)min(p, a.table_rows - 1) * HD;  // [hd/2][2] of position p
+
+  // ---- the owner of position p rotates K and stores the new K / V rows
+  if (!a.pre && t0 <= p && p < t1 && warp == 0 && lane < LPR) {
+    const uint4 traw = ld_128(trow + lane * 8);
+    const uint4 kraw = ld_128(xrow + (size_t)(a.H + g) * HD + lane * 8);
+    const uint4 vraw = ld_128(xrow + (size_t)(a.H + a.G + g) * HD + lane * 8);
+    const int pg = bt_row[p >> a.page_shift], slot = p & (a.page - 1);
+    const size_t off = (((size_t)pg * a.G + g) * a.page + slot) * HD + (size_t)lane * 8;
+    *reinterpret_cast<uint4*>(a.k_layer + off) = rope8(kraw, traw);
+    *reinterpret_cast<uint4*>(a.v_layer + off) = vraw;
+  }
+  // ---- B fragments of q^T: column n = lane/4 is query head g*NREP + n (clamped: columns >= NREP are never stored)
+  uint32_t qf[KS][2];
+  {
+    const __half* qh = xrow + (size_t)(g * NREP + min(qr, NREP - 1)) * HD;
+#pragma unroll
+    for (int k = 0; k < KS; k++) {
+      const int c0 = k * 16 + qc, c1 = c0 + 8;
+      uint32_t x0 = *reinterpret_cast<const uint32_t*>(qh + c0), x1 = *reinterpret_cast<const uint32_t*>(qh + c1);
+      if (!a.pre) {
+        x0 = am_rope2(x0, *reinterpret_cast<const uint32_t*>(trow + c0));
+        x1 = am_rope2(x1, *reinterpret_cast<const uint32_t*>(trow + c1));
+      }
+      qf[k][0] = x0; qf[k][1] = x1;
+    }
+  }
+  __syncthreads();  // the new K / V rows are visible to this CTA's loads below
+
+  auto load_tile = [&](const __half* layer, int j, __half* dst) {
+    for (int idx = tid; idx < AM_TK * (HD / 8); idx += AM_THREADS) {
+      const int row = idx / (HD / 8), c = idx % (HD / 8);
+      const int t = t0 + j * AM_TK + row;
+      const bool ok = t < t1;
+      const __half* src = ok ? kv_row(layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + c * 8 : layer;
+      am_cp16(dst + row * LD + c * 8, src, ok);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  // ---- scores of this rank's positions -> shared memory; warp w takes positions [16w, 16w+16) of every tile
+  float lmax0 = -INFINITY, lmax1 = -INFINITY;  // heads qc and qc+1
+  if (n_tiles > 0) load_tile(a.k_layer, 0, tiles);
+#pragma unroll 1
+  for (int j = 0; j < n_tiles; j++) {
+    if (j + 1 < n_tiles) {
+      load_tile(a.k_layer, j + 1, tiles + ((j + 1) & 1) * AM_TK * LD);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __half* Ks = tiles + (j & 1) * AM_TK * LD + (warp * 16) * LD;
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < KS; k++) {
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(Ks + qr * LD + k * 16 + qc);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(Ks + (qr + 8) * LD + k * 16 + qc);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(Ks + qr * LD + k * 16 + 8 + qc);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(Ks + (qr + 8) * LD + k * 16 + 8 + qc);
+      am_mma(c, a0, a1, a2, a3, qf[k][0], qf[k][1]);
+    }
+    const int ia = j * AM_TK + warp * 16 + qr, ib = ia + 8;  // local positions of this lane's two rows
+    if (qc < NREP) {
+      if (ia < n_local) { const float s = __fmul_rn(c[0], a.scale); sc[(size_t)qc * a.chunk_cap + ia] = s; lmax0 = fmaxf(lmax0, s); }
+      if (ib < n_local) { const float s = __fmul_rn(c[2], a.scale); sc[(size_t)qc * a.chunk_cap + ib] = s; lmax0 = fmaxf(lmax0, s); }
+    }
+    if (qc + 1 < NREP) {
+      if (ia < n_local) { const float s = __fmul_rn(c[1], a.scale); sc[(size_t)(qc + 1) * a.chunk_cap + ia] = s; lmax1 = fmaxf(lmax1, s); }
+      if (ib < n_local) { const float s = __fmul_rn(c[3], a.scale); sc[(size_t)(qc + 1) * a.chunk_cap + ib] = s; lmax1 = fmaxf(lmax1, s); }
+    }
+    __syncthreads();  // the buffer read here is refilled two iterations on
+  }
+  // V tile 0 travels while the statistics are worked out
+  if (n_tiles > 0) load_tile(a.v_layer, 0, tiles);
+#pragma unroll
+  for (int o = 4; o < 32; o <<= 1) {
+    lmax0 = fmaxf(lmax0, __shfl_xor_sync(0xffffffffu, lmax0, o));
+    lmax1 = fmaxf(lmax1, __shfl_xor_sync(0xffffffffu, lmax1, o));
+  }
+  if (lane < 4) { red[warp][qc] = lmax0; red[warp][qc + 1] = lmax1; }
+  __syncthreads();
+  if (tid < NREP) {
+    float m = red[0][tid];
+    for (int w = 1; w < AM_WARPS; w++) m = fmaxf(m, red[w][tid]);
+    s_m[tid] = m;
+  }
+  __syncthreads();
+  // ---- sum of exponentials relative to this rank's own max (combined across ranks below)
+  const float log2e = 1.4426950408889634f;
+  float lsum[NREP];
+#pragma unroll
+  for (int r = 0; r < NREP; r++) lsum[r] = 0.f;
+  for (int t = tid; t < n_local; t += AM_THREADS) {
+#pragma unroll
+    for (int r = 0; r < NREP; r++)
+      lsum[r] = __fadd_rn(lsum[r], jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_m[r]), log2e)));
+  }
+  __syncthreads();  // `red` is reused
+#pragma unroll
+  for (int r = 0; r < NREP; r++) {
+    const float v = warp_sum(lsum[r]);
+    if (lane == 0) red[warp][r] = v;
+  }
+  __syncthreads();
+  if (tid < NREP) {
+    float v = 0.f;
+    for (int w = 0; w < AM_WARPS; w++) v += red[w][tid];
+    s_l[tid] = v;
+  }
+  cluster.sync();
+  // ---- global max M and normaliser L = sum_j l_j * exp2((m_j - M)/ln2) over the ranks, in rank order
+  if (tid < NREP) {
+    float M = -INFINITY;
+    for (int rk = 0; rk < CS; rk++) M = fmaxf(M, *cluster.map_shared_rank(&s_m[tid], rk));
+    float L = 0.f;
+    for (int rk = 0; rk < CS; rk++) {
+      const float mj = *cluster.map_shared_rank(&s_m[tid], rk), lj = *cluster.map_shared_rank(&s_l[tid], rk);
+      L = __fadd_rn(L, __fmul_rn(lj, jg_xexp2_f32(__fmul_rn(__fsub_rn(mj, M), log2e))));
+    }
+    s_M[tid] = M;
+    s_rL[tid] = __fdiv_rn(1.0f, L);
+  }
+  __syncthreads();
+  // ---- probabilities in place: p = half(exp2((s-M)/ln2) * 1/L), kept as the fp32 value of that fp16
+  for (int t = tid; t < n_local; t += AM_THREADS) {
+#pragma unroll
+    for (int r = 0; r < NREP; r++) {
+      const float e = jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_M[r]), log2e));
+      sc[(size_t)r * a.chunk_cap + t] = __half2float(__float2half_rn(__fmul_rn(e, s_rL[r])));
+    }
+  }
+  __syncthreads();
+
+  // ---- out^T = V^T . p^T: warp w owns output dims [16 * MPW * w, +16 * MPW)
+  float acc[MPW][4];
+#pragma unroll
+  for (int m = 0; m < MPW; m++) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+  const float* prow = sc + (size_t)min(qr, NREP - 1) * a.chunk_cap;  // B column n = lane/4 is head n (clamped)
+#pragma unroll 1
+  for (int j = 0; j < n_tiles; j++) {
+    if (j + 1 < n_tiles) {
+      load_tile(a.v_layer, j + 1, tiles + ((j + 1) & 1) * AM_TK * LD);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __half* Vs = tiles + (j & 1) * AM_TK * LD;
+    if (warp * MPW < MT) {
+#pragma unroll
+      for (int kk = 0; kk < AM_TK / 16; kk++) {
+        const int i0 = j * AM_TK + kk * 16 + qc, i1 = i0 + 8;  // local positions of this lane's B elements
+        const float2 pa = (i0 + 1 < n_local) ? *reinterpret_cast<const float2*>(prow + i0)
+                                             : make_float2(i0 < n_local ? prow[i0] : 0.f, 0.f);
+        const float2 pb = (i1 + 1 < n_local) ? *reinterpret_cast<const float2*>(prow + i1)
+                                             : make_float2(i1 < n_local ? prow[i1] : 0.f, 0.f);
+        const uint32_t b0 = am_pack(pa.x, pa.y), b1 = am_pack(pb.x, pb.y);
+#pragma unroll
+        for (int m = 0; m < MPW; m++) {
+          const int mt = warp * MPW + m;
+          // V^T fragment: four 8x8 blocks of the tile read transposed; lane l names row (position) kk*16 + 8*(l/16) +
+          // l%8 at dims mt*16 + 8*((l/8)%2)
+          const __half* vp = Vs + (kk * 16 + ((lane >> 4) << 3) + (lane & 7)) * LD + mt * 16 + (((lane >> 3) & 1) << 3);
+          uint32_t a0, a1, a2, a3;
+          const uint32_t addr = (uint32_t)__cvta_generic_to_shared(vp);
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                       : "r"(addr));
+          am_mma(acc[m], a0, a1, a2, a3, b0, b1);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (warp * MPW < MT) {
+#pragma unroll
+    for (int m = 0; m < MPW; m++) {
+      const int d = (warp * MPW + m) * 16 + qr;
+      if (qc < NREP) { o_part[qc * HD + d] = acc[m][0]; o_part[qc * HD + d + 8] = acc[m][2]; }
+      if (qc + 1 < NREP) { o_part[(qc + 1) * HD + d] = acc[m][1]; o_part[(qc + 1) * HD + d + 8] = acc[m][3]; }
+    }
+  }
+  cluster.sync();
+
+  // ---- each rank folds its slice of the NREP*HD outputs over the ranks, in rank order
+  const int per_rank = (NREP * HD + CS - 1) / CS;
+  for (int k = tid; k < per_rank; k += AM_THREADS) {
+    const int idx = rank * per_rank + k;
+    if (idx < NREP * HD) {
+      float s = 0.f;
+      for (int rk = 0; rk < CS; rk++) s = __fadd_rn(s, *cluster.map_shared_rank(&o_part[idx], rk));
+      a.out[(size_t)b * a.H * HD + (size_t)g * NREP * HD + idx] = __float2half_rn(s);
+    }
+  }
+  cluster.sync();  // peers may still be reading this CTA's shared memory
+}

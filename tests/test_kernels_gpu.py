@@ -241,7 +241,7 @@ def test_tensor_core_projection(dev, M, int8):
 
 # ------------------------------------------------------------------------------------------------ RoPE + attention
 @pytest.mark.parametrize("hd,H,G", [(64, 32, 8), (128, 24, 8), (128, 8, 8), (64, 4, 2), (128, 16, 2)])
-@pytest.mark.parametrize("B,T,n_split", [(1, 1, 0), (1, 97, 0), (2, 300, 3), (1, 1000, 0), (3, 65, 1)])
+@pytest.mark.parametrize("B,T,n_split", [(1, 1, 0), (1, 97, 0), (2, 300, 3), (1, 1000, 0), (3, 65, 1), (6, 130, 0)])
 def test_rope_cache_attention(dev, hd, H, G, B, T, n_split):
     rng = np.random.default_rng(hd + H + T)
     max_ctx = 1024
