@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "peer.cuh"
 
 // The slice of NCCL's C API used here (nccl.h of NCCL 2.x; the values are ABI-stable).
 typedef struct { char internal[128]; } nccl_unique_id;
@@ -129,20 +130,18 @@ JG_API int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count) {
 
 // ------------------------------------------------------------------------------------------------ peer-memory reductions
 // A decode step at small batch all-reduces 16 KB twice per layer; a library collective spends most of that in launch
-// and protocol latency.  The exchange below is one kernel per rank over NVLink peer memory: every rank stores its fp32
-// partial sums straight into a slot of every peer's buffer, raises a flag there, waits (bounded) for the peers' flags on
-// its own buffer, adds the slots in rank order — the same order on every rank, so all ranks hold bit-identical sums —
-// and applies the residual add of TransformerBlock.call (jsgrad/models/llama.ts:125-126) in the same pass.
-// Buffers alternate between two parities (of one exchange counter per rank, kept on the device): a rank can be at most
-// one exchange ahead of a peer (it needs that peer's flag of the current exchange to finish it, and the peer raises it
-// only after its previous exchange has completed), so the slots a slow peer is still reading are never overwritten.
-// Peer buffers are plain cudaMalloc memory opened through CUDA IPC handles; plain stores and loads only.
-constexpr int PEER_MAX_WORLD = 8;
-constexpr int PEER_MAX_CTAS = 16;
-constexpr size_t PEER_SLOT_FLOATS = 128 * 1024;  // 512 KB of fp32 per (parity, rank): larger exchanges go through NCCL
-constexpr size_t PEER_FLAG_WORDS = 2 * PEER_MAX_CTAS * PEER_MAX_WORLD;
-constexpr size_t PEER_BYTES = 2 * PEER_MAX_WORLD * PEER_SLOT_FLOATS * sizeof(float) + PEER_FLAG_WORDS * sizeof(uint32_t);
-
+// and protocol latency.  The exchanges below run over NVLink peer memory (plain cudaMalloc buffers opened through CUDA
+// IPC handles; plain stores and loads only).  Sums use flag-in-data entries (peer.cuh): every rank stores each of its
+// fp32 partial sums, paired with the exchange number, straight into its slot of every peer's buffer with one 8-byte
+// store, then reads the peers' entries from its own buffer, waiting (bounded) until each carries the current exchange
+// number — no fence, no separate flag, one NVLink crossing of latency — adds them in rank order (the same order on
+// every rank, so all ranks hold bit-identical sums) and applies the residual add of TransformerBlock.call
+// (jsgrad/models/llama.ts:125-126) in the same pass.  gemv.cu runs the same exchange inside the projection kernel for
+// up to 8 rows (jg_linear_allreduce_residual).  The max-reduction of the greedy keys uses data + one flag per peer.
+// Buffers alternate between two parities (of one exchange counter per rank, kept on the device so that graph replays
+// advance it): a rank can be at most one exchange ahead of a peer (it needs that peer's entries of the current exchange
+// to finish it, and the peer writes them only after its previous exchange has completed), so the slots a slow peer is
+// still reading are never overwritten.
 struct jg_peer {
   unsigned char* local;                   // this rank's buffer: slots [2][world][PEER_SLOT_FLOATS], then the flags
   unsigned char* mapped[PEER_MAX_WORLD];  // every rank's buffer as mapped here (own entry = local)
@@ -153,107 +152,81 @@ struct jg_peer {
 };
 static jg_peer g_peer[64] = {};  // by device ordinal
 
-struct PeerArgs {
-  unsigned char* buf[PEER_MAX_WORLD];
-  uint32_t* epoch;
-  int* err;
-  const float* part;  // [n] this rank's partial sums (fp32) / packed keys (as 2 x u32 per key)
-  __half* h;          // [n] residual stream, updated in place (sum mode)
-  unsigned long long* keys;  // [n] (max mode), updated in place
-  long long n;        // floats (sum mode) or keys (max mode)
-  unsigned long long timeout_ns;
-  int rank, world;
-};
-
-__device__ __forceinline__ float* peer_slot(unsigned char* buf, int parity, int r) {
-  return reinterpret_cast<float*>(buf) + ((size_t)parity * PEER_MAX_WORLD + r) * PEER_SLOT_FLOATS;
-}
-__device__ __forceinline__ uint32_t* peer_flag(unsigned char* buf, int parity, int cta, int r) {
-  return reinterpret_cast<uint32_t*>(buf + 2 * PEER_MAX_WORLD * PEER_SLOT_FLOATS * sizeof(float)) +
-         ((size_t)parity * PEER_MAX_CTAS + cta) * PEER_MAX_WORLD + r;
-}
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-
-// MODE 0: h <- h + half(sum over ranks of part)   MODE 1: keys <- max over ranks of keys (u64)
-template <int MODE>
-__global__ void __launch_bounds__(256) peer_reduce_kernel(const PeerArgs a) {
-  __shared__ int s_fail;
-  const int cta = blockIdx.x, tid = threadIdx.x;
+// h <- h + half(sum over ranks of part): flag-in-data exchange, every thread carries its own elements through it.
+__global__ void __launch_bounds__(256) peer_sum_residual_kernel(const PeerArgs a) {
   pdl_launch();
   pdl_wait();
   const uint32_t epoch = a.epoch[0] + 1;  // advanced below by the last CTA of this launch to finish
   const int parity = (int)(epoch & 1u);
-  // 16-byte units: 4 floats or 2 keys
-  const long long units = MODE == 0 ? a.n / 4 : (a.n + 1) / 2;
-  const long long per = (units + gridDim.x - 1) / gridDim.x;
-  const long long u0 = cta * per, u1 = (u0 + per < units) ? u0 + per : units;
-  if (tid == 0) s_fail = 0;
-  // ---- push this rank's slice into slot [rank] of every peer
-  const float4* src = reinterpret_cast<const float4*>(MODE == 0 ? (const void*)a.part : (const void*)a.keys);
-  for (long long u = u0 + tid; u < u1; u += blockDim.x) {
-    const float4 v = src[u];
+  const long long stride = (long long)gridDim.x * blockDim.x, first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (long long i = first; i < a.n; i += stride) {
+    const float v = a.part[i];
     for (int p = 0; p < a.world; p++)
-      if (p != a.rank) reinterpret_cast<float4*>(peer_slot(a.buf[p], parity, a.rank))[u] = v;
+      if (p != a.rank) peer_ll_store(peer_ll(a.buf[p], parity, a.rank) + i, v, epoch);
   }
-  __threadfence_system();
-  __syncthreads();
-  if (tid < a.world && tid != a.rank) {
-    uint32_t* f = peer_flag(a.buf[tid], parity, cta, a.rank);
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
-    // ---- wait for that peer's flag on this rank's own buffer; give up after timeout_ns and say so
-    const uint32_t* mine = peer_flag(a.buf[a.rank], parity, cta, tid);
-    const unsigned long long t0 = global_ns();
-    for (;;) {
-      uint32_t v;
-      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-      if ((int32_t)(v - epoch) >= 0) break;
-      if (global_ns() - t0 > a.timeout_ns) { s_fail = 1; atomicCAS(a.err, 0, 1); break; }
-      __nanosleep(20);
+  bool ok = true;
+  for (long long i = first; i < a.n && ok; i += stride) {
+    float sum = 0.f;
+    for (int r = 0; r < a.world && ok; r++) {  // rank order on every rank
+      float v = a.part[i];
+      if (r != a.rank) ok = peer_ll_load(peer_ll(a.buf[a.rank], parity, r) + i, epoch, a.timeout_ns, &v);
+      sum = __fadd_rn(sum, v);
     }
+    if (ok) a.h[i] = hadd1(a.h[i], __float2half_rn(sum));
   }
+  if (!ok) atomicCAS(a.err, 0, 1);
   __syncthreads();
-  if (!s_fail) {
-    for (long long u = u0 + tid; u < u1; u += blockDim.x) {
-      if (MODE == 0) {
-        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < a.world; r++) {  // rank order on every rank
-          const float4 v = (r == a.rank) ? src[u] : reinterpret_cast<const float4*>(peer_slot(a.buf[a.rank], parity, r))[u];
-          s.x = __fadd_rn(s.x, v.x); s.y = __fadd_rn(s.y, v.y); s.z = __fadd_rn(s.z, v.z); s.w = __fadd_rn(s.w, v.w);
-        }
-        uint2 raw = reinterpret_cast<uint2*>(a.h)[u];
-        __half* hh = reinterpret_cast<__half*>(&raw);
-        hh[0] = hadd1(hh[0], __float2half_rn(s.x));
-        hh[1] = hadd1(hh[1], __float2half_rn(s.y));
-        hh[2] = hadd1(hh[2], __float2half_rn(s.z));
-        hh[3] = hadd1(hh[3], __float2half_rn(s.w));
-        reinterpret_cast<uint2*>(a.h)[u] = raw;
-      } else {
-        for (int e = 0; e < 2; e++) {
-          const long long i = u * 2 + e;
-          if (i >= a.n) break;
-          unsigned long long best = a.keys[i];
-          for (int r = 0; r < a.world; r++) {
-            if (r == a.rank) continue;
-            const unsigned long long v = reinterpret_cast<const unsigned long long*>(peer_slot(a.buf[a.rank], parity, r))[i];
-            best = v > best ? v : best;
-          }
-          a.keys[i] = best;
-        }
-      }
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
+  if (threadIdx.x == 0) {
     __threadfence();
-    if (atomicAdd(&a.epoch[1], 1u) == gridDim.x - 1) {  // every CTA of the launch has read the epoch by now
+    if (atomicAdd(&a.epoch[1], 1u) == gridDim.x - 1) {
       a.epoch[1] = 0;
       a.epoch[0] = epoch;
     }
   }
+}
+
+// keys <- max over ranks of keys (u64): data into the upper half of every peer's slot, one flag per peer, bounded wait.
+__global__ void __launch_bounds__(256) peer_max_kernel(const PeerArgs a) {
+  __shared__ int s_fail;
+  const int tid = threadIdx.x;
+  pdl_launch();
+  pdl_wait();
+  const uint32_t epoch = a.epoch[0] + 1;
+  const int parity = (int)(epoch & 1u);
+  if (tid == 0) s_fail = 0;
+  for (long long i = tid; i < a.n; i += blockDim.x) {
+    const unsigned long long v = a.keys[i];
+    for (int p = 0; p < a.world; p++)
+      if (p != a.rank) reinterpret_cast<unsigned long long*>(peer_slot_hi(a.buf[p], parity, a.rank))[i] = v;
+  }
+  __syncthreads();  // the release below is cumulative over what this CTA's threads stored before the barrier
+  if (tid < a.world && tid != a.rank) {
+    uint32_t* f = peer_flag(a.buf[tid], parity, 0, a.rank);
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    const uint32_t* mine = peer_flag(a.buf[a.rank], parity, 0, tid);
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if (global_ns() - t0 > a.timeout_ns) { s_fail = 1; atomicCAS(a.err, 0, 1); break; }
+    }
+    asm volatile("fence.acquire.sys;" ::: "memory");
+  }
+  __syncthreads();
+  if (!s_fail) {
+    for (long long i = tid; i < a.n; i += blockDim.x) {
+      unsigned long long best = a.keys[i];
+      for (int r = 0; r < a.world; r++) {
+        if (r == a.rank) continue;
+        const unsigned long long v = reinterpret_cast<const unsigned long long*>(peer_slot_hi(a.buf[a.rank], parity, r))[i];
+        best = v > best ? v : best;
+      }
+      a.keys[i] = best;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) { __threadfence(); a.epoch[0] = epoch; }  // single CTA
 }
 
 // Allocate this rank's exchange buffer and return its 64-byte CUDA IPC handle, to be handed to every other rank.
@@ -309,25 +282,33 @@ JG_API int jg_comm_peer_open(jg_comm* comm, const void* handles) {
 JG_API int jg_comm_peer_capacity(jg_comm* comm, uint64_t* floats) {
   JG_REQUIRE(comm != nullptr && floats != nullptr, "comm_peer_capacity: null argument");
   const int o = comm->dev->ordinal;
-  *floats = (o >= 0 && o < 64 && g_peer[o].open) ? PEER_SLOT_FLOATS : 0;
+  *floats = (o >= 0 && o < 64 && g_peer[o].open) ? PEER_LL_VALUES : 0;
+  return JG_OK;
+}
+
+int jg_peer_fill_args(jg_comm* comm, PeerArgs* a) {
+  jg_dev* dev = comm->dev;
+  JG_REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64 && g_peer[dev->ordinal].open,
+             "peer reduction: the peer buffers are not open (jg_comm_peer_export / jg_comm_peer_open)");
+  jg_peer& p = g_peer[dev->ordinal];
+  for (int r = 0; r < comm->world; r++) a->buf[r] = p.mapped[r];
+  a->epoch = p.epoch; a->err = p.err; a->timeout_ns = p.timeout_ns; a->rank = comm->rank; a->world = comm->world;
+  dev->peer_pending = true;
   return JG_OK;
 }
 
 static int peer_launch(jg_comm* comm, int mode, uint64_t h, uint64_t part, uint64_t keys, long long n) {
   jg_dev* dev = comm->dev;
-  jg_peer& p = g_peer[dev->ordinal];
-  JG_REQUIRE(p.open, "peer reduction: the peer buffers are not open (jg_comm_peer_export / jg_comm_peer_open)");
   PeerArgs a = {};
-  for (int r = 0; r < comm->world; r++) a.buf[r] = p.mapped[r];
-  a.epoch = p.epoch; a.err = p.err; a.part = (const float*)part; a.h = (__half*)h; a.keys = (unsigned long long*)keys;
-  a.n = n; a.timeout_ns = p.timeout_ns; a.rank = comm->rank; a.world = comm->world;
-  const long long units = mode == 0 ? n / 4 : (n + 1) / 2;
-  int ctas = (int)((units + 1023) / 1024);  // 16 KB per CTA
-  if (ctas < 1) ctas = 1;
-  if (ctas > PEER_MAX_CTAS) ctas = PEER_MAX_CTAS;
-  dev->peer_pending = true;
-  if (mode == 0) return jg_launch(dev, "peer_allreduce_residual", peer_reduce_kernel<0>, dim3(ctas), dim3(256), 0, a);
-  return jg_launch(dev, "peer_allreduce_max", peer_reduce_kernel<1>, dim3(ctas), dim3(256), 0, a);
+  int rc = jg_peer_fill_args(comm, &a);
+  if (rc) return rc;
+  a.part = (const float*)part; a.h = (__half*)h; a.keys = (unsigned long long*)keys; a.n = n;
+  if (mode == 0) {
+    int ctas = (int)((n + 1023) / 1024);
+    if (ctas > 32) ctas = 32;
+    return jg_launch(dev, "peer_allreduce_residual", peer_sum_residual_kernel, dim3(ctas), dim3(256), 0, a);
+  }
+  return jg_launch(dev, "peer_allreduce_max", peer_max_kernel, dim3(1), dim3(256), 0, a);
 }
 
 // h[i] <- h[i] + half( sum over ranks of part[i] ), i < n: all-reduce of a row-parallel projection's fp32 partial sums
@@ -335,9 +316,9 @@ static int peer_launch(jg_comm* comm, int mode, uint64_t h, uint64_t part, uint6
 JG_API int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32, uint64_t n) {
   JG_REQUIRE(comm != nullptr, "peer_allreduce_residual: null communicator");
   JG_ENTER(comm->dev);
-  JG_REQUIRE(n > 0 && n % 4 == 0 && n <= PEER_SLOT_FLOATS, "peer_allreduce_residual: n=%llu must be a multiple of 4, at most %llu",
-             (unsigned long long)n, (unsigned long long)PEER_SLOT_FLOATS);
-  JG_REQUIRE(jg_aligned(h, 8) && jg_aligned(part32, 16), "peer_allreduce_residual: null or misaligned pointer");
+  JG_REQUIRE(n > 0 && n <= PEER_LL_VALUES, "peer_allreduce_residual: n=%llu must be at most %llu", (unsigned long long)n,
+             (unsigned long long)PEER_LL_VALUES);
+  JG_REQUIRE(jg_aligned(h, 2) && jg_aligned(part32, 4), "peer_allreduce_residual: null or misaligned pointer");
   return peer_launch(comm, 0, h, part32, 0, (long long)n);
 }
 
@@ -345,10 +326,12 @@ JG_API int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32
 JG_API int jg_peer_allreduce_max_u64(jg_comm* comm, uint64_t keys, uint64_t n) {
   JG_REQUIRE(comm != nullptr, "peer_allreduce_max_u64: null communicator");
   JG_ENTER(comm->dev);
-  JG_REQUIRE(n > 0 && n * 2 <= PEER_SLOT_FLOATS, "peer_allreduce_max_u64: n=%llu out of range", (unsigned long long)n);
-  JG_REQUIRE(jg_aligned(keys, 16), "peer_allreduce_max_u64: null or misaligned pointer");
+  JG_REQUIRE(n > 0 && n * 4 <= PEER_SLOT_FLOATS, "peer_allreduce_max_u64: n=%llu out of range", (unsigned long long)n);
+  JG_REQUIRE(jg_aligned(keys, 8), "peer_allreduce_max_u64: null or misaligned pointer");
   return peer_launch(comm, 1, 0, 0, keys, (long long)n);
 }
+
+jg_dev* jg_comm_device(jg_comm* comm) { return comm ? comm->dev : nullptr; }
 
 // Device error word of the peer reductions for jg_check_device_errors (0 = none recorded).
 int jg_peer_error(jg_dev* dev, int* code) {

@@ -19,10 +19,16 @@
 //   epilogue  RESIDUAL  y <- residual + half(acc)       (x.add(...), fp16 add)
 //             SWIGLU    y <- silu(half(acc_gate)) * half(acc_up)
 //             LOGITS    y <- half(acc) and (value, lowest index) folded into a 64-bit max key per row
+//             PARTIAL   y32 <- acc (fp32): one rank's share of a row-parallel projection, reduced by a later call
+//             PEER      y <- residual + half(sum over ranks of acc): the same share, all-reduced inside this kernel
+//                       over NVLink peer memory — CTA c of every rank owns the same output rows, so it pushes its
+//                       partial sums into the peers' buffers, raises a flag per peer, waits (bounded) for the peers'
+//                       CTA c and finishes its rows itself; no grid-wide step and no second launch
 #include "common.cuh"
+#include "peer.cuh"
 #include "transcendental.cuh"
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3, EPI_PARTIAL = 4 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3, EPI_PARTIAL = 4, EPI_PEER = 5 };
 
 struct GemvArgs {
   const __half* x;       // [M][K]
@@ -38,6 +44,7 @@ struct GemvArgs {
   int row_offset;           // LOGITS: vocabulary index of weight row 0 (vocabulary-sharded output layer)
   float eps, recip_k;
   int M, N, K;
+  PeerArgs peer;            // PEER: exchange buffers of the ranks, exchange counter, error word
 };
 
 constexpr int GEMV_THREADS = 256;
@@ -111,6 +118,16 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
 
   // ---- everything below reads what the previous kernel wrote
   pdl_wait();
+  // PEER: this exchange's number and buffer parity (the counter is advanced by the last CTA of this launch to finish);
+  // the partial sums land in this rank's own slot first
+  uint32_t peer_epoch = 0;
+  int peer_parity = 0;
+  float* peer_mine = nullptr;
+  if (EPI == EPI_PEER) {
+    peer_epoch = a.peer.epoch[0] + 1;
+    peer_parity = (int)(peer_epoch & 1u);
+    peer_mine = peer_slot(a.peer.buf[a.peer.rank], peer_parity, a.peer.rank);
+  }
 
   // ---- prologue: activation rows -> shared memory (normalised when NORM); rows beyond M are zero
   for (int m = 0; m < MT; m++) {
@@ -186,6 +203,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
   auto finish = [&](int row, int m, float s_a, float s_b) {
     const size_t o = (size_t)m * N + (size_t)row;
     if (EPI == EPI_PARTIAL) { a.y32[o] = s_a; return; }
+    if (EPI == EPI_PEER) { peer_mine[o] = s_a; return; }
     __half v = __float2half_rn(s_a);
     if (EPI == EPI_RESIDUAL) v = hadd1(a.residual[o], v);
     if (EPI == EPI_SWIGLU) v = jg_silu_mul(v, __float2half_rn(s_b));
@@ -287,6 +305,40 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
     __syncthreads();  // `part` is rewritten by the next pass
   }
 
+  if (EPI == EPI_PEER) {
+    // ---- all-reduce of this CTA's output rows [r_lo, r_hi) with CTA blockIdx.x of the other ranks, then the residual
+    //      add.  Each thread carries its outputs through the whole exchange (flag-in-data entries, see peer.cuh).
+    const int r_lo = u0 * RW, r_hi = min(u1 * RW, N), nr = r_hi - r_lo;
+    const int rank = a.peer.rank, world = a.peer.world;
+    __syncthreads();  // the partial sums written by other threads of this CTA are visible
+    bool ok = true;
+    for (int i = tid; i < nr * a.M; i += GEMV_THREADS) {
+      const size_t o = (size_t)(i / nr) * N + r_lo + (i % nr);
+      const float v = peer_mine[o];
+      for (int p = 0; p < world; p++)
+        if (p != rank) peer_ll_store(peer_ll(a.peer.buf[p], peer_parity, rank) + o, v, peer_epoch);
+    }
+    for (int i = tid; i < nr * a.M; i += GEMV_THREADS) {
+      const size_t o = (size_t)(i / nr) * N + r_lo + (i % nr);
+      float sum = 0.f;
+      for (int r = 0; r < world && ok; r++) {  // rank order on every rank: identical sums everywhere
+        float v = peer_mine[o];
+        if (r != rank) ok = peer_ll_load(peer_ll(a.peer.buf[rank], peer_parity, r) + o, peer_epoch, a.peer.timeout_ns, &v);
+        sum = __fadd_rn(sum, v);
+      }
+      if (ok) a.y[o] = hadd1(a.residual[o], __float2half_rn(sum));
+    }
+    if (!ok) atomicCAS(a.peer.err, 0, 1);
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      if (atomicAdd(&a.peer.epoch[1], 1u) == gridDim.x - 1) {  // every CTA of the launch has read the counter by now
+        a.peer.epoch[1] = 0;
+        a.peer.epoch[0] = peer_epoch;
+      }
+    }
+  }
+
   if (EPI == EPI_LOGITS) {
     // every thread may have stored outputs of some batch row m (bulk: lane r*MT+m; remainder: tid % MT)
 #pragma unroll
@@ -334,6 +386,7 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
   const int n_units = (a.N + RW - 1) / RW;
   long long blocks = (long long)dev->sm_count * occ_for[slot];
   if (blocks > n_units) blocks = n_units;
+  if (EPI == EPI_PEER && blocks > PEER_MAX_CTAS) blocks = PEER_MAX_CTAS;  // one flag row per CTA
   if (blocks < 1) blocks = 1;
   return jg_launch(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, a);
 }
@@ -361,6 +414,14 @@ static int tc_min_rows() {
 
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
+  if (EPI == EPI_PEER) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
+    if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
+    if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
+    if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
+    if (a.M <= 8) return launch_gemv<8, W8, EPI, NORM>(dev, a, name);
+    jg_set_error("%s: the projection fused with its all-reduce takes at most 8 rows (M=%d)", name, a.M);
+    return JG_ENOTSUP;
+  }
   if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
   if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
@@ -466,4 +527,27 @@ static int logits_impl(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, u
   a.M = M; a.N = V; a.K = K; a.row_offset = row_offset;
   if (norm_w == 0) return scale ? dispatch_m<true, EPI_LOGITS, false>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, false>(dev, a, "norm_logits_argmax");
   return scale ? dispatch_m<true, EPI_LOGITS, true>(dev, a, "norm_logits_argmax") : dispatch_m<false, EPI_LOGITS, true>(dev, a, "norm_logits_argmax");
+}
+
+// h <- h + half( sum over ranks of x . W^T ): a row-parallel projection (this rank holds a K-slice of W) fused with its
+// all-reduce over NVLink peer memory and the residual add of TransformerBlock.call (jsgrad/models/llama.ts:125-126), one
+// launch per rank, up to 8 rows.  Every rank must call it with the same shapes, in the same order relative to its other
+// peer reductions.  Needs jg_comm_peer_open; M * N is limited by the exchange buffer.
+jg_dev* jg_comm_device(jg_comm* comm);
+JG_API int jg_linear_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t x, uint64_t w, uint64_t scale, int32_t M,
+                                        int32_t N, int32_t K) {
+  JG_REQUIRE(comm != nullptr, "linear_allreduce_residual: null communicator");
+  jg_dev* dev = jg_comm_device(comm);
+  JG_ENTER(dev);
+  int rc = check_common("linear_allreduce_residual", h, x, w, scale, M, N, K);
+  if (rc) return rc;
+  JG_REQUIRE(M <= 8 && (size_t)M * N <= PEER_LL_VALUES, "linear_allreduce_residual: M=%d N=%d exceed 8 rows / %zu outputs",
+             M, N, (size_t)PEER_LL_VALUES);
+  GemvArgs a = {};
+  a.x = (const __half*)x; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)h; a.residual = (const __half*)h;
+  a.M = M; a.N = N; a.K = K;
+  rc = jg_peer_fill_args(comm, &a.peer);
+  if (rc) return rc;
+  return scale ? dispatch_m<true, EPI_PEER, false>(dev, a, "linear_allreduce_residual")
+               : dispatch_m<false, EPI_PEER, false>(dev, a, "linear_allreduce_residual");
 }

@@ -1,0 +1,69 @@
+// Shared between comm.cu (buffers, stand-alone reductions) and gemv.cu (projection fused with its all-reduce): layout
+// of a rank's peer-exchange buffer and the device helpers that address it.
+#pragma once
+#include "common.cuh"
+
+constexpr int PEER_MAX_WORLD = 8;
+constexpr int PEER_MAX_CTAS = 512;  // flag rows: a fused projection raises one flag per CTA and rank
+constexpr size_t PEER_SLOT_FLOATS = 128 * 1024;  // 512 KB of fp32 per (parity, rank): larger exchanges go through NCCL
+constexpr size_t PEER_FLAG_WORDS = 2 * PEER_MAX_CTAS * PEER_MAX_WORLD;
+constexpr size_t PEER_BYTES = 2 * PEER_MAX_WORLD * PEER_SLOT_FLOATS * sizeof(float) + PEER_FLAG_WORDS * sizeof(uint32_t);
+
+struct PeerArgs {
+  unsigned char* buf[PEER_MAX_WORLD];
+  uint32_t* epoch;
+  int* err;
+  const float* part;  // [n] this rank's partial sums (fp32) / packed keys (as 2 x u32 per key)
+  __half* h;          // [n] residual stream, updated in place (sum mode)
+  unsigned long long* keys;  // [n] (max mode), updated in place
+  long long n;        // floats (sum mode) or keys (max mode)
+  unsigned long long timeout_ns;
+  int rank, world;
+};
+
+__device__ __forceinline__ float* peer_slot(unsigned char* buf, int parity, int r) {
+  return reinterpret_cast<float*>(buf) + ((size_t)parity * PEER_MAX_WORLD + r) * PEER_SLOT_FLOATS;
+}
+__device__ __forceinline__ uint32_t* peer_flag(unsigned char* buf, int parity, int cta, int r) {
+  return reinterpret_cast<uint32_t*>(buf + 2 * PEER_MAX_WORLD * PEER_SLOT_FLOATS * sizeof(float)) +
+         ((size_t)parity * PEER_MAX_CTAS + cta) * PEER_MAX_WORLD + r;
+}
+// Flag-in-data exchange for small sums: the lower half of a slot holds up to PEER_LL_VALUES entries of
+// (value bits, exchange number), each written with one 8-byte store, so a receiver that sees the right exchange number
+// has the value — no fence and no separate flag.  Flag-based exchanges (keys) use the upper half of the slot.
+constexpr size_t PEER_LL_VALUES = PEER_SLOT_FLOATS / 4;  // 32 K entries = 256 KB
+__device__ __forceinline__ uint2* peer_ll(unsigned char* buf, int parity, int r) {
+  return reinterpret_cast<uint2*>(peer_slot(buf, parity, r));
+}
+__device__ __forceinline__ float* peer_slot_hi(unsigned char* buf, int parity, int r) {
+  return peer_slot(buf, parity, r) + PEER_SLOT_FLOATS / 2;
+}
+__device__ __forceinline__ void peer_ll_store(uint2* p, float v, uint32_t epoch) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(epoch) : "memory");
+}
+__device__ __forceinline__ unsigned long long global_ns();
+// Wait (bounded) until entry *p carries `epoch`; false = gave up.
+__device__ __forceinline__ bool peer_ll_load(const uint2* p, uint32_t epoch, unsigned long long timeout_ns, float* out) {
+  uint32_t v, e;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(e) : "l"(p) : "memory");
+  if (e != epoch) {
+    const unsigned long long t0 = global_ns();
+    do {
+      if (global_ns() - t0 > timeout_ns) return false;
+      asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v), "=r"(e) : "l"(p) : "memory");
+    } while (e != epoch);
+  }
+  *out = __uint_as_float(v);
+  return true;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+
+struct jg_comm;
+// Fill the exchange-related fields of `a` (buffers, counters, rank, world, timeout) for this communicator; JG_EINVAL
+// when the peer buffers are not open.
+int jg_peer_fill_args(jg_comm* comm, PeerArgs* a);

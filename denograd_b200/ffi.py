@@ -98,6 +98,7 @@ SIGNATURES: dict[str, list] = {
     "jg_comm_peer_capacity": [_vp, _vp],
     "jg_peer_allreduce_residual": [_vp, _u64, _u64, _u64],
     "jg_peer_allreduce_max_u64": [_vp, _u64, _u64],
+    "jg_linear_allreduce_residual": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_linear_partial": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_residual_add_f32": [_vp, _u64, _u64, _i64],
     "jg_norm_logits_argmax_shard": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32, _i32],

@@ -196,6 +196,9 @@ class TransformerBlock:
             lin.call(x, residual=ws.h, out=ws.h)
             return
         dev = ws.h.dev
+        if ws.B <= tp.fused_rows(lin.scale_ptr != 0):
+            tp.linear_into_residual(ws.h, x, lin, ws.B)
+            return
         dev.call("jg_linear_partial", ws.part32.ptr, x.ptr, lin.weight.ptr, lin.scale_ptr, ws.B, lin.out_features, lin.in_features)
         tp.reduce_into_residual(ws.h, ws.part32)
 

@@ -154,6 +154,18 @@ class TensorParallel:
             self.all_reduce_sum(part32)
             self.dev.call("jg_residual_add_f32", h.ptr, part32.ptr, n)
 
+    def fused_rows(self, int8: bool) -> int:
+        """Most rows for which a row-parallel projection runs fused with its exchange (`linear_into_residual`):
+        the matrix-vector kernels win up to 2 rows of fp16 weights and serve int8 up to 8; 0 without peer memory."""
+        if self.peer_capacity <= 0 or os.environ.get("JG_TP_FUSED", "1") == "0":
+            return 0
+        return 8 if int8 else 2
+
+    def linear_into_residual(self, h: Tensor, x: Tensor, lin, rows: int) -> None:
+        """h <- h + half(sum over ranks of lin(x)) in one launch per rank (projection + all-reduce + residual add)."""
+        ffi.call("jg_linear_allreduce_residual", self.handle, h.ptr, x.ptr, lin.weight.ptr, lin.scale_ptr, rows,
+                 lin.out_features, lin.in_features)
+
     def all_reduce_sum(self, t: Tensor) -> None:
         assert t.dtype == "float32"
         ffi.call("jg_allreduce_sum_f32", self.handle, t.ptr, t.numel())

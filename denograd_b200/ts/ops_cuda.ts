@@ -83,6 +83,7 @@ export const SYMBOLS = {
   jg_comm_peer_capacity: fn([ptr, ptr]),
   jg_peer_allreduce_residual: fn([ptr, u64, u64, u64]),
   jg_peer_allreduce_max_u64: fn([ptr, u64, u64]),
+  jg_linear_allreduce_residual: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
   jg_linear_partial: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
   jg_residual_add_f32: fn([ptr, u64, u64, 'i64']),
   jg_norm_logits_argmax_shard: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32, i32]),

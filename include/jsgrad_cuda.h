@@ -239,6 +239,12 @@ int jg_comm_peer_open(jg_comm* comm, const void* handles);
 int jg_comm_peer_capacity(jg_comm* comm, uint64_t* floats);
 int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32, uint64_t n);
 int jg_peer_allreduce_max_u64(jg_comm* comm, uint64_t keys, uint64_t n);
+/* A row-parallel Linear (this rank holds a K-slice of W, nn/index.ts:411) fused with that exchange and the residual
+ * add: h <- h + half(sum over ranks of x . W^T) in one launch per rank, for up to 8 rows.  CTA c of every rank owns
+ * the same output rows: it stores its partial sums into the peers' buffers, raises one flag per peer, waits (bounded)
+ * for the peers' CTA c and finishes its rows. */
+int jg_linear_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N,
+                                 int32_t K);
 /* y32[m][n] = sum_k x[m][k] W[n][k] left in fp32 (this rank's K-slice of a row-parallel Linear, nn/index.ts:411). */
 int jg_linear_partial(jg_dev* dev, uint64_t y32, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K);
 /* h <- h + half(p32): rounding + residual add of jsgrad/models/llama.ts:125-126 after the all-reduce. */
