@@ -270,7 +270,8 @@ def run_gpu(args) -> None:
     ws = model._workspace(B)
     d, f = p["dim"], p["hidden_dim"] // world  # f: this rank's share of the FFN width
 
-    big = B > 8 or (B >= 3 and not int8)
+    from denograd_b200.llama import _norm_first
+    big = _norm_first(B, int8)  # the projection takes pre-normalised rows and runs on the tensor cores
 
     def gateup(layer):
         ff = layer.feed_forward

@@ -302,6 +302,7 @@ static int dispatch_ks(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
 
 template <int EPI, bool W8>
 static int dispatch_mt(jg_dev* dev, const GemmSmallArgs& a, const char* name) {
+  if (a.M <= 8) return dispatch_ks<8, EPI, W8>(dev, a, name);
   if (a.M <= 16) return dispatch_ks<16, EPI, W8>(dev, a, name);
   if (a.M <= 32) return dispatch_ks<32, EPI, W8>(dev, a, name);
   if (a.M <= 64) return dispatch_ks<64, EPI, W8>(dev, a, name);

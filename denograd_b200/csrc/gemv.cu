@@ -412,6 +412,12 @@ static int tc_min_rows() {
   return v;
 }
 
+static bool w8_mma() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JG_W8_MMA"); v = (e && atoi(e) == 0) ? 0 : 1; }
+  return v != 0;
+}
+
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (EPI == EPI_PEER) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
@@ -424,6 +430,11 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   }
   if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
+  // int8 weights: the CUDA-core kernel spends its issue slots on dequantisation (half(q) * scale, widen, FMA: about 80
+  // instructions per 16 bytes) and reaches half of the HBM rate; on the tensor cores the widening and the FMAs are
+  // gone, so pre-normalised int8 projections of any row count go to the mma.sync kernel (JG_W8_MMA=0 keeps the
+  // CUDA-core kernel)
+  if (W8 && !NORM && a.K >= 256 && w8_mma()) return jg_gemm_small(dev, EPI, a.x, a.w0, a.w1, a.s0, a.s1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
   if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
   // from 3 rows on the CUDA cores cannot keep up with the weight stream: unnormalised fp16 projections go to the

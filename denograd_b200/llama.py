@@ -160,7 +160,7 @@ class TransformerBlock:
         wqkv = a._wqkv
         # from 3 rows on (fp16 weights) normalise into ws.xn and project on the tensor cores; the fused-norm kernels
         # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: up to 8 rows)
-        big = B > 8 or (B >= 3 and wqkv.scale_ptr == 0)
+        big = _norm_first(B, wqkv.scale_ptr != 0)
         if big:
             self.attention_norm.call(ws.h, out=ws.xn)
             dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, wqkv.weight.ptr, wqkv.scale_ptr, 0, B, wqkv.out_features, d)
@@ -214,6 +214,15 @@ def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float) 
     out = Tensor.empty((rows,), "int32", logits.dev)
     logits.dev.call("jg_argmax", out.ptr, logits.ptr, rows, logits.shape[-1])
     return out
+
+
+def _norm_first(rows: int, int8: bool) -> bool:
+    """Whether RMSNorm runs as its own kernel ahead of a projection.  The matrix-vector kernels fuse the norm into
+    their prologue; the tensor-core kernels take normalised rows: fp16 weights from 3 rows on, int8 weights always
+    (their CUDA-core kernel is bound by dequantisation, not by HBM; JG_W8_MMA=0 restores it up to 8 rows)."""
+    if int8:
+        return rows > 8 or os.environ.get("JG_W8_MMA", "1") != "0"
+    return rows >= 3
 
 
 class _Workspace:
@@ -351,7 +360,7 @@ class Transformer:
             for layer in self.layers:
                 layer.call_fused(ws, ws.pos, self.freqs_cis, self._tp)
             out = self.output
-            if B > 8 or (B >= 3 and out.scale_ptr == 0):
+            if _norm_first(B, out.scale_ptr != 0):
                 self.norm.call(ws.h, out=ws.xn)
                 dev.call("jg_norm_logits_argmax_shard", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
                          out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)

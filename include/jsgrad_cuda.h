@@ -230,10 +230,11 @@ int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count);  /* greed
  * (multi.ts has no counterpart: its functions throw).  jg_comm_peer_export allocates this rank's exchange buffer and
  * returns its 64-byte CUDA IPC handle; after every rank's handle has been gathered out of band (world x 64 bytes in
  * rank order) jg_comm_peer_open maps the peers' buffers.  jg_peer_allreduce_residual then does
- * h[i] <- h[i] + half(sum over ranks of part32[i]) in one launch: partial sums are stored into every peer's buffer,
- * flags raised, the peers' flags awaited (bounded: JG_ETIMEDOUT at the next synchronisation if a peer never
- * arrives; JG_PEER_TIMEOUT_MS, default 20000), slots added in rank order.  All ranks must issue the same sequence of
- * peer reductions.  jg_comm_peer_capacity reports the largest n (0 while the peer path is not open). */
+ * h[i] <- h[i] + half(sum over ranks of part32[i]) in one launch: each partial sum is stored, paired with the number
+ * of the exchange, into every peer's buffer with one 8-byte store; the peers' entries are awaited on this rank's own
+ * buffer (bounded: JG_ETIMEDOUT at the next synchronisation if a peer never arrives; JG_PEER_TIMEOUT_MS, default
+ * 20000) and added in rank order.  All ranks must issue the same sequence of peer reductions.
+ * jg_comm_peer_capacity reports the largest n (0 while the peer path is not open). */
 int jg_comm_peer_export(jg_comm* comm, void* handle64);
 int jg_comm_peer_open(jg_comm* comm, const void* handles);
 int jg_comm_peer_capacity(jg_comm* comm, uint64_t* floats);

@@ -373,3 +373,48 @@ def test_invalid_arguments_are_rejected_before_launch(dev):
     assert e.value.status == ffi.JG_EINVAL
     dev.synchronize()  # the device is still usable
     assert (y.numpy() == 0).all()
+
+
+# ------------------------------------------------------------------------------------------------ exchanges, one rank
+def test_peer_exchange_entry_points_with_a_single_rank(dev):
+    """A world of one rank exercises the peer-memory kernels' own arithmetic and argument checks without a second GPU:
+    the projection fused with its all-reduce must equal the plain residual projection bit for bit (same kernel, sum
+    over one rank), the stand-alone exchange must equal round-and-add, the key reduction is the identity."""
+    import ctypes as C
+    from denograd_b200.multi import TensorParallel
+    tp = TensorParallel(dev, 0, 1, TensorParallel.unique_id())
+    rng = np.random.default_rng(77)
+    M, N, K = 2, 1027, 2048
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float16)
+    h0 = rng.standard_normal((M, N)).astype(np.float16)
+    xt, wt = Tensor(x, device=dev), Tensor(w, device=dev)
+    h = Tensor(h0.copy(), device=dev)
+    with pytest.raises(ffi.JgError) as e:  # before the buffers are open
+        ffi.call("jg_linear_allreduce_residual", tp.handle, h.ptr, xt.ptr, wt.ptr, 0, M, N, K)
+    assert e.value.status == 22
+    assert tp.open_peers(lambda mine: [mine])
+    ffi.call("jg_linear_allreduce_residual", tp.handle, h.ptr, xt.ptr, wt.ptr, 0, M, N, K)
+    ref = Tensor(h0.copy(), device=dev)
+    dev.call("jg_linear", ref.ptr, xt.ptr, wt.ptr, 0, ref.ptr, M, N, K)
+    assert (h.numpy().view(np.uint16) == ref.numpy().view(np.uint16)).all()
+    # twice more: the exchange counter alternates the buffer parity
+    for _ in range(2):
+        ffi.call("jg_linear_allreduce_residual", tp.handle, h.ptr, xt.ptr, wt.ptr, 0, M, N, K)
+        dev.call("jg_linear", ref.ptr, xt.ptr, wt.ptr, 0, ref.ptr, M, N, K)
+    assert (h.numpy().view(np.uint16) == ref.numpy().view(np.uint16)).all()
+    with pytest.raises(ffi.JgError):  # more than 8 rows
+        ffi.call("jg_linear_allreduce_residual", tp.handle, h.ptr, xt.ptr, wt.ptr, 0, 9, N, K)
+    # stand-alone sum + residual
+    part = rng.standard_normal((5, 777)).astype(np.float32)
+    hh0 = rng.standard_normal((5, 777)).astype(np.float16)
+    pt, hh = Tensor(part, device=dev), Tensor(hh0.copy(), device=dev)
+    ffi.call("jg_peer_allreduce_residual", tp.handle, hh.ptr, pt.ptr, part.size)
+    want = (hh0.astype(np.float32) + part.astype(np.float16).astype(np.float32)).astype(np.float16)
+    assert (hh.numpy().view(np.uint16) == want.view(np.uint16)).all()
+    # keys
+    keys = rng.integers(0, 2**63, 7, dtype=np.uint64)
+    kt = Tensor(keys.copy(), device=dev)
+    ffi.call("jg_peer_allreduce_max_u64", tp.handle, kt.ptr, keys.size)
+    assert (kt.numpy() == keys).all()
+    dev.synchronize()
