@@ -4,9 +4,9 @@
 // Arithmetic is Tensor.scaled_dot_product_attention with the additive causal mask of Transformer.forward
 // (jsgrad/tensor.ts:3920-3934, softmax :2186-2214, mask jsgrad/models/llama.ts:208): fp32 scores (q.k) * 1/sqrt(hd),
 // masked above the diagonal; e = exp2((s - max) * 1/ln2) with the polynomial exp2; p = half(e * (1/sum e));
-// out = half(sum_t p_t * v_t) accumulated in fp32.  p is rounded to fp16 *after* normalisation, so the true row
-// maximum and sum must be known before the first p.v product: the context is walked three times (max, sum, p.v),
-// recomputing the cheap q.k^T on the tensor cores each time instead of keeping a [rows][context] score matrix.
+// out = half(sum_t p_t * v_t) accumulated in fp32.  p is rounded to fp16 *after* normalisation, so the row maximum and
+// sum must be known before the first p.v product: the context is walked twice (max and sum together, then p.v),
+// recomputing the cheap q.k^T on the tensor cores instead of keeping a [rows][context] score matrix.
 //
 // One CTA = 16 consecutive positions x the n_rep query heads that share one kv head (repeat_kv,
 // jsgrad/models/llama.ts:34-39) of one sequence; warp r owns head r as one m16 tile of mma.sync.m16n8k16 (fp16 in,
@@ -123,55 +123,52 @@ __global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a
 
   const float log2e = 1.4426950408889634f;
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
-  // ---- passes 1 and 2 over K: row maxima, then row sums of exp2((s - max) / ln 2)
+  // ---- pass 1 over K: row maxima and row sums of exp2((s - max) / ln 2), the sums carried relative to the running
+  //      maximum and rescaled whenever it grows (the decode kernels combine their context slices the same way)
+  load_tile(a.k_layer, 0, Kb);
+  cp_async_commit();
 #pragma unroll 1
-  for (int pass = 0; pass < 2; pass++) {
-    load_tile(a.k_layer, 0, Kb);
-    cp_async_commit();
-#pragma unroll 1
-    for (int j = 0; j < n_tiles; j++) {
-      if (j + 1 < n_tiles) {
-        load_tile(a.k_layer, j + 1, Kb + ((j + 1) & 1) * CH_KV * LD);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
-      __syncthreads();
-      float s[NS][4];
-      score_tile(Kb + (j & 1) * CH_KV * LD, j, s);
-      if (pass == 0) {
-#pragma unroll
-        for (int n = 0; n < NS; n++) {
-          m_a = fmaxf(m_a, fmaxf(s[n][0], s[n][1]));
-          m_b = fmaxf(m_b, fmaxf(s[n][2], s[n][3]));
-        }
-      } else {
-#pragma unroll
-        for (int n = 0; n < NS; n++) {
-          l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][0], m_a), log2e)));
-          l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][1], m_a), log2e)));
-          l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][2], m_b), log2e)));
-          l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][3], m_b), log2e)));
-        }
-      }
-      __syncthreads();  // the buffer read here is refilled two iterations on
-    }
-    if (pass == 0) {
-      m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 1));
-      m_a = fmaxf(m_a, __shfl_xor_sync(0xffffffffu, m_a, 2));
-      m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 1));
-      m_b = fmaxf(m_b, __shfl_xor_sync(0xffffffffu, m_b, 2));
+  for (int j = 0; j < n_tiles; j++) {
+    if (j + 1 < n_tiles) {
+      load_tile(a.k_layer, j + 1, Kb + ((j + 1) & 1) * CH_KV * LD);
+      cp_async_commit();
+      cp_async_wait<1>();
     } else {
-      l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 1));
-      l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 2));
-      l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 1));
-      l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 2));
+      cp_async_wait<0>();
     }
+    __syncthreads();
+    float s[NS][4];
+    score_tile(Kb + (j & 1) * CH_KV * LD, j, s);
+    float t_a = -INFINITY, t_b = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NS; n++) {
+      t_a = fmaxf(t_a, fmaxf(s[n][0], s[n][1]));
+      t_b = fmaxf(t_b, fmaxf(s[n][2], s[n][3]));
+    }
+    // the four lanes of a quad hold one row between them: they must agree on its maximum
+    t_a = fmaxf(t_a, __shfl_xor_sync(0xffffffffu, t_a, 1));
+    t_a = fmaxf(t_a, __shfl_xor_sync(0xffffffffu, t_a, 2));
+    t_b = fmaxf(t_b, __shfl_xor_sync(0xffffffffu, t_b, 1));
+    t_b = fmaxf(t_b, __shfl_xor_sync(0xffffffffu, t_b, 2));
+    const float n_a = fmaxf(m_a, t_a), n_b = fmaxf(m_b, t_b);
+    if (n_a != m_a) { l_a = __fmul_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(m_a, n_a), log2e))); m_a = n_a; }
+    if (n_b != m_b) { l_b = __fmul_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(m_b, n_b), log2e))); m_b = n_b; }
+#pragma unroll
+    for (int n = 0; n < NS; n++) {
+      l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][0], m_a), log2e)));
+      l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][1], m_a), log2e)));
+      l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][2], m_b), log2e)));
+      l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][3], m_b), log2e)));
+    }
+    __syncthreads();  // the buffer read here is refilled two iterations on
   }
+  l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 1));
+  l_a = __fadd_rn(l_a, __shfl_xor_sync(0xffffffffu, l_a, 2));
+  l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 1));
+  l_b = __fadd_rn(l_b, __shfl_xor_sync(0xffffffffu, l_b, 2));
   const float rl_a = __fdiv_rn(1.0f, l_a), rl_b = __fdiv_rn(1.0f, l_b);
 
-  // ---- pass 3: p = half(e * 1/sum) and out += p.v
+  // ---- pass 2: p = half(e * 1/sum) and out += p.v
   float o[ND][4];
 #pragma unroll
   for (int n = 0; n < ND; n++) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
