@@ -36,6 +36,25 @@ def test_shard_plan_covers_every_tensor_exactly_once():
         shard_plan(p, 0, 3, tied=True)
 
 
+def test_int8_shard_plan_carries_the_scales_with_the_rows():
+    """Per-output-row scales follow the rows of their weight's window: split with column-parallel weights,
+    whole (replicated) with the row-parallel wo / w2, whose windows span every output row."""
+    p = dict(TINY)
+    d = p["dim"]
+    plans = [shard_plan(p, r, 2, tied=True, int8=True) for r in range(2)]
+    for r, plan in enumerate(plans):
+        for name, sh in plan.items():
+            if not name.endswith(".weight"):
+                continue
+            sc = plan[name.replace(".weight", ".scale")]
+            assert (sc.rows, sc.cols, sc.row0, sc.col0) == (sh.rows, 1, sh.row0, 0), name
+            assert sc.seed_name == sh.seed_name.replace(".weight", ".scale")
+        assert plan["layers.0.attention.wo.scale"].rows == d and plan["layers.0.attention.wo.scale"].row0 == 0
+        assert plan["layers.0.feed_forward.w1.scale"].row0 == r * (p["hidden_dim"] // 2)
+        assert plan["output.scale"].seed_name == "tok_embeddings.scale"
+    assert not any(k.endswith(".scale") for k in shard_plan(p, 0, 2, tied=True))
+
+
 def _rank(rank: int, world: int, port: int, out_dir: str) -> None:
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     sys.path.insert(0, ROOT)
