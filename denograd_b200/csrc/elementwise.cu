@@ -296,6 +296,38 @@ JG_API int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value)
   return jg_after_launch(dev, "fill_const_f16");
 }
 
+// ------------------------------------------------------------------------------------------------ int8 -> fp16 weights
+// The dequantised matrix of Int8Linear.call (jsgrad/models/llama3.ts:35: weight.cast(half) * scale, one fp16 rounding per
+// element), materialised once so that a many-row projection can run on the fp16 tensor-core kernel — what the reference
+// graph itself does when a call has more than one row.
+__global__ void dequant_i8_f16_kernel(__half* __restrict__ dst, const int8_t* __restrict__ w, const __half* __restrict__ scale,
+                                      long long n16, int k16) {
+  pdl_launch();
+  pdl_wait();
+  for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < n16; c += (long long)gridDim.x * blockDim.x) {
+    const long long row = c / k16;
+    const uint4 raw = ld_stream_128(reinterpret_cast<const uint4*>(w) + c);
+    const __half s = scale[row];
+    const int8_t* q = reinterpret_cast<const int8_t*>(&raw);
+    __align__(16) __half o[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) o[i] = hmul1(__int2half_rn((int)q[i]), s);
+    reinterpret_cast<uint4*>(dst)[2 * c] = *reinterpret_cast<uint4*>(&o[0]);
+    reinterpret_cast<uint4*>(dst)[2 * c + 1] = *reinterpret_cast<uint4*>(&o[8]);
+  }
+}
+
+JG_API int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t N, int64_t K) {
+  JG_ENTER(dev);
+  JG_REQUIRE(N > 0 && K > 0 && K % 16 == 0, "dequant_i8_f16: bad shape N=%lld K=%lld (K must be a multiple of 16)", (long long)N, (long long)K);
+  JG_REQUIRE(jg_aligned(dst, 16) && jg_aligned(w, 16) && jg_aligned(scale, 2), "dequant_i8_f16: null or misaligned pointer");
+  const long long n16 = N * K / 16;
+  long long blocks = (n16 + 255) / 256;
+  if (blocks > (long long)dev->sm_count * 16) blocks = (long long)dev->sm_count * 16;
+  return jg_launch(dev, "dequant_i8_f16", dequant_i8_f16_kernel, dim3((unsigned)blocks), dim3(256), 0, (__half*)dst,
+                   (const int8_t*)w, (const __half*)scale, n16, (int)(K / 16));
+}
+
 // ------------------------------------------------------------------------------------------------ tensor-parallel helpers
 // h <- h + half(p): the residual add of TransformerBlock.call (jsgrad/models/llama.ts:125-126) applied to the fp32 sum
 // of a row-parallel projection after its all-reduce: one rounding of the full sum to fp16, then the fp16 add, exactly

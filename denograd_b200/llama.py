@@ -189,17 +189,19 @@ class TransformerBlock:
         self._row_parallel(f.w2, ws.ffn, ws, tp)
 
     @staticmethod
-    def _row_parallel(lin, x: Tensor, ws: "_Workspace", tp) -> None:
+    def _row_parallel(lin, x: Tensor, ws: "_Workspace", tp, w=None) -> None:
         """h <- h + lin(x).  On one device the add is the projection's epilogue; under tensor parallelism `lin` holds a
-        K-slice, so its fp32 partial sums are all-reduced first and rounded + added afterwards."""
-        if tp is None:
-            lin.call(x, residual=ws.h, out=ws.h)
-            return
+        K-slice, so its fp32 partial sums are all-reduced first and rounded + added afterwards.  `w` = (weight pointer,
+        scale pointer) replaces lin's own (a dequantised copy of int8 weights)."""
+        wp, sp = w if w is not None else (lin.weight.ptr, lin.scale_ptr)
         dev = ws.h.dev
-        if ws.B <= tp.fused_rows(lin.scale_ptr != 0):
+        if tp is None:
+            dev.call("jg_linear", ws.h.ptr, x.ptr, wp, sp, ws.h.ptr, ws.B, lin.out_features, lin.in_features)
+            return
+        if w is None and ws.B <= tp.fused_rows(lin.scale_ptr != 0):
             tp.linear_into_residual(ws.h, x, lin, ws.B)
             return
-        dev.call("jg_linear_partial", ws.part32.ptr, x.ptr, lin.weight.ptr, lin.scale_ptr, ws.B, lin.out_features, lin.in_features)
+        dev.call("jg_linear_partial", ws.part32.ptr, x.ptr, wp, sp, ws.B, lin.out_features, lin.in_features)
         tp.reduce_into_residual(ws.h, ws.part32)
 
     __call__ = call
@@ -410,14 +412,34 @@ class Transformer:
     def _max_chunk_rows(self) -> int:
         """Rows one projection call takes: 64 on the mma.sync kernel (int8 weights, or fp16 shapes off the tile grid),
         512 when every projection of a block also fits the tcgen05 kernel (out features % 128, in features % 64)."""
-        if self.output.scale_ptr != 0:
-            return 64
         a, f = self.layers[0].attention, self.layers[0].feed_forward
         shapes = [(a._wqkv.out_features, self.dim), (self.dim, a.n_heads * self.head_dim),
                   (f.w1.out_features, self.dim), (self.dim, f.w1.out_features)]
-        if all(n % 128 == 0 and k % 64 == 0 for n, k in shapes):
+        if all(n % 128 == 0 and k % 64 == 0 for n, k in shapes) and (self.output.scale_ptr == 0 or self._dequant_prefill()):
             return int(os.environ.get("JG_PREFILL_ROWS", "512"))
         return 64
+
+    @staticmethod
+    def _dequant_prefill() -> bool:
+        """int8 weights, more than 64 rows per chunk: each matrix is dequantised once per chunk into an fp16 scratch
+        (what the reference graph does for multi-row calls, jsgrad/models/llama3.ts:35) and goes through the tcgen05
+        projection; JG_W8_DEQUANT_PREFILL=0 keeps 64-row chunks on the mma.sync kernel instead."""
+        return os.environ.get("JG_W8_DEQUANT_PREFILL", "1") != "0"
+
+    def _fp16_weights(self, *lins):
+        """(pointer, 0) per projection: the weights themselves when fp16, else their dequantised copy in the scratch."""
+        if lins[0].scale_ptr == 0:
+            return [(l.weight.ptr, 0) for l in lins]
+        need = sum(l.out_features * l.in_features for l in lins)
+        if getattr(self, "_dq_scratch", None) is None or self._dq_scratch.numel() < need:
+            self._dq_scratch = Tensor.empty((need,), "float16", self.dev)
+        out, off = [], 0
+        for l in lins:
+            ptr = self._dq_scratch.ptr + 2 * off
+            self.dev.call("jg_dequant_i8_f16", ptr, l.weight.ptr, l.scale_ptr, l.out_features, l.in_features)
+            out.append((ptr, 0))
+            off += l.out_features * l.in_features
+        return out
 
     def _forward_rows(self, toks: np.ndarray, start_pos: int, last: bool) -> None:
         """One chunk of a multi-position call: rows r = s * B + b (position-major), R = B * Sc.  With `last` the
@@ -431,21 +453,28 @@ class Transformer:
         ws.seq.assign(np.tile(np.arange(B, dtype=np.int32), Sc))
         self.tok_embeddings.call(ws.tokens, out=ws.h)
         d = self.dim
+        # int8 weights and more rows than the mma.sync kernel takes: dequantised fp16 copies, made once per chunk
+        dq = R > 64 and self.output.scale_ptr != 0
+
+        def weights(*lins):
+            return self._fp16_weights(*lins) if dq else [(l.weight.ptr, l.scale_ptr) for l in lins]
+
         for layer in self.layers:
             a, f = layer.attention, layer.feed_forward
             layer.attention_norm.call(ws.h, out=ws.xn)
-            dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, a._wqkv.weight.ptr, a._wqkv.scale_ptr, 0, R, a._wqkv.out_features, d)
+            (wp, sp), = weights(a._wqkv)
+            dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, wp, sp, 0, R, a._wqkv.out_features, d)
             dev.call("jg_rope_kvwrite_rows", a._kv.handle, a._layer, ws.qkv.ptr, self.freqs_cis.ptr, self.freqs_cis.shape[0],
                      ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
             if Sc >= 8 and os.environ.get("JG_ATTN_CHUNK", "1") != "0":  # tensor-core attention over the regular chunk
                 dev.call("jg_attn_chunk", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, B, Sc, a.n_heads)
             else:
                 dev.call("jg_attn_rows", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, ws.pos.ptr, ws.seq.ptr, R, a.n_heads)
-            layer._row_parallel(a.wo, ws.attn, ws, tp)
+            layer._row_parallel(a.wo, ws.attn, ws, tp, weights(a.wo)[0] if dq else None)
             layer.ffn_norm.call(ws.h, out=ws.xn)
-            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, f.w1.weight.ptr, f.w1.scale_ptr,
-                     f.w3.weight.ptr, f.w3.scale_ptr, R, f.w1.out_features, d)
-            layer._row_parallel(f.w2, ws.ffn, ws, tp)
+            (w1p, s1p), (w3p, s3p) = weights(f.w1, f.w3)
+            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, w1p, s1p, w3p, s3p, R, f.w1.out_features, d)
+            layer._row_parallel(f.w2, ws.ffn, ws, tp, weights(f.w2)[0] if dq else None)
         if last:
             wsb = self._workspace(B)  # logits / keys / next tokens live in the batch-sized workspace, as after a step
             h_last = ws.h.view_rows(R - B, R)

@@ -254,6 +254,10 @@ int jg_residual_add_f32(jg_dev* dev, uint64_t h, uint64_t p32, int64_t n);
 int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint64_t x, uint64_t norm_w, float eps,
                                 uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset);
 
+/* Int8Linear's dequantised matrix (jsgrad/models/llama3.ts:35: weight.cast(half) * scale, fp16 [N][K]) written out
+ * once, so that a call with many rows can use the fp16 tensor-core projection on it. */
+int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t N, int64_t K);
+
 /* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the
  *      workloads replace by fixed distributions).  Counter-based, so any sub-range can be generated. */
 int jg_fill_normal_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float std);

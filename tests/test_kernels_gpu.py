@@ -418,3 +418,25 @@ def test_peer_exchange_entry_points_with_a_single_rank(dev):
     ffi.call("jg_peer_allreduce_max_u64", tp.handle, kt.ptr, keys.size)
     assert (kt.numpy() == keys).all()
     dev.synchronize()
+
+
+def test_int8_dequantised_copy_is_bit_exact(dev):
+    """jg_dequant_i8_f16 = Int8Linear's weight.cast(half) * scale, one rounding per element; a projection over the
+    copy equals the int8 projection's definition."""
+    rng = np.random.default_rng(91)
+    N, K, M = 384, 1024, 70
+    wq = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sc = (rng.uniform(0.5, 1.5, N) * synth.INT8_SCALE_BASE).astype(np.float16)
+    wt, st = Tensor(wq, device=dev), Tensor(sc, device=dev)
+    dq = Tensor.empty((N, K), "float16", dev)
+    dev.call("jg_dequant_i8_f16", dq.ptr, wt.ptr, st.ptr, N, K)
+    want = wq.astype(np.float16) * sc[:, None]
+    assert (dq.numpy().view(np.uint16) == want.view(np.uint16)).all()
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    xt = Tensor(x, device=dev)
+    y = Tensor.empty((M, N), "float16", dev)
+    dev.call("jg_linear", y.ptr, xt.ptr, dq.ptr, 0, 0, M, N, K)  # 70 rows: tcgen05 kernel on the fp16 copy
+    assert_reduction_close(y.numpy(), O.linear_w8(x, wq, sc), max_ulp=1, max_frac=0.08, what="projection over the dequantised copy")
+    with pytest.raises(ffi.JgError):
+        dev.call("jg_dequant_i8_f16", dq.ptr, wt.ptr, st.ptr, N, K + 8)
+    dev.synchronize()
