@@ -23,6 +23,10 @@ struct jg_dev {
   int* err_word;    // device word written by kernels whose bounded waits gave up (0 = fine); allocated on first use
   bool tc_pending;  // such kernels were launched since the word was last checked
   bool peer_pending;  // peer-memory reductions (comm.cu) were launched since their error word was last checked
+  // Device ranges most recently written by a kernel that produces weights (jg_dequant_i8_f16).  The projection kernels
+  // request weight tiles before they wait for their predecessor — right for parameters, wrong for such a copy.
+  uint64_t fresh_lo[4], fresh_hi[4];
+  unsigned fresh_n;
 };
 int jg_check_device_errors(jg_dev* dev);  // after a stream synchronise: JG_ETIMEDOUT if a bounded wait gave up
 
@@ -70,6 +74,19 @@ static inline int jg_after_launch(jg_dev* dev, const char* name) {
   } while (0)
 
 static inline bool jg_aligned(uint64_t p, uint64_t a) { return p != 0 && (p % a) == 0; }
+static inline void jg_mark_fresh(jg_dev* dev, uint64_t lo, uint64_t bytes) {
+  const unsigned i = dev->fresh_n++ & 3u;
+  dev->fresh_lo[i] = lo;
+  dev->fresh_hi[i] = lo + bytes;
+}
+// Whether `p` lies in memory a weight-producing kernel wrote recently: such weights must not be read ahead of the
+// dependency wait.
+static inline bool jg_is_fresh(const jg_dev* dev, const void* p) {
+  const uint64_t v = (uint64_t)(uintptr_t)p;
+  for (int i = 0; i < 4; i++)
+    if (v != 0 && v >= dev->fresh_lo[i] && v < dev->fresh_hi[i]) return true;
+  return false;
+}
 
 #ifdef __CUDACC__
 // Every kernel of the library is launched through here.  With `dev->pdl` the launch carries the programmatic

@@ -322,6 +322,7 @@ JG_API int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t sca
   JG_REQUIRE(N > 0 && K > 0 && K % 16 == 0, "dequant_i8_f16: bad shape N=%lld K=%lld (K must be a multiple of 16)", (long long)N, (long long)K);
   JG_REQUIRE(jg_aligned(dst, 16) && jg_aligned(w, 16) && jg_aligned(scale, 2), "dequant_i8_f16: null or misaligned pointer");
   const long long n16 = N * K / 16;
+  jg_mark_fresh(dev, dst, (uint64_t)N * K * 2);
   long long blocks = (n16 + 255) / 256;
   if (blocks > (long long)dev->sm_count * 16) blocks = (long long)dev->sm_count * 16;
   return jg_launch(dev, "dequant_i8_f16", dequant_i8_f16_kernel, dim3((unsigned)blocks), dim3(256), 0, (__half*)dst,

@@ -36,6 +36,7 @@ struct GemmSmallArgs {
   unsigned long long* key;  // [M] (LOGITS)
   float* y32;               // [M][N] unrounded sums (PARTIAL)
   int M, N, K, row_offset;
+  int w_late;  // the weights were written by the preceding kernel: no load before the dependency wait
 };
 
 constexpr int GS_THREADS = 256;
@@ -134,8 +135,9 @@ __global__ void __launch_bounds__(GS_THREADS, (MT <= 32 ? 2 : 1)) gemm_small_ker
       }
     }
   };
-  load_w(0, 0);
+  if (!a.w_late) load_w(0, 0);
   pdl_wait();
+  if (a.w_late) load_w(0, 0);
 
   // activation tile loader: MT rows x GS_KT halves, 16 bytes per cp.async, zero fill past M or K
   auto load_x = [&](int kt, int bufi) {
@@ -331,6 +333,7 @@ int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const voi
   a.x = (const __half*)x; a.w0 = w0; a.w1 = w1; a.s0 = (const __half*)s0; a.s1 = (const __half*)s1; a.y = (__half*)y;
   a.residual = (const __half*)residual; a.key = (unsigned long long*)key; a.M = M; a.N = N; a.K = K;
   a.row_offset = row_offset;
+  a.w_late = jg_is_fresh(dev, w0) || jg_is_fresh(dev, w1);
   if (epi == GS_PARTIAL) { a.y = nullptr; a.y32 = (float*)y; }
   return s0 ? dispatch_epi<true>(dev, epi, a) : dispatch_epi<false>(dev, epi, a);
 }

@@ -37,6 +37,7 @@ struct TcArgs {
   const __half* residual;
   int* err;  // device word: 0 = fine, otherwise the code of the first wait that gave up
   int M, N, K;
+  int w_late;  // the weights were written by the preceding kernel: no load before the dependency wait
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -169,6 +170,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   if (warp == 0 && lane == 0) {
     // ---- producer.  Weights do not depend on the preceding kernel: the first tiles are requested before the wait.
     const int pre = nk < STAGES ? nk : STAGES;
+    if (a.w_late) pdl_wait();
     for (int i = 0; i < pre; i++) {
       unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
       mbar_expect_tx(&full_bar[i], STAGE_BYTES);
@@ -386,6 +388,7 @@ int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* 
   }
   TcArgs a = {};
   a.y = (__half*)y; a.y32 = (float*)y; a.residual = (const __half*)residual; a.err = dev->err_word; a.M = M; a.N = N; a.K = K;
+  a.w_late = jg_is_fresh(dev, w0) || jg_is_fresh(dev, w1);
   switch (epi) {
     case TC_STORE: return launch_tc_rows<TC_STORE>(dev, x, w0, w1, a);
     case TC_RESIDUAL: return launch_tc_rows<TC_RESIDUAL>(dev, x, w0, w1, a);

@@ -255,7 +255,8 @@ int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint
                                 uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset);
 
 /* Int8Linear's dequantised matrix (jsgrad/models/llama3.ts:35: weight.cast(half) * scale, fp16 [N][K]) written out
- * once, so that a call with many rows can use the fp16 tensor-core projection on it. */
+ * once, so that a call with many rows can use the fp16 tensor-core projection on it.  The projection entry points
+ * notice a weight pointer inside a recently written copy and do not read it ahead of their dependency wait. */
 int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t N, int64_t K);
 
 /* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the
