@@ -334,8 +334,8 @@ def run_gpu(args) -> None:
         pf = max_over_ranks(dev.timer_stop()) / reps
         extra["prefill"] = {"tok_s": P / pf, "ms": pf * 1e3, "prompt_tokens": P, "batch": 1,
                             "tflops_per_gpu": flops_per_tok * P / pf / 1e12, "frac_of_measured_bf16_peak": flops_per_tok * P / pf / 1e12 / tf_peak,
-                            "how": ("Transformer.forward over the whole prompt in chunks of up to 512 rows: each int8 matrix dequantised once per chunk into an fp16 copy, tcgen05/TMA projections on the copy, tensor-core causal attention" if int8 else
-                                    "Transformer.forward over the whole prompt in chunks of up to 512 rows: tcgen05/TMA projections, tensor-core causal attention")}
+                            "how": ("Transformer.forward over the whole prompt in chunks of up to 2048 rows: each int8 matrix dequantised once per chunk into an fp16 copy, tcgen05/TMA projections on the copy, tensor-core causal attention" if int8 else
+                                    "Transformer.forward over the whole prompt in chunks of up to 2048 rows: tcgen05/TMA projections, tensor-core causal attention")}
         if xb:
             pb = synth.prompt_tokens(P, p["vocab_size"], batch=xb, seed=synth.PROMPT_SEED)
             llm.reset()

@@ -386,7 +386,7 @@ class Transformer:
     def forward(self, tokens, start_pos: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 0.8,
                 alpha_f: float = 0.0, alpha_p: float = 0.0) -> Tensor:
         """Transformer.forward (jsgrad/models/llama.ts:201-213), eager.  tokens: int32 [B, S] (host array or Tensor).
-        S > 1 runs in chunks of up to 512 rows (batch x positions; 64 where a projection's shape keeps it off the
+        S > 1 runs in chunks of up to 2048 rows (batch x positions; 64 where a projection's shape keeps it off the
         tcgen05 kernel or the weights are int8): one pass over the weights per chunk, every row
         attending to the cache up to its own position — what the reference's additive causal mask (:208) computes.
         Returns the greedy next token of every batch row after the last position ([B] int32)."""
@@ -411,12 +411,12 @@ class Transformer:
 
     def _max_chunk_rows(self) -> int:
         """Rows one projection call takes: 64 on the mma.sync kernel (int8 weights, or fp16 shapes off the tile grid),
-        512 when every projection of a block also fits the tcgen05 kernel (out features % 128, in features % 64)."""
+        2048 when every projection of a block also fits the tcgen05 kernel (out features % 128, in features % 64)."""
         a, f = self.layers[0].attention, self.layers[0].feed_forward
         shapes = [(a._wqkv.out_features, self.dim), (self.dim, a.n_heads * self.head_dim),
                   (f.w1.out_features, self.dim), (self.dim, f.w1.out_features)]
         if all(n % 128 == 0 and k % 64 == 0 for n, k in shapes) and (self.output.scale_ptr == 0 or self._dequant_prefill()):
-            return int(os.environ.get("JG_PREFILL_ROWS", "512"))
+            return int(os.environ.get("JG_PREFILL_ROWS", "2048"))
         return 64
 
     @staticmethod
