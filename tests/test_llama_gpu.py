@@ -249,3 +249,27 @@ def test_reduced_depth_slices_of_larger_architectures(size, quant, layers, batch
     for b in range(batch):  # compare until a tie-sensitive step of that row, if any
         n = 4 if safe[:, b].all() else int(np.argmin(safe[:, b]))
         assert (ids[b, :n] == ref_ids[b, :n]).all()
+
+
+@pytest.mark.parametrize("size,quant,batch,S", [("8B", "float16", 1, 150), ("8B", "int8", 2, 70), ("1B", "float16", 3, 40)])
+def test_full_width_one_pass_prefill_equals_token_at_a_time(size, quant, batch, S):
+    """Size-independent property at the real projection shapes (2-layer slices): a prompt fed as one multi-position
+    forward (tcgen05 projections — on dequantised copies for int8 — and chunk attention) must leave the same cache and
+    give the same next-token logits, within the fp16 tolerance, as feeding it one position at a time through the
+    decode kernels; a decode step on top of either cache must agree too."""
+    p = dict(MODEL_PARAMS[size]["args"])
+    prompt = synth.prompt_tokens(S, p["vocab_size"], batch=batch, seed=71)
+    a = make(size, quantize=quant, n_layers=2, max_context=256, max_batch=batch)
+    b = make(size, quantize=quant, n_layers=2, max_context=256, max_batch=batch)
+    ta = a.prefill(prompt).numpy()
+    la = a.model.last_logits(batch)
+    tb = b._prefill(prompt).numpy()
+    lb = b.model.last_logits(batch)
+    assert np.abs(la - lb).max() <= LOGIT_TOL
+    top2 = np.sort(lb, axis=1)[:, -2:]
+    for r in range(batch):  # same greedy pick unless the two largest logits are within the tolerance of each other
+        assert ta[r] == tb[r] or (top2[r, 1] - top2[r, 0]) <= LOGIT_TOL
+    nxt = tb.reshape(batch, 1)
+    a.model.call(nxt, S, 0.0)
+    b.model.call(nxt, S, 0.0)
+    assert np.abs(a.model.last_logits(batch) - b.model.last_logits(batch)).max() <= LOGIT_TOL
