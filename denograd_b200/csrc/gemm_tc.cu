@@ -1,4 +1,4 @@
-// Dense projection on the 5th-generation tensor cores for 9 rows and more (batched decode, prompt processing):
+// Dense projection on the 5th-generation tensor cores for 3 rows and more (batched decode, prompt processing):
 // Y[m][n] = epilogue( sum_k X[m][k] * W[n][k] ) with tcgen05.mma, the accumulator in tensor memory and both operands
 // brought into 128-byte swizzled shared memory by TMA (cp.async.bulk.tensor).
 //

@@ -1,4 +1,4 @@
-"""GPU parity of the tcgen05 / TMA projection (9 activation rows and more) against fp32 host arithmetic and, on
+"""GPU parity of the tcgen05 / TMA projection (3 activation rows and more) against fp32 host arithmetic and, on
 sampled rows, against the CPU checker's sequential fp32 accumulation."""
 import numpy as np
 import pytest
@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 256, 512), (200, 384, 1024), (512, 6144, 4096), (300, 4096, 14336),
                                    # few rows: weight streaming with split-K over a cluster (8, 2, 3, 4 CTAs per tile)
-                                   (9, 256, 512), (16, 4096, 4096), (32, 1024, 14336), (48, 6144, 4096), (64, 4096, 4096),
+                                   (3, 256, 512), (5, 2048, 2048), (9, 256, 512), (16, 4096, 4096), (32, 1024, 14336), (48, 6144, 4096), (64, 4096, 4096),
                                    (512, 4096, 4096)])
 def test_dense_projection_all_epilogues(dev, M, N, K):
     rng = np.random.default_rng(M + N + K)
