@@ -723,10 +723,14 @@ static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs,
   auto kern = MMA ? attn_decode_mma_kernel<HD, NREP> : attn_decode_fused_kernel<HD, NREP>;
   static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int slot = dev->ordinal & 7;
+  static bool wide_set[8] = {false, false, false, false, false, false, false, false};
   if (smem > smem_set[slot]) {
     JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (cs > 8) JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
     smem_set[slot] = smem;
+  }
+  if (cs > 8 && !wide_set[slot]) {  // clusters of 16 are beyond the portable size: opt in once per kernel and device
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1));
+    wide_set[slot] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(cs, a.G, B);
@@ -777,11 +781,14 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
     if (cluster != 1 && cluster != 2 && cluster != 4 && cluster != 8 && cluster != 16) cluster = 0;
   }
   // The tensor-core variant of the kernel (attention_mma.cuh) serves launches with 16 or more (row, kv head) pairs;
-  // below that the CUDA-core kernel's shorter dependency chain wins (8B, one row: 3.28 against 3.31 ms per step).
-  // JG_ATTN_MMA=0 / 1 forces one of them.
+  // below that the CUDA-core kernel in clusters of 8 is the robust choice.  (Few rows over a short context in clusters
+  // of 16 light tensor-core CTAs measured 3.23 against 3.28 ms per step on the 8B shapes but 2.04 against 1.87 on
+  // the 3B and 0.92 against 0.84 on the 1B ones.)  JG_ATTN_MMA=0 / 1 and JG_ATTN_CLUSTER force the choice.
   static int mma_env = -2;
   if (mma_env == -2) { const char* e = getenv("JG_ATTN_MMA"); mma_env = e ? (atoi(e) != 0) : -1; }
-  const int use_mma = mma_env >= 0 ? mma_env : ((long long)B * G >= 16);
+  // Eight query heads per kv head (70B shapes) fill the MMA's eight columns and overwhelm the CUDA-core kernel's
+  // registers: one row over 8200 positions takes 49 us against 95 us.
+  const int use_mma = mma_env >= 0 ? mma_env : ((long long)B * G >= 16 || n_rep >= 8);
   const size_t tile_bytes = use_mma ? (size_t)2 * AM_TK * (hd + 8) * sizeof(__half) : 0;
   // scores per CTA: rows of chunk_cap floats; the tensor-core variant pads the row so that heads fall on distinct banks
   auto cap_of = [&](int c) { const int per = (kv->max_ctx + c - 1) / c; return use_mma ? (((per + 31) & ~31) + 8) : ((per + 3) & ~3); };
