@@ -178,7 +178,8 @@ def workload_config(args, p) -> dict:
             "batch": args.batch, "prompt_tokens": args.prompt, "weights": args.quant, "layers": p["n_layers"],
             "l2": "inputs larger than L2: every step streams all weights (GBs) once, no flush needed",
             "parallelism": f"tp{args.gpus}" + ("" if args.gpus == 1 else
-                            ": heads / FFN width / vocabulary sharded, NCCL fp32 all-reduce after wo and w2")}
+                            ": heads / FFN width / vocabulary sharded; fp32 all-reduce after wo and w2 over NVLink peer memory inside "
+                            "the projection kernel (NCCL for messages above 128 KB)")}
 
 
 # ------------------------------------------------------------------------------------------------ GPU arm
