@@ -59,3 +59,27 @@ def test_two_rank_tensor_parallel_matches_the_checker(peer, quant):
     for b in range(batch):
         n = n_new if safe[:, b].all() else int(np.argmin(safe[:, b]))
         assert (res[0]["ids"][b, :n] == ref_ids[b, :n]).all()
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs 2 GPUs")
+def test_a_peer_that_never_joins_is_reported_not_waited_for():
+    """Host-made failure (a rank stops launching between steps, nothing in flight): the waiting rank's kernel gives up
+    after JG_PEER_TIMEOUT_MS, the next synchronisation returns JG_ETIMEDOUT (110) and the device remains usable."""
+    world = 2
+    with tempfile.TemporaryDirectory() as work:
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", JG_TP_PEER="1", JG_PEER_TIMEOUT_MS="1000")
+        logs = [open(os.path.join(work, f"rank{r}.log"), "w+") for r in range(world)]
+        procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(r), str(world), work,
+                                   "1", "1", "missing-peer"], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
+                 for r in range(world)]
+        for p in procs:
+            p.wait(timeout=300)
+        outs = []
+        for f in logs:
+            f.seek(0)
+            outs.append(f.read())
+            f.close()
+        assert all(p.returncode == 0 for p in procs), "\n".join(outs)[-4000:]
+        res = [np.load(os.path.join(work, f"out_{r}.npz")) for r in range(world)]
+    assert bool(res[0]["ok_first"]) and bool(res[1]["ok_first"])
+    assert int(res[0]["status"]) == 110 and bool(res[0]["usable"])

@@ -47,6 +47,9 @@ def main() -> None:
         ok = tp.open_peers(exchange_via_directory(work, rank, world))
         with open(os.path.join(work, f"peer_{rank}.txt"), "w") as f:
             f.write("1" if ok else "0")
+    if quant == "missing-peer":
+        missing_peer(dev, tp, rank, work)
+        return
     llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ids = llm.generate(prompt, n_new)
@@ -60,6 +63,33 @@ def main() -> None:
     dev.synchronize()
     # the communicator is left to process exit: NCCL waits in ncclCommDestroy for captured graphs that still hold its
     # collectives, and the models (with their graphs) are alive here
+
+
+def missing_peer(dev, tp, rank: int, work: str) -> None:
+    """Failure detection without a GPU fault: both ranks do one exchange, then rank 0 starts a second one that rank 1
+    never joins (rank 1 has nothing in flight and simply stops launching).  Rank 0's kernel gives up after the
+    configured limit and records it; the next synchronising call reports JG_ETIMEDOUT and the device stays usable."""
+    from denograd_b200 import ffi
+    from denograd_b200.device import Tensor
+    n = 4096
+    part = Tensor(np.full((n,), float(rank + 1), np.float32), device=dev)
+    h = Tensor(np.zeros((n,), np.float16), device=dev)
+    ffi.call("jg_peer_allreduce_residual", tp.handle, h.ptr, part.ptr, n)  # both ranks: 1 + 2 = 3
+    dev.synchronize()
+    ok_first = bool((h.numpy() == 3).all())
+    status, usable = 0, False
+    if rank == 0:
+        ffi.call("jg_peer_allreduce_residual", tp.handle, h.ptr, part.ptr, n)  # nobody answers
+        try:
+            dev.synchronize()
+        except ffi.JgError as e:
+            status = e.status
+        # the context is intact: an ordinary kernel still runs and synchronises cleanly
+        z = Tensor(np.ones((8,), np.float16), device=dev)
+        dev.call("jg_fill_const_f16", z.ptr, 8, 2.0)
+        dev.synchronize()
+        usable = bool((z.numpy() == 2).all())
+    np.savez(os.path.join(work, f"out_{rank}.npz"), ok_first=ok_first, status=status, usable=usable)
 
 
 if __name__ == "__main__":
