@@ -84,6 +84,33 @@ class Llama3:
         load_state_dict(self.model, weights, strict=False)
         return self
 
+    def load_weights(self, path: str) -> "Llama3":
+        """Weights from a checkpoint on disk, the tail of Llama3.load (jsgrad/models/llama3.ts:220-260) without the
+        download: read the .safetensors file (or the shards named by its .index.json), map Hugging Face names and
+        q/k row layout to the model's, narrow bf16 to fp16, cast to fp16 or quantise to int8 with the reference's
+        arithmetic, cut this rank's windows under tensor parallelism, and copy by name (non-strict)."""
+        from .state import convert_from_huggingface, load_checkpoint
+        p = self.params
+        w = load_checkpoint(path)
+        if "model.embed_tokens.weight" in w:
+            w = convert_from_huggingface(w, p["n_layers"], p["n_heads"], p["n_kv_heads"])
+        w = {k: np.asarray(v).astype(np.float16) for k, v in w.items()}
+        if self.quantize == "int8":
+            w = Int8Linear.quantize(w, quantize_embeds=self.quantize_embeds)
+        shards = self.model._shards
+        if shards:
+            if "output.weight" not in w:  # tied: the output layer is a window of the embedding table
+                w["output.weight"] = w["tok_embeddings.weight"]
+                if "tok_embeddings.scale" in w:
+                    w["output.scale"] = w["tok_embeddings.scale"]
+            for k, sh in shards.items():
+                if k not in w:
+                    continue
+                w[k] = (w[k][sh.row0:sh.row0 + sh.rows] if k.endswith(".scale")
+                        else w[k][sh.row0:sh.row0 + sh.rows, sh.col0:sh.col0 + sh.cols])
+        load_state_dict(self.model, {k: np.ascontiguousarray(v) for k, v in w.items()}, strict=False)
+        return self
+
     def load_synthetic(self, seed: int = synth.BASE_SEED) -> "Llama3":
         synth.fill_model(self.model, seed)
         return self

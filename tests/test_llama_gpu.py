@@ -273,3 +273,67 @@ def test_full_width_one_pass_prefill_equals_token_at_a_time(size, quant, batch, 
     a.model.call(nxt, S, 0.0)
     b.model.call(nxt, S, 0.0)
     assert np.abs(a.model.last_logits(batch) - b.model.last_logits(batch)).max() <= LOGIT_TOL
+
+
+@pytest.mark.parametrize("quant", ["float16", "int8"])
+def test_weights_from_a_sharded_safetensors_checkpoint(tmp_path, quant):
+    """Llama3.load_weights on a two-file Hugging Face style checkpoint (names and q/k row layout as Hugging Face stores
+    them): for fp16 every device tensor equals the source bit for bit and the forward equals the checker's on the
+    same weights; for int8 the on-load quantisation follows Int8Linear.quantize and the model generates."""
+    import json as _json
+    from denograd_b200.nn import Int8Linear
+    from denograd_b200.state import safe_save
+    from tests.util import synth_weight, tensor_shapes
+    p = dict(TINY)
+    H, G, d = p["n_heads"], p["n_kv_heads"], p["dim"]
+    shapes = tensor_shapes(p)
+
+    def to_hf_rows(w, heads):  # inverse of the loader's permutation: interleaved pairs -> two halves per head
+        o, i = w.shape
+        return w.reshape(heads, o // heads // 2, 2, i).transpose(0, 2, 1, 3).reshape(o, i)
+
+    llama, hf = {}, {}
+    hf_names = {"attention.wq": "self_attn.q_proj", "attention.wk": "self_attn.k_proj", "attention.wv": "self_attn.v_proj",
+                "attention.wo": "self_attn.o_proj", "feed_forward.w1": "mlp.gate_proj", "feed_forward.w2": "mlp.down_proj",
+                "feed_forward.w3": "mlp.up_proj"}
+    for l in range(p["n_layers"]):
+        for suffix, hn in hf_names.items():
+            w, _ = synth_weight(f"layers.{l}.{suffix}", shapes[suffix], False)
+            llama[f"layers.{l}.{suffix}.weight"] = w
+            hf[f"model.layers.{l}.{hn}.weight"] = (to_hf_rows(w, H) if suffix == "attention.wq"
+                                                    else to_hf_rows(w, G) if suffix == "attention.wk" else w)
+        hf[f"model.layers.{l}.input_layernorm.weight"] = np.ones(d, np.float16)
+        hf[f"model.layers.{l}.post_attention_layernorm.weight"] = np.ones(d, np.float16)
+    emb, _ = synth_weight("tok_embeddings", (p["vocab_size"], d), False)
+    llama["tok_embeddings.weight"] = emb
+    hf["model.embed_tokens.weight"] = emb
+    hf["model.norm.weight"] = np.ones(d, np.float16)
+    names = sorted(hf)
+    half = len(names) // 2
+    safe_save({k: hf[k] for k in names[:half]}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    safe_save({k: hf[k] for k in names[half:]}, str(tmp_path / "model-00002-of-00002.safetensors"))
+    index = tmp_path / "model.safetensors.index.json"
+    index.write_text(_json.dumps({"weight_map": {k: ("model-00001-of-00002.safetensors" if i < half else
+                                                      "model-00002-of-00002.safetensors") for i, k in enumerate(names)}}))
+    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=2, tied_output=True).load_weights(str(index))
+    sd = get_state_dict(llm.model)
+    prompt = synth.prompt_tokens(6, p["vocab_size"], batch=2, seed=17)
+    if quant == "float16":
+        for k, v in llama.items():
+            assert (sd[k].numpy().view(np.uint16) == v.view(np.uint16)).all(), k
+        ids = llm.generate(prompt, 6)
+        m = build_oracle(TINY, max_context=64, max_batch=2, int8=False, tied=True)  # the same synthetic weights
+        ref_ids, ref_logits, margins = oracle_greedy(m, prompt, 6)
+        assert np.abs(llm.model.last_logits(2) - ref_logits[-1]).max() <= LOGIT_TOL or not (ids == ref_ids).all()
+        ulp = 2.0 ** (np.floor(np.log2(np.abs(ref_logits.max(axis=2)))) - 10)
+        safe = (margins / ulp) >= 3
+        for b in range(2):
+            n = 6 if safe[:, b].all() else int(np.argmin(safe[:, b]))
+            assert (ids[b, :n] == ref_ids[b, :n]).all()
+    else:
+        want = Int8Linear.quantize(dict(llama), quantize_embeds=True)
+        for k in ("layers.0.attention.wq", "layers.1.feed_forward.w2", "tok_embeddings"):
+            assert (sd[k + ".weight"].numpy() == want[k + ".weight"]).all(), k
+            assert (sd[k + ".scale"].numpy().view(np.uint16) == want[k + ".scale"].view(np.uint16)).all(), k
+        ids = llm.generate(prompt, 4)
+        assert ids.shape == (2, 4) and (ids >= 0).all() and (ids < p["vocab_size"]).all()
