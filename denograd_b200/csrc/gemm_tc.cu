@@ -8,7 +8,8 @@
 // With few activation rows the kernel is a weight stream: every weight byte crosses HBM once, the pipeline is as deep
 // as shared memory allows, and the first weight tiles are requested before the kernel waits for its predecessor.
 // Warp roles: warp 0 issues the TMA loads (one lane), warp 1 owns tensor memory and issues the MMAs (one lane),
-// warps 2-5 read the accumulator back (tcgen05.ld, each warp its 32-lane quarter) and apply the epilogue.
+// warps 2-9 read the accumulator back (tcgen05.ld; a warp may touch the 32-lane quarter given by its id modulo 4, so
+// two warps share a quarter and split its columns) and apply the epilogue.
 //
 // Split-K over a thread-block cluster: when the output tiles alone do not fill the GPU, the CTAs of a cluster
 // (1,1,ks) share one output tile, each accumulating a slice of K; ranks > 0 then write their accumulators into rank 0's
@@ -28,7 +29,7 @@ enum { TC_STORE = 0, TC_RESIDUAL = 1, TC_SWIGLU = 2, TC_PARTIAL = 4 };
 
 constexpr int TC_BM = 128;  // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;   // k per stage: 64 halves = one 128-byte swizzle row
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per 32-lane quarter of tensor memory)
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;  // polls of one mbarrier phase before giving up (~ tens of ms)
 
 struct TcArgs {
@@ -218,6 +219,10 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
 
   // warp (id % 4) may touch tensor-memory lanes [32 * (id % 4), +32); lane l of it is weight row feat0 + 32q + l
   const int q = warp & 3, row = q * 32 + lane;
+  // the two warps of a quarter split the accumulator columns (activation rows) between them
+  const int chalf = (warp - 2) >> 2;
+  const int tn_lo = TN >= 32 ? chalf * (TN / 2) : 0, tn_hi = TN >= 32 ? tn_lo + TN / 2 : (chalf == 0 ? TN : 0);
+  const int nc_lo = NCOL >= 32 ? chalf * (NCOL / 2) : 0, nc_hi = NCOL >= 32 ? nc_lo + NCOL / 2 : (chalf == 0 ? NCOL : 0);
   const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
   float* red = reinterpret_cast<float*>(tiles);  // rank 0: [ks-1][NCOL][128] partial accumulators of the peers
   if (ks > 1) {
@@ -225,7 +230,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
     if (rank > 0 && warp >= 2 && acc_ok) {
       const uint32_t dst0 = map_to_rank(smem_u32(red + ((size_t)(rank - 1) * NCOL) * TC_BM + row), 0);
 #pragma unroll 1
-      for (int c0 = 0; c0 < NCOL; c0 += 16) {
+      for (int c0 = nc_lo; c0 < nc_hi; c0 += 16) {
         float r0[16];
         tmem_ld16(t_lane + c0, r0);
 #pragma unroll
@@ -237,7 +242,7 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   if (rank == 0 && warp >= 2 && acc_ok) {
     const int feat = feat0 + row;
 #pragma unroll 1
-    for (int c0 = 0; c0 < TN; c0 += 16) {
+    for (int c0 = tn_lo; c0 < tn_hi; c0 += 16) {
       float r0[16], r1[16];
       tmem_ld16(t_lane + c0, r0);
       if (NW == 2) tmem_ld16(t_lane + TN + c0, r1);
