@@ -29,7 +29,8 @@ enum { TC_STORE = 0, TC_RESIDUAL = 1, TC_SWIGLU = 2, TC_PARTIAL = 4 };
 
 constexpr int TC_BM = 128;  // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;   // k per stage: 64 halves = one 128-byte swizzle row
-constexpr int TC_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per 32-lane quarter of tensor memory)
+// Threads of a CTA: warp 0 TMA, warp 1 MMA, then EPW epilogue warps for each 32-lane quarter of tensor memory.
+constexpr int tc_threads(int epw) { return 64 + 128 * epw; }
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;  // polls of one mbarrier phase before giving up (~ tens of ms)
 
 struct TcArgs {
@@ -123,6 +124,11 @@ template <int TN, int EPI>
 struct TcCfg {
   static constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
   static constexpr int NCOL = NW * TN;                 // accumulator columns
+  // epilogue warps per tensor-memory quarter: wide tiles leave each of them 64 columns (measured at 512 rows: 12.1 ->
+  // 11.8 ms per prefill against two warps), narrow ones are over before more warps would pay (batch 32: 6.92k tok/s
+  // with two, 6.84k with four)
+  static constexpr int EPW = TN >= 128 ? 4 : 2;
+  static constexpr int THREADS = tc_threads(EPW);
   static constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
   static constexpr uint32_t B_BYTES = TN * TC_BK * 2;
   static constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
@@ -135,7 +141,7 @@ struct TcCfg {
 };
 
 template <int TN, int EPI>
-__global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
+__global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
                                                              const __grid_constant__ CUtensorMap tm_w1,
                                                              const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
   using Cfg = TcCfg<TN, EPI>;
@@ -220,9 +226,11 @@ __global__ void __launch_bounds__(TC_THREADS) gemm_tc_kernel(const __grid_consta
   // warp (id % 4) may touch tensor-memory lanes [32 * (id % 4), +32); lane l of it is weight row feat0 + 32q + l
   const int q = warp & 3, row = q * 32 + lane;
   // the two warps of a quarter split the accumulator columns (activation rows) between them
-  const int chalf = (warp - 2) >> 2;
-  const int tn_lo = TN >= 32 ? chalf * (TN / 2) : 0, tn_hi = TN >= 32 ? tn_lo + TN / 2 : (chalf == 0 ? TN : 0);
-  const int nc_lo = NCOL >= 32 ? chalf * (NCOL / 2) : 0, nc_hi = NCOL >= 32 ? nc_lo + NCOL / 2 : (chalf == 0 ? NCOL : 0);
+  const int part = (warp - 2) >> 2;
+  constexpr int TN_PER = (TN / Cfg::EPW) >= 16 ? (TN / Cfg::EPW) : 16;
+  constexpr int NC_PER = (NCOL / Cfg::EPW) >= 16 ? (NCOL / Cfg::EPW) : 16;
+  const int tn_lo = part * TN_PER, tn_hi = min(TN, tn_lo + TN_PER);
+  const int nc_lo = part * NC_PER, nc_hi = min(NCOL, nc_lo + NC_PER);
   const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
   float* red = reinterpret_cast<float*>(tiles);  // rank 0: [ks-1][NCOL][128] partial accumulators of the peers
   if (ks > 1) {
@@ -343,7 +351,7 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
   dev->tc_pending = true;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((a.M + TN - 1) / TN, a.N / TC_BM, ks);  // activation tiles fastest: CTAs sharing weights run together
-  cfg.blockDim = dim3(TC_THREADS);
+  cfg.blockDim = dim3(Cfg::THREADS);
   cfg.dynamicSmemBytes = Cfg::SMEM;
   cfg.stream = dev->stream;
   cudaLaunchAttribute attr[2];

@@ -459,12 +459,6 @@ class Transformer:
         def weights(*lins):
             return self._fp16_weights(*lins) if dq else [(l.weight.ptr, l.scale_ptr) for l in lins]
 
-        # from 256 rows on, gate and up run as two single-matrix projections plus an elementwise SiLU*mul (measured:
-        # 512 rows 14.4 -> 12.6 ms per prefill, 2048 rows 52.4 -> 46.3 ms; the two-matrix kernel has 3 stages of 64 KB)
-        split_ffn = R >= int(os.environ.get("JG_SPLIT_FFN_ROWS", "256")) and (dq or self.output.scale_ptr == 0)
-        if split_ffn and getattr(ws, "gate", None) is None:
-            ws.gate = Tensor.empty((R, self.hidden_dim), "float16", dev)
-            ws.up = Tensor.empty((R, self.hidden_dim), "float16", dev)
         for layer in self.layers:
             a, f = layer.attention, layer.feed_forward
             layer.attention_norm.call(ws.h, out=ws.xn)
@@ -479,15 +473,7 @@ class Transformer:
             layer._row_parallel(a.wo, ws.attn, ws, tp, weights(a.wo)[0] if dq else None)
             layer.ffn_norm.call(ws.h, out=ws.xn)
             (w1p, s1p), (w3p, s3p) = weights(f.w1, f.w3)
-            if split_ffn:
-                # two single-matrix projections and an elementwise SiLU*mul: same arithmetic as the fused epilogue
-                # (both round the projections to fp16 first), but the single-matrix tcgen05 pipeline is deeper
-                fh = f.w1.out_features
-                dev.call("jg_linear", ws.gate.ptr, ws.xn.ptr, w1p, s1p, 0, R, fh, d)
-                dev.call("jg_linear", ws.up.ptr, ws.xn.ptr, w3p, s3p, 0, R, fh, d)
-                dev.call("jg_swiglu", ws.ffn.ptr, ws.gate.ptr, ws.up.ptr, R * fh)
-            else:
-                dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, w1p, s1p, w3p, s3p, R, f.w1.out_features, d)
+            dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, layer.ffn_norm.eps, w1p, s1p, w3p, s3p, R, f.w1.out_features, d)
             layer._row_parallel(f.w2, ws.ffn, ws, tp, weights(f.w2)[0] if dq else None)
         if last:
             wsb = self._workspace(B)  # logits / keys / next tokens live in the batch-sized workspace, as after a step
