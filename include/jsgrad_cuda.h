@@ -106,9 +106,11 @@ int jg_rmsnorm(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, int32_t rows, in
 
 /* Linear.call / Int8Linear.call: jsgrad/nn/index.ts:411, jsgrad/models/llama3.ts:35; `residual` (0 = none) is
  * the `x.add(...)` of TransformerBlock.call, jsgrad/models/llama.ts:125-126, fused as an epilogue.
- * Row counts: M <= 8 streams the weights through the CUDA cores; 8 < M <= 64 through the tensor cores (fp16 weights
- * only, and the fused-norm entry points then want norm_w = 0 with rows normalised by jg_rmsnorm first); larger M is
- * JG_ENOTSUP (split the rows into chunks of 64). */
+ * Row counts: 1-2 rows of fp16 weights stream through the CUDA cores (norm fused where the entry point has one).
+ * From 3 rows on, and for int8 weights at every row count, the tensor cores take over and the fused-norm entry
+ * points want norm_w = 0 with rows normalised by jg_rmsnorm first: fp16 weights with N % 128 == 0 and K % 64 == 0 on
+ * the tcgen05 kernel (any M), other fp16 shapes and int8 weights on the mma.sync kernel (M <= 64; more rows are
+ * JG_ENOTSUP: split them into chunks of 64, or for int8 use jg_dequant_i8_f16 and project over the fp16 copy). */
 int jg_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, uint64_t scale, uint64_t residual, int32_t M,
               int32_t N, int32_t K);
 
