@@ -1,4 +1,5 @@
-// Weight-streaming projection for 9..64 activation rows (batched decode, short prefill chunks):
+// Weight-streaming projection for up to 64 activation rows (batched decode, short prefill chunks) — int8 weights, fp16
+// shapes off the tcgen05 tile grid, and the logits with their argmax keys:
 //   y[m][n] = epilogue( sum_k x[m][k] * W[n][k] ),  fp16 operands, fp32 accumulation on the tensor cores.
 //
 // At these row counts the projection is still bound by reading W once from HBM, but the multiply-accumulate work no

@@ -159,7 +159,7 @@ class TransformerBlock:
         d = ws.h.shape[-1]
         wqkv = a._wqkv
         # from 3 rows on (fp16 weights) normalise into ws.xn and project on the tensor cores; the fused-norm kernels
-        # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: up to 8 rows)
+        # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: never)
         big = _norm_first(B, wqkv.scale_ptr != 0)
         if big:
             self.attention_norm.call(ws.h, out=ws.xn)
