@@ -38,6 +38,7 @@ struct AttnArgs {
   unsigned int* tickets;
   __half* out;  // [B][H*hd]
   int qkv_stride, H, G, page, page_shift, max_pages_per_seq, n_split, max_ctx;
+  int n_pages;  // pages in a caller-owned pool whose block table is checked entry by entry; 0 = validated on the host
   float scale;
 };
 
@@ -89,7 +90,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_scores_kernel(const AttnArgs
 #pragma unroll
     for (int u = 0; u < U; u++) {
       const int t = tb + u * ATT_WARPS * RPW;
-      kv[u] = (t < t1) ? ld_128(kv_row(a.k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8)
+      kv[u] = (t < t1) ? ld_kv_128(kv_row_checked(a.k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD, a.n_pages), sub * 8)
                        : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_pv_kernel(const AttnArgs a) 
       for (int u = 0; u < U; u++) {
         const int t = tb + u * ATT_WARPS * RPW;
         const bool ok = t < t1;
-        vv[u] = ok ? ld_128(kv_row(a.v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8)
+        vv[u] = ok ? ld_kv_128(kv_row_checked(a.v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD, a.n_pages), sub * 8)
                    : make_uint4(0, 0, 0, 0);
         pr[u] = (ok && sub < NREP) ? srow[(size_t)my_r * a.max_ctx + t] : -INFINITY;
       }
@@ -270,7 +271,7 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
                                     const int32_t* __restrict__ pos, const int32_t* __restrict__ block_table,
                                     __half* __restrict__ k_layer, __half* __restrict__ v_layer, int B, int H, int G,
                                     int hd, int page, int page_shift, int max_pages_per_seq, int table_rows,
-                                    const int32_t* __restrict__ seq) {
+                                    const int32_t* __restrict__ seq, int n_seq) {
   pdl_launch();
   pdl_wait();
   const int per_head = hd / 8;
@@ -282,6 +283,8 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
     const int b = (int)(it / ((long long)per_head * heads));
     const int p = pos[b];
     if (p < 0 || p >= max_pages_per_seq * page || p >= table_rows) continue;  // out-of-range position: leave the row untouched
+    const int sq = seq ? seq[b] : b;
+    if ((unsigned)sq >= (unsigned)n_seq) continue;  // row mapped to a sequence the block table does not have: skipped too
     __half* src = qkv + ((size_t)b * heads + h) * hd + (size_t)c * 8;
     uint4 raw = *reinterpret_cast<uint4*>(src);
     if (h < H + G) {
@@ -302,7 +305,7 @@ __global__ void rope_kvwrite_kernel(__half* __restrict__ qkv, const __half* __re
     } else {
       const int g = (h < H + G) ? (h - H) : (h - H - G);
       __half* layer = (h < H + G) ? k_layer : v_layer;
-      const int pg = block_table[(size_t)(seq ? seq[b] : b) * max_pages_per_seq + (p >> page_shift)];
+      const int pg = block_table[(size_t)sq * max_pages_per_seq + (p >> page_shift)];
       const int slot = p & (page - 1);
       *reinterpret_cast<uint4*>(layer + (((size_t)pg * G + g) * page + slot) * hd + (size_t)c * 8) = raw;
     }
@@ -330,6 +333,7 @@ struct AttnFusedArgs {
   const int32_t* seq;  // row -> sequence (block-table row); null = identity.  Several rows may belong to one sequence
   __half* out;
   int table_rows, qkv_stride, H, G, page, page_shift, max_pages_per_seq, max_ctx, chunk_cap;
+  int n_seq;  // rows of the block table: a row whose seq[] entry lies outside [0, n_seq) is skipped (output untouched)
   int pre;  // 1: Q is already rotated and K/V are already in the cache (multi-position calls): attend only
   float scale;
 };
@@ -366,11 +370,13 @@ __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const At
   pdl_launch();
   pdl_wait();
 
+  const int sq = a.seq ? a.seq[b] : b;
+  if ((unsigned)sq >= (unsigned)a.n_seq) return;  // the same for every CTA of the cluster (they share b)
   const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);
   const int p = T - 1;  // position of the new token
   const int chunk = min((T + CS - 1) / CS, a.chunk_cap);  // the host sizes chunk_cap so that CS * chunk_cap >= max_ctx
   const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
-  const int32_t* bt_row = a.block_table + (size_t)(a.seq ? a.seq[b] : b) * a.max_pages_per_seq;
+  const int32_t* bt_row = a.block_table + (size_t)sq * a.max_pages_per_seq;
   const __half* xrow = a.qkv + (size_t)b * a.qkv_stride;
   const uint4 traw = a.pre ? make_uint4(0, 0, 0, 0)
                            : ld_128(a.table + ((size_t)min(p, a.table_rows - 1) * (HD / 2) + (size_t)sub * 4) * 2);
@@ -679,7 +685,7 @@ static int rope_kvwrite_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_
   return jg_launch(dev, "rope_kvwrite", rope_kvwrite_kernel, dim3(blocks), dim3(128), 0, (__half*)qkv, (const __half*)table,
                    (const int32_t*)pos, (const int32_t*)kv->block_table, kv->k_pool + kv->layer_elems * layer,
                    kv->v_pool + kv->layer_elems * layer, B, H, G, hd, kv->d.page_size, ilog2(kv->d.page_size),
-                   kv->d.max_pages_per_seq, table_rows, (const int32_t*)seq);
+                   kv->d.max_pages_per_seq, table_rows, (const int32_t*)seq, kv->d.max_batch);
 }
 
 template <int HD, int NREP>
@@ -812,7 +818,7 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   a.qkv = (const __half*)qkv; a.table = (const __half*)table; a.table_rows = table_rows;
   a.k_layer = kv->k_pool + kv->layer_elems * layer; a.v_layer = kv->v_pool + kv->layer_elems * layer;
   a.block_table = kv->block_table; a.pos = (const int32_t*)pos; a.out = (__half*)out;
-  a.seq = (const int32_t*)seq; a.pre = pre;
+  a.seq = (const int32_t*)seq; a.pre = pre; a.n_seq = kv->d.max_batch;
   a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
   a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap;
   a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));
@@ -844,16 +850,19 @@ static inline size_t align_up_256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 JG_API int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint64_t k_layer, uint64_t v_layer,
                                   uint64_t block_table, uint64_t pos, int32_t B, int32_t H, int32_t G, int32_t head_dim,
-                                  int32_t page_size, int32_t max_pages_per_seq, int32_t n_split) {
+                                  int32_t page_size, int32_t max_pages_per_seq, int32_t n_split, int32_t n_pages) {
   JG_ENTER(dev);
   JG_REQUIRE(B > 0 && H > 0 && G > 0 && H % G == 0 && max_pages_per_seq > 0, "attn_decode_noalloc: bad shape B=%d H=%d G=%d pages=%d", B, H, G, max_pages_per_seq);
+  JG_REQUIRE(n_pages > 0, "attn_decode_noalloc: the pools hold n_pages=%d pages", n_pages);
   JG_REQUIRE(head_dim == 64 || head_dim == 128, "attn_decode_noalloc: head_dim %d not supported (64 or 128)", head_dim);
   JG_REQUIRE(page_size == 16 || page_size == 32 || page_size == 64, "attn_decode_noalloc: page_size %d not in {16,32,64}", page_size);
   JG_REQUIRE(n_split >= 1 && n_split <= 64, "attn_decode_noalloc: n_split %d outside [1,64]", n_split);
   JG_REQUIRE(jg_aligned(out, 16) && jg_aligned(qkv, 16) && jg_aligned(k_layer, 16) && jg_aligned(v_layer, 16) &&
                  jg_aligned(block_table, 4) && jg_aligned(pos, 4), "attn_decode_noalloc: null or misaligned pointer");
   JG_REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64, "attn_decode_noalloc: device ordinal %d out of range", dev->ordinal);
-  const int n_rep = H / G, max_ctx = max_pages_per_seq * page_size;
+  const long long max_ctx64 = (long long)max_pages_per_seq * page_size;
+  JG_REQUIRE(max_ctx64 <= 0x7fffffffLL, "attn_decode_noalloc: %d pages of %d positions per sequence overflow the context length", max_pages_per_seq, page_size);
+  const int n_rep = H / G, max_ctx = (int)max_ctx64;
   // carve the fixed array: scores | (max, sum) per split | partial outputs per split | tickets
   const size_t sc_bytes = align_up_256((size_t)B * H * max_ctx * sizeof(float));
   const size_t ml_bytes = align_up_256((size_t)B * H * n_split * 2 * sizeof(float));
@@ -867,6 +876,8 @@ JG_API int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint6
   }
   // first call on this device: resolve the device address of the array (dev is current: JG_ENTER set it)
   if (g_noalloc_scratch_addr[dev->ordinal] == nullptr) {
+    JG_REQUIRE(!dev->capturing, "attn_decode_noalloc: the first call on a device looks up the scratch array's address and "
+               "must come before any graph capture");
     void* p = nullptr;
     JG_CUDA(cudaGetSymbolAddress(&p, g_noalloc_scratch));
     JG_REQUIRE(p != nullptr, "attn_decode_noalloc: the scratch symbol has no address on device %d", dev->ordinal);
@@ -886,6 +897,7 @@ JG_API int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint6
   a.out = (__half*)out;
   a.qkv_stride = (H + 2 * G) * head_dim; a.H = H; a.G = G; a.page = page_size; a.page_shift = ilog2(page_size);
   a.max_pages_per_seq = max_pages_per_seq; a.n_split = n_split; a.max_ctx = max_ctx;
+  a.n_pages = n_pages;  // the block table is the caller's and unvalidated: entries outside the pool read as zero rows
   a.scale = (float)(1.0 / (double)(float)sqrt((double)head_dim));
   // the array keeps whatever the last call (of any shape) left in it; only the tickets must start at zero
   JG_CUDA(cudaMemsetAsync(a.tickets, 0, tk_bytes, dev->stream));

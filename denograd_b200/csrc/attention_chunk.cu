@@ -30,6 +30,7 @@ struct ChunkArgs {
   const int32_t* seq;  // [R] row -> block-table row, or null (row b of the chunk is sequence b)
   __half* out;         // [R][H * hd]
   int qkv_stride, H, G, B, Sc, page, page_shift, max_pages_per_seq, max_ctx;
+  int n_seq;  // rows of the block table: a sequence whose seq[] entry lies outside [0, n_seq) is skipped
   float scale;
 };
 
@@ -68,13 +69,15 @@ __global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a
   pdl_launch();
   pdl_wait();
 
+  const int sq = a.seq ? a.seq[b] : b;
+  if ((unsigned)sq >= (unsigned)a.n_seq) return;
   const int pos0 = a.pos[b];
   const int written = min(pos0 + a.Sc, a.max_ctx);           // the cache holds positions [0, written) of this sequence
   const int s0 = qt * CH_Q;                                  // first chunk position of this CTA
   const int p_lo = pos0 + s0;                                // its absolute position
   const int T = min(p_lo + CH_Q, written);                   // positions any row of the tile may attend to
   const int n_tiles = (T + CH_KV - 1) / CH_KV;
-  const int32_t* bt_row = a.block_table + (size_t)(a.seq ? a.seq[b] : b) * a.max_pages_per_seq;
+  const int32_t* bt_row = a.block_table + (size_t)sq * a.max_pages_per_seq;
 
   // ---- query fragments of head g*NREP + r: rows qr and qr+8 of the tile (clamped to the chunk)
   uint32_t qf[KS][4];
@@ -264,7 +267,7 @@ JG_API int jg_attn_chunk(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t ou
   a.pos = (const int32_t*)pos; a.seq = (const int32_t*)seq; a.out = (__half*)out;
   a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.B = B; a.Sc = Sc;
   a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
-  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx;
+  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.n_seq = kv->d.max_batch;
   a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));  // as the reference folds it (jsgrad/tensor.ts:3923)
 #define JG_CH_CASE(HD_, NR_) if (hd == HD_ && n_rep == NR_) return launch_chunk<HD_, NR_>(dev, a);
   JG_CH_CASE(64, 1) JG_CH_CASE(64, 2) JG_CH_CASE(64, 3) JG_CH_CASE(64, 4) JG_CH_CASE(64, 8)

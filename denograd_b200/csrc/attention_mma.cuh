@@ -56,13 +56,15 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
   pdl_launch();
   pdl_wait();
 
+  const int sq = a.seq ? a.seq[b] : b;
+  if ((unsigned)sq >= (unsigned)a.n_seq) return;  // no such block-table row: skipped by every CTA of the cluster alike
   const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);
   const int p = T - 1;  // position of the new token
   const int chunk = min((T + CS - 1) / CS, a.chunk_cap);
   const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
   const int n_local = max(t1 - t0, 0);
   const int n_tiles = (n_local + AM_TK - 1) / AM_TK;
-  const int32_t* bt_row = a.block_table + (size_t)(a.seq ? a.seq[b] : b) * a.max_pages_per_seq;
+  const int32_t* bt_row = a.block_table + (size_t)sq * a.max_pages_per_seq;
   const __half* xrow = a.qkv + (size_t)b * a.qkv_stride;
   const __half* trow = a.table + (size_t)min(p, a.table_rows - 1) * HD;  // [hd/2][2] of position p
 

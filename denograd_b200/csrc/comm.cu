@@ -22,6 +22,8 @@ typedef int (*fn_comm_init_rank)(nccl_comm_t*, int, nccl_unique_id, int);
 typedef int (*fn_comm_destroy)(nccl_comm_t);
 typedef int (*fn_all_reduce)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t);
 typedef const char* (*fn_get_error_string)(int);
+typedef int (*fn_comm_init_all)(nccl_comm_t*, int, const int*);
+typedef int (*fn_group)(void);
 
 static struct {
   void* handle;
@@ -30,12 +32,15 @@ static struct {
   fn_comm_destroy comm_destroy;
   fn_all_reduce all_reduce;
   fn_get_error_string get_error_string;
+  fn_comm_init_all comm_init_all;  // optional: single-process communicators
+  fn_group group_start, group_end;
 } g_nccl = {};
 
 struct jg_comm {
   jg_dev* dev;
   nccl_comm_t comm;
   int rank, world;
+  bool in_process;  // made by jg_comm_init_all: the peers' buffers are addressed directly, not through IPC handles
 };
 
 static int nccl_open(const char* path) {
@@ -50,6 +55,9 @@ static int nccl_open(const char* path) {
   g_nccl.comm_destroy = (fn_comm_destroy)dlsym(h, "ncclCommDestroy");
   g_nccl.all_reduce = (fn_all_reduce)dlsym(h, "ncclAllReduce");
   g_nccl.get_error_string = (fn_get_error_string)dlsym(h, "ncclGetErrorString");
+  g_nccl.comm_init_all = (fn_comm_init_all)dlsym(h, "ncclCommInitAll");
+  g_nccl.group_start = (fn_group)dlsym(h, "ncclGroupStart");
+  g_nccl.group_end = (fn_group)dlsym(h, "ncclGroupEnd");
   if (!g_nccl.get_unique_id || !g_nccl.comm_init_rank || !g_nccl.comm_destroy || !g_nccl.all_reduce || !g_nccl.get_error_string) {
     jg_set_error("the NCCL library lacks one of ncclGetUniqueId / ncclCommInitRank / ncclCommDestroy / ncclAllReduce");
     dlclose(h);
@@ -95,12 +103,15 @@ JG_API int jg_comm_init(jg_dev* dev, const char* nccl_path, const void* id128, i
 
 static void comm_destroy_now(void* p) { jg_comm_destroy((jg_comm*)p); }
 
+static void peer_release(jg_comm* comm);
+
 JG_API int jg_comm_destroy(jg_comm* comm) {
   if (!comm) return JG_OK;
   if (g_jg_capturing > 0) { jg_defer(comm_destroy_now, comm); return JG_OK; }
   cudaSetDevice(comm->dev->ordinal);
   cudaStreamSynchronize(comm->dev->stream);
-  if (g_nccl.comm_destroy) g_nccl.comm_destroy(comm->comm);
+  peer_release(comm);  // unmap the peers' exchange buffers, free this rank's own
+  if (g_nccl.comm_destroy && comm->comm) g_nccl.comm_destroy(comm->comm);
   delete comm;
   return JG_OK;
 }
@@ -111,6 +122,7 @@ JG_API int jg_allreduce_sum_f32(jg_comm* comm, uint64_t buf, uint64_t count) {
   JG_ENTER(comm->dev);
   JG_REQUIRE(count > 0 && jg_aligned(buf, 4), "allreduce_sum_f32: bad buffer");
   if (comm->world == 1) return JG_OK;
+  JG_REQUIRE(comm->comm != nullptr, "allreduce_sum_f32: this communicator has no NCCL side");
   int n = g_nccl.all_reduce((const void*)buf, (void*)buf, (size_t)count, NCCL_FLOAT32, NCCL_SUM, comm->comm, comm->dev->stream);
   if (n != 0) return nccl_fail(n, "ncclAllReduce(sum, f32)");
   return JG_OK;
@@ -123,6 +135,7 @@ JG_API int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count) {
   JG_ENTER(comm->dev);
   JG_REQUIRE(count > 0 && jg_aligned(buf, 8), "allreduce_max_u64: bad buffer");
   if (comm->world == 1) return JG_OK;
+  JG_REQUIRE(comm->comm != nullptr, "allreduce_max_u64: this communicator has no NCCL side");
   int n = g_nccl.all_reduce((const void*)buf, (void*)buf, (size_t)count, NCCL_UINT64, NCCL_MAX, comm->comm, comm->dev->stream);
   if (n != 0) return nccl_fail(n, "ncclAllReduce(max, u64)");
   return JG_OK;
@@ -149,8 +162,26 @@ struct jg_peer {
   int* err;                               // device word: 0 = fine, 1 = a wait for a peer's flag ran out
   unsigned long long timeout_ns;
   bool open;
+  bool ipc[PEER_MAX_WORLD];               // mapped[r] came from cudaIpcOpenMemHandle and must be closed
 };
 static jg_peer g_peer[64] = {};  // by device ordinal
+
+// Undo jg_comm_peer_export / jg_comm_peer_open for this communicator's device: close the IPC mappings, free the
+// buffer and the counters, and leave the slot ready for a later communicator.  The stream is idle (caller synchronised).
+static void peer_release(jg_comm* comm) {
+  const int o = comm->dev->ordinal;
+  if (o < 0 || o >= 64) return;
+  jg_peer& p = g_peer[o];
+  for (int r = 0; r < PEER_MAX_WORLD; r++) {
+    if (p.mapped[r] != nullptr && p.ipc[r]) cudaIpcCloseMemHandle(p.mapped[r]);
+    p.mapped[r] = nullptr;
+    p.ipc[r] = false;
+  }
+  if (p.local) cudaFree(p.local);
+  if (p.epoch) cudaFree(p.epoch);
+  cudaGetLastError();
+  p = jg_peer{};
+}
 
 // h <- h + half(sum over ranks of part): flag-in-data exchange, every thread carries its own elements through it.
 __global__ void __launch_bounds__(256) peer_sum_residual_kernel(const PeerArgs a) {
@@ -229,11 +260,96 @@ __global__ void __launch_bounds__(256) peer_max_kernel(const PeerArgs a) {
   if (tid == 0) { __threadfence(); a.epoch[0] = epoch; }  // single CTA
 }
 
+// h <- h + half(sum over ranks of partial), two-shot: for messages too large for every rank to send everything to
+// everybody.  Rank r owns the r-th slice of the n values.  Each CTA (i) tells the same CTA of every peer that this
+// rank's partial sums are complete — they were written by the preceding kernel, into the region of the exchange
+// buffer the peers can read — and waits (bounded) for the same word from them; (ii) reads its part of this rank's
+// slice from every rank's partial region with plain peer loads, adds them in rank order, rounds once, adds the
+// residual, stores the new h and sends it to every peer as flag-in-data entries of (two halves, exchange number);
+// (iii) collects the other slices from the entries the peers sent.  One NVLink round trip for the reads plus one
+// crossing for the results, n * 4 / world bytes in and n * 2 bytes out per rank.
+__global__ void __launch_bounds__(256) peer_sum2_residual_kernel(const PeerArgs a) {
+  __shared__ int s_fail;
+  const int tid = threadIdx.x, cta = blockIdx.x, nct = gridDim.x;
+  pdl_launch();
+  pdl_wait();
+  const uint32_t epoch = a.epoch[0] + 1;
+  const int parity = (int)(epoch & 1u);
+  const int rank = a.rank, world = a.world;
+  if (tid == 0) s_fail = 0;
+  __syncthreads();
+  // (i) hand-shake with CTA `cta` of every peer
+  if (tid < world && tid != rank) {
+    uint32_t* f = peer_flag(a.buf[tid], parity, cta, rank);
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(epoch) : "memory");
+    const uint32_t* mine = peer_flag(a.buf[rank], parity, cta, tid);
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+      uint32_t v;
+      asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+      if ((int32_t)(v - epoch) >= 0) break;
+      if (global_ns() - t0 > a.timeout_ns) { s_fail = 1; atomicCAS(a.err, 0, 1); break; }
+    }
+    asm volatile("fence.acquire.sys;" ::: "memory");
+  }
+  __syncthreads();
+  const long long quads = a.n / 4;                                  // 4 values = one 16-byte peer load, two result entries
+  const long long per_rank = (quads + world - 1) / world;           // slice of a rank, in quads
+  const long long per_cta = (per_rank + nct - 1) / nct;             // part of a slice handled by one CTA
+  if (!s_fail) {
+    // (ii) this rank's slice
+    const long long q_lo = rank * per_rank + (long long)cta * per_cta;
+    const long long q_hi = min(min(q_lo + per_cta, (long long)(rank + 1) * per_rank), quads);
+    for (long long q = q_lo + tid; q < q_hi; q += blockDim.x) {
+      float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < world; r++) {  // rank order on every rank
+        const float4* src = reinterpret_cast<const float4*>(peer_partial(a.buf[r])) + q;
+        float4 v;
+        asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(src) : "memory");
+        sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y); sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+      }
+      uint2 raw = reinterpret_cast<const uint2*>(a.h)[q];
+      __half* hh = reinterpret_cast<__half*>(&raw);
+      hh[0] = hadd1(hh[0], __float2half_rn(sum.x)); hh[1] = hadd1(hh[1], __float2half_rn(sum.y));
+      hh[2] = hadd1(hh[2], __float2half_rn(sum.z)); hh[3] = hadd1(hh[3], __float2half_rn(sum.w));
+      reinterpret_cast<uint2*>(a.h)[q] = raw;
+      for (int p = 0; p < world; p++) {
+        if (p == rank) continue;
+        uint2* dst = peer_result(a.buf[p], parity) + 2 * q;
+        peer_ll_store_bits(dst, raw.x, epoch);
+        peer_ll_store_bits(dst + 1, raw.y, epoch);
+      }
+    }
+    // (iii) the other ranks' slices, from the entries they sent
+    bool ok = true;
+    for (int r = 0; r < world && ok; r++) {
+      if (r == rank) continue;
+      const long long o_lo = r * per_rank + (long long)cta * per_cta;
+      const long long o_hi = min(min(o_lo + per_cta, (long long)(r + 1) * per_rank), quads);
+      for (long long q = o_lo + tid; q < o_hi && ok; q += blockDim.x) {
+        float b0, b1;
+        ok = peer_ll_load2(peer_result(a.buf[rank], parity) + 2 * q, epoch, a.timeout_ns, &b0, &b1);
+        if (ok) reinterpret_cast<uint2*>(a.h)[q] = make_uint2(__float_as_uint(b0), __float_as_uint(b1));
+      }
+    }
+    if (!ok) atomicCAS(a.err, 0, 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(&a.epoch[1], 1u) == gridDim.x - 1) {
+      a.epoch[1] = 0;
+      a.epoch[0] = epoch;
+    }
+  }
+}
+
 // Allocate this rank's exchange buffer and return its 64-byte CUDA IPC handle, to be handed to every other rank.
 JG_API int jg_comm_peer_export(jg_comm* comm, void* handle64) {
   JG_REQUIRE(comm != nullptr && handle64 != nullptr, "comm_peer_export: null argument");
   JG_ENTER(comm->dev);
   JG_REQUIRE(comm->world <= PEER_MAX_WORLD, "comm_peer_export: at most %d ranks", PEER_MAX_WORLD);
+  JG_REQUIRE(!comm->in_process, "comm_peer_export: communicators made by jg_comm_init_all have their buffers already");
   JG_REQUIRE(comm->dev->ordinal >= 0 && comm->dev->ordinal < 64, "comm_peer_export: device ordinal out of range");
   JG_REQUIRE(!comm->dev->capturing, "comm_peer_export: not inside a graph capture");
   jg_peer& p = g_peer[comm->dev->ordinal];
@@ -244,7 +360,7 @@ JG_API int jg_comm_peer_export(jg_comm* comm, void* handle64) {
     JG_CUDA(cudaMemset(p.epoch, 0, PEER_MAX_CTAS * sizeof(uint32_t) + sizeof(int)));
     p.err = reinterpret_cast<int*>(p.epoch + PEER_MAX_CTAS);
     const char* e = getenv("JG_PEER_TIMEOUT_MS");
-    p.timeout_ns = (unsigned long long)(e ? atoll(e) : 20000) * 1000000ull;
+    p.timeout_ns = (unsigned long long)(e ? atoll(e) : 5000) * 1000000ull;
   }
   cudaIpcMemHandle_t h;
   JG_CUDA(cudaIpcGetMemHandle(&h, p.local));
@@ -261,8 +377,8 @@ JG_API int jg_comm_peer_open(jg_comm* comm, const void* handles) {
   JG_REQUIRE(p.local != nullptr, "comm_peer_open: call jg_comm_peer_export first");
   JG_REQUIRE(!comm->dev->capturing, "comm_peer_open: not inside a graph capture");
   for (int r = 0; r < comm->world; r++) {
-    if (r == comm->rank) { p.mapped[r] = p.local; continue; }
-    if (p.mapped[r] != nullptr) continue;
+    if (r == comm->rank) { p.mapped[r] = p.local; p.ipc[r] = false; continue; }
+    if (p.mapped[r] != nullptr && p.ipc[r]) { cudaIpcCloseMemHandle(p.mapped[r]); p.mapped[r] = nullptr; }  // an earlier communicator's
     cudaIpcMemHandle_t h;
     memcpy(&h, (const unsigned char*)handles + (size_t)r * 64, sizeof(h));
     void* ptr = nullptr;
@@ -273,6 +389,7 @@ JG_API int jg_comm_peer_open(jg_comm* comm, const void* handles) {
       return JG_ENOTSUP;
     }
     p.mapped[r] = (unsigned char*)ptr;
+    p.ipc[r] = true;
   }
   p.open = true;
   return JG_OK;
@@ -308,6 +425,14 @@ static int peer_launch(jg_comm* comm, int mode, uint64_t h, uint64_t part, uint6
     if (ctas > 32) ctas = 32;
     return jg_launch(dev, "peer_allreduce_residual", peer_sum_residual_kernel, dim3(ctas), dim3(256), 0, a);
   }
+  if (mode == 2) {
+    // one quad per thread in step (ii) when the slice allows it; at most 64 CTAs (one flag row each)
+    const long long per_rank = (n / 4 + comm->world - 1) / comm->world;
+    int ctas = (int)((per_rank + 255) / 256);
+    if (ctas > 64) ctas = 64;
+    if (ctas < 1) ctas = 1;
+    return jg_launch(dev, "peer_allreduce2_residual", peer_sum2_residual_kernel, dim3(ctas), dim3(256), 0, a);
+  }
   return jg_launch(dev, "peer_allreduce_max", peer_max_kernel, dim3(1), dim3(256), 0, a);
 }
 
@@ -320,6 +445,28 @@ JG_API int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32
              (unsigned long long)PEER_LL_VALUES);
   JG_REQUIRE(jg_aligned(h, 2) && jg_aligned(part32, 4), "peer_allreduce_residual: null or misaligned pointer");
   return peer_launch(comm, 0, h, part32, 0, (long long)n);
+}
+
+// Where this rank's fp32 partial sums must be written (by jg_linear_partial) for jg_peer_allreduce2_residual: a region
+// of the exchange buffer the peers read directly.  floats = its capacity.
+JG_API int jg_comm_peer_partial(jg_comm* comm, uint64_t* ptr, uint64_t* floats) {
+  JG_REQUIRE(comm != nullptr && ptr != nullptr && floats != nullptr, "comm_peer_partial: null argument");
+  const int o = comm->dev->ordinal;
+  JG_REQUIRE(o >= 0 && o < 64 && g_peer[o].open, "comm_peer_partial: the peer buffers are not open");
+  *ptr = (uint64_t)(uintptr_t)(g_peer[o].local + PEER_PARTIAL_OFFSET);
+  *floats = PEER_TWOSHOT_VALUES;
+  return JG_OK;
+}
+
+// h[i] <- h[i] + half( sum over ranks of partial[i] ), i < n, where every rank's partial sums lie in its
+// jg_comm_peer_partial region (two-shot exchange: each rank reduces 1/world of the values and sends the results).
+JG_API int jg_peer_allreduce2_residual(jg_comm* comm, uint64_t h, uint64_t n) {
+  JG_REQUIRE(comm != nullptr, "peer_allreduce2_residual: null communicator");
+  JG_ENTER(comm->dev);
+  JG_REQUIRE(n > 0 && n % 4 == 0 && n <= PEER_TWOSHOT_VALUES, "peer_allreduce2_residual: n=%llu must be a multiple of 4, at most %llu",
+             (unsigned long long)n, (unsigned long long)PEER_TWOSHOT_VALUES);
+  JG_REQUIRE(jg_aligned(h, 8), "peer_allreduce2_residual: null or misaligned pointer");
+  return peer_launch(comm, 2, h, 0, 0, (long long)n);
 }
 
 // keys[i] <- max over ranks of keys[i] (packed greedy keys of a vocabulary-sharded output layer).
@@ -341,3 +488,73 @@ int jg_peer_error(jg_dev* dev, int* code) {
   if (*code) JG_CUDA(cudaMemset(g_peer[dev->ordinal].err, 0, sizeof(int)));
   return JG_OK;
 }
+
+// ------------------------------------------------------------------------------------------------ one process, N devices
+// All ranks of a tensor-parallel group in ONE process (the reference engine is a single thread that drives every
+// device, jsgrad/tensor.ts:676-687): devs[r] becomes rank r.  The exchange buffers are allocated here and addressed
+// directly after cudaDeviceEnablePeerAccess, so neither a unique id nor IPC handles travel anywhere;
+// jg_comm_peer_export / jg_comm_peer_open are not needed (and not allowed) on these communicators.  The peer-memory
+// exchanges work as with one process per rank: a kernel that waits for its peers does so on its own GPU while the host
+// thread goes on to launch the peers' kernels.  NCCL collectives issued rank after rank by one thread must be
+// bracketed by jg_comm_group_begin / jg_comm_group_end.
+JG_API int jg_comm_init_all(int32_t n, jg_dev** devs, const char* nccl_path, jg_comm** out) {
+  JG_REQUIRE(devs != nullptr && out != nullptr && n >= 1 && n <= PEER_MAX_WORLD, "comm_init_all: 1..%d devices", PEER_MAX_WORLD);
+  for (int r = 0; r < n; r++) {
+    JG_REQUIRE(devs[r] != nullptr && devs[r]->ordinal >= 0 && devs[r]->ordinal < 64, "comm_init_all: bad device %d", r);
+    JG_REQUIRE(!devs[r]->capturing, "comm_init_all: not inside a graph capture");
+    JG_REQUIRE(g_peer[devs[r]->ordinal].local == nullptr, "comm_init_all: device %d already has an exchange buffer", devs[r]->ordinal);
+    for (int q = 0; q < r; q++) JG_REQUIRE(devs[q]->ordinal != devs[r]->ordinal, "comm_init_all: device %d listed twice", devs[r]->ordinal);
+  }
+  nccl_comm_t nc[PEER_MAX_WORLD] = {};
+  bool have_nccl = false;
+  if (n > 1 && nccl_open(nccl_path) == JG_OK && g_nccl.comm_init_all) {
+    int ords[PEER_MAX_WORLD];
+    for (int r = 0; r < n; r++) ords[r] = devs[r]->ordinal;
+    const int rc = g_nccl.comm_init_all(nc, n, ords);
+    if (rc != 0) return nccl_fail(rc, "ncclCommInitAll");
+    have_nccl = true;
+  }
+  // exchange buffers + peer access in both directions
+  for (int r = 0; r < n; r++) {
+    JG_CUDA(cudaSetDevice(devs[r]->ordinal));
+    jg_peer& p = g_peer[devs[r]->ordinal];
+    JG_CUDA(cudaMalloc(&p.local, PEER_BYTES));
+    JG_CUDA(cudaMemset(p.local, 0, PEER_BYTES));
+    JG_CUDA(cudaMalloc(&p.epoch, PEER_MAX_CTAS * sizeof(uint32_t) + sizeof(int)));
+    JG_CUDA(cudaMemset(p.epoch, 0, PEER_MAX_CTAS * sizeof(uint32_t) + sizeof(int)));
+    p.err = reinterpret_cast<int*>(p.epoch + PEER_MAX_CTAS);
+    const char* e = getenv("JG_PEER_TIMEOUT_MS");
+    p.timeout_ns = (unsigned long long)(e ? atoll(e) : 5000) * 1000000ull;
+    for (int q = 0; q < n; q++) {
+      if (q == r) continue;
+      int can = 0;
+      JG_CUDA(cudaDeviceCanAccessPeer(&can, devs[r]->ordinal, devs[q]->ordinal));
+      if (!can) { jg_set_error("comm_init_all: device %d cannot address device %d's memory", devs[r]->ordinal, devs[q]->ordinal); return JG_ENOTSUP; }
+      cudaError_t pe = cudaDeviceEnablePeerAccess(devs[q]->ordinal, 0);
+      if (pe != cudaSuccess && pe != cudaErrorPeerAccessAlreadyEnabled) return jg_cuda_fail(pe, "cudaDeviceEnablePeerAccess", __FILE__, __LINE__);
+      cudaGetLastError();
+    }
+  }
+  for (int r = 0; r < n; r++) {
+    jg_peer& p = g_peer[devs[r]->ordinal];
+    for (int q = 0; q < n; q++) { p.mapped[q] = g_peer[devs[q]->ordinal].local; p.ipc[q] = false; }
+    p.open = true;
+    jg_comm* cm = new jg_comm();
+    cm->dev = devs[r]; cm->comm = have_nccl ? nc[r] : nullptr; cm->rank = r; cm->world = n; cm->in_process = true;
+    out[r] = cm;
+  }
+  return JG_OK;
+}
+
+// ncclGroupStart / ncclGroupEnd: one thread issuing the same NCCL collective for several ranks must bracket them.
+JG_API int jg_comm_group_begin(void) {
+  if (!g_nccl.group_start) return JG_OK;
+  const int rc = g_nccl.group_start();
+  return rc == 0 ? JG_OK : nccl_fail(rc, "ncclGroupStart");
+}
+JG_API int jg_comm_group_end(void) {
+  if (!g_nccl.group_end) return JG_OK;
+  const int rc = g_nccl.group_end();
+  return rc == 0 ? JG_OK : nccl_fail(rc, "ncclGroupEnd");
+}
+

@@ -23,9 +23,11 @@ struct jg_dev {
   int* err_word;    // device word written by kernels whose bounded waits gave up (0 = fine); allocated on first use
   bool tc_pending;  // such kernels were launched since the word was last checked
   bool peer_pending;  // peer-memory reductions (comm.cu) were launched since their error word was last checked
-  // Device ranges most recently written by a kernel that produces weights (jg_dequant_i8_f16).  The projection kernels
-  // request weight tiles before they wait for their predecessor — right for parameters, wrong for such a copy.
-  uint64_t fresh_lo[4], fresh_hi[4];
+  // Device ranges written by the library's own launches since the stream was last synchronised (the latest
+  // JG_FRESH_RING of them).  The tensor-core projection kernels load weight tiles before they wait for their
+  // predecessor — right for parameters that were there all along, wrong for a matrix one of the preceding launches
+  // is still writing (a dequantised copy, a seeded fill, a projection output reused as a weight).
+  uint64_t fresh_lo[16], fresh_hi[16];
   unsigned fresh_n;
 };
 int jg_check_device_errors(jg_dev* dev);  // after a stream synchronise: JG_ETIMEDOUT if a bounded wait gave up
@@ -74,16 +76,21 @@ static inline int jg_after_launch(jg_dev* dev, const char* name) {
   } while (0)
 
 static inline bool jg_aligned(uint64_t p, uint64_t a) { return p != 0 && (p % a) == 0; }
+constexpr unsigned JG_FRESH_RING = 16;
 static inline void jg_mark_fresh(jg_dev* dev, uint64_t lo, uint64_t bytes) {
-  const unsigned i = dev->fresh_n++ & 3u;
+  const unsigned i = dev->fresh_n++ % JG_FRESH_RING;
   dev->fresh_lo[i] = lo;
   dev->fresh_hi[i] = lo + bytes;
+}
+// After a stream synchronisation nothing is in flight: every earlier write is visible to any later launch.
+static inline void jg_clear_fresh(jg_dev* dev) {
+  for (unsigned i = 0; i < JG_FRESH_RING; i++) dev->fresh_lo[i] = dev->fresh_hi[i] = 0;
 }
 // Whether `p` lies in memory a weight-producing kernel wrote recently: such weights must not be read ahead of the
 // dependency wait.
 static inline bool jg_is_fresh(const jg_dev* dev, const void* p) {
   const uint64_t v = (uint64_t)(uintptr_t)p;
-  for (int i = 0; i < 4; i++)
+  for (unsigned i = 0; i < JG_FRESH_RING; i++)
     if (v != 0 && v >= dev->fresh_lo[i] && v < dev->fresh_hi[i]) return true;
   return false;
 }
@@ -93,22 +100,39 @@ static inline bool jg_is_fresh(const jg_dev* dev, const void* p) {
 // stream-serialization attribute: the kernel may begin while its predecessor on the stream is still draining, and
 // must execute pdl_wait() before it touches anything the predecessor wrote (all kernels here do, at their top or,
 // for the weight-streaming kernels, right after their first weight prefetch).
+// `cluster_x` > 1 launches thread-block clusters of that many CTAs along x (the grid's x must be a multiple of it).
 template <typename... KArgs, typename... Args>
-static inline int jg_launch(jg_dev* dev, const char* name, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                            Args... args) {
+static inline int jg_launch_cluster(jg_dev* dev, const char* name, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    int cluster_x, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = dev->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (cluster_x > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = (unsigned)cluster_x;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    na++;
+  }
+  if (dev->pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = dev->pdl ? 1 : 0;
+  cfg.numAttrs = na;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
   if (e != cudaSuccess) return jg_cuda_fail(e, name, __FILE__, __LINE__);
   return jg_after_launch(dev, name);
+}
+template <typename... KArgs, typename... Args>
+static inline int jg_launch(jg_dev* dev, const char* name, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                            Args... args) {
+  return jg_launch_cluster(dev, name, kern, grid, block, smem, 1, args...);
 }
 #endif
 

@@ -116,6 +116,7 @@ int jg_check_device_errors(jg_dev* dev) {
 JG_API int jg_device_sync(jg_dev* dev) {
   JG_ENTER(dev);
   JG_CUDA(cudaStreamSynchronize(dev->stream));
+  jg_clear_fresh(dev);
   return jg_check_device_errors(dev);
 }
 
@@ -170,6 +171,7 @@ JG_API int jg_copyin(jg_dev* dev, uint64_t dst, const void* host, size_t nbytes)
   JG_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, host, nbytes, cudaMemcpyHostToDevice, dev->stream));
   // a pinned source would make the call truly asynchronous; callers of this entry point may not keep `host` alive
   JG_CUDA(cudaStreamSynchronize(dev->stream));
+  jg_clear_fresh(dev);
   return JG_OK;
 }
 
@@ -180,6 +182,7 @@ JG_API int jg_copyout(jg_dev* dev, void* host, uint64_t src, size_t nbytes) {
   JG_REQUIRE(!dev->capturing, "host copy while a graph is being captured");
   JG_CUDA(cudaMemcpyAsync(host, (const void*)(uintptr_t)src, nbytes, cudaMemcpyDeviceToHost, dev->stream));
   JG_CUDA(cudaStreamSynchronize(dev->stream));
+  jg_clear_fresh(dev);
   return jg_check_device_errors(dev);
 }
 
@@ -188,6 +191,7 @@ JG_API int jg_copyin_async(jg_dev* dev, uint64_t dst, const void* pinned_host, s
   if (nbytes == 0) return JG_OK;
   JG_REQUIRE(dst != 0 && pinned_host != nullptr, "null pointer in copyin_async");
   JG_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, pinned_host, nbytes, cudaMemcpyHostToDevice, dev->stream));
+  jg_mark_fresh(dev, dst, nbytes);
   return JG_OK;
 }
 
@@ -221,6 +225,7 @@ JG_API int jg_memset(jg_dev* dev, uint64_t dst, int32_t byte, size_t nbytes) {
   if (nbytes == 0) return JG_OK;
   JG_REQUIRE(dst != 0, "null pointer in memset");
   JG_CUDA(cudaMemsetAsync((void*)(uintptr_t)dst, byte, nbytes, dev->stream));
+  jg_mark_fresh(dev, dst, nbytes);
   return JG_OK;
 }
 
@@ -229,6 +234,7 @@ JG_API int jg_copy(jg_dev* dev, uint64_t dst, uint64_t src, size_t nbytes) {
   if (nbytes == 0) return JG_OK;
   JG_REQUIRE(dst != 0 && src != 0, "null pointer in copy");
   JG_CUDA(cudaMemcpyAsync((void*)(uintptr_t)dst, (const void*)(uintptr_t)src, nbytes, cudaMemcpyDeviceToDevice, dev->stream));
+  jg_mark_fresh(dev, dst, nbytes);
   return JG_OK;
 }
 
@@ -259,6 +265,7 @@ JG_API int jg_timer_stop(jg_dev* dev, double* seconds) {
   JG_REQUIRE(seconds != nullptr, "null output pointer");
   JG_CUDA(cudaEventRecord(dev->t1, dev->stream));
   JG_CUDA(cudaEventSynchronize(dev->t1));
+  jg_clear_fresh(dev);
   float ms = 0.f;
   JG_CUDA(cudaEventElapsedTime(&ms, dev->t0, dev->t1));
   *seconds = (double)ms * 1e-3;

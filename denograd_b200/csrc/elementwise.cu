@@ -274,24 +274,28 @@ static inline int fill_blocks(jg_dev* dev, uint64_t n) {
 JG_API int jg_fill_normal_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float std) {
   JG_ENTER(dev);
   JG_REQUIRE(n > 0 && jg_aligned(dst, 2), "fill_normal_f16: bad arguments");
+  jg_mark_fresh(dev, dst, n * 2);
   fill_normal_f16_kernel<<<fill_blocks(dev, n), 256, 0, dev->stream>>>((__half*)dst, seed, first, n, std / 65536.0f);
   return jg_after_launch(dev, "fill_normal_f16");
 }
 JG_API int jg_fill_uniform_i8(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n) {
   JG_ENTER(dev);
   JG_REQUIRE(n > 0 && dst != 0, "fill_uniform_i8: bad arguments");
+  jg_mark_fresh(dev, dst, n);
   fill_uniform_i8_kernel<<<fill_blocks(dev, n), 256, 0, dev->stream>>>((int8_t*)dst, seed, first, n);
   return jg_after_launch(dev, "fill_uniform_i8");
 }
 JG_API int jg_fill_scale_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float base) {
   JG_ENTER(dev);
   JG_REQUIRE(n > 0 && jg_aligned(dst, 2), "fill_scale_f16: bad arguments");
+  jg_mark_fresh(dev, dst, n * 2);
   fill_scale_f16_kernel<<<fill_blocks(dev, n), 256, 0, dev->stream>>>((__half*)dst, seed, first, n, base);
   return jg_after_launch(dev, "fill_scale_f16");
 }
 JG_API int jg_fill_const_f16(jg_dev* dev, uint64_t dst, uint64_t n, float value) {
   JG_ENTER(dev);
   JG_REQUIRE(n > 0 && jg_aligned(dst, 2), "fill_const_f16: bad arguments");
+  jg_mark_fresh(dev, dst, n * 2);
   fill_const_f16_kernel<<<fill_blocks(dev, n), 256, 0, dev->stream>>>((__half*)dst, n, __float2half_rn(value));
   return jg_after_launch(dev, "fill_const_f16");
 }
@@ -391,6 +395,7 @@ JG_API int jg_fill_uniform_i8_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint6
                                  uint64_t row0, uint64_t col0) {
   JG_ENTER(dev);
   JG_REQUIRE(rows > 0 && cols > 0 && col0 + cols <= full_cols && dst != 0, "fill_uniform_i8_2d: bad arguments");
+  jg_mark_fresh(dev, dst, rows * cols);
   fill_uniform_i8_2d_kernel<<<fill_blocks(dev, rows * cols), 256, 0, dev->stream>>>((int8_t*)dst, seed, rows, cols, full_cols, row0, col0);
   return jg_after_launch(dev, "fill_uniform_i8_2d");
 }
@@ -399,6 +404,7 @@ JG_API int jg_fill_normal_f16_2d(jg_dev* dev, uint64_t dst, uint64_t seed, uint6
                                  uint64_t row0, uint64_t col0, float std) {
   JG_ENTER(dev);
   JG_REQUIRE(rows > 0 && cols > 0 && col0 + cols <= full_cols && jg_aligned(dst, 2), "fill_normal_f16_2d: bad arguments");
+  jg_mark_fresh(dev, dst, rows * cols * 2);
   fill_normal_f16_2d_kernel<<<fill_blocks(dev, rows * cols), 256, 0, dev->stream>>>((__half*)dst, seed, rows, cols, full_cols,
                                                                                    row0, col0, std / 65536.0f);
   return jg_after_launch(dev, "fill_normal_f16_2d");

@@ -31,7 +31,10 @@ constexpr int TC_BM = 128;  // weight rows per CTA (MMA M)
 constexpr int TC_BK = 64;   // k per stage: 64 halves = one 128-byte swizzle row
 // Threads of a CTA: warp 0 TMA, warp 1 MMA, then EPW epilogue warps for each 32-lane quarter of tensor memory.
 constexpr int tc_threads(int epw) { return 64 + 128 * epw; }
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;  // polls of one mbarrier phase before giving up (~ tens of ms)
+// Polls of one mbarrier phase before a wait gives up.  A try_wait that fails returns after the hardware's own
+// suspend time (up to ~1 us), so the limit is of the order of seconds; every wait starts after the kernel's dependency
+// wait, i.e. it only ever measures this kernel's own TMA / MMA progress.
+constexpr uint32_t TC_SPIN_LIMIT = 1u << 24;
 
 struct TcArgs {
   __half* y;
@@ -200,6 +203,9 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const 
     // ---- MMA issuer: 4 x (128 x TN x 16) per stage and matrix, accumulating in tensor memory
     const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);  // f32 acc, f16 x f16, K-major both
     bool ok = true;
+    // the poll budget of the waits below starts only once the predecessor is done: the producer cannot request the
+    // activation tiles any earlier, so a slow predecessor must not use the budget up
+    pdl_wait();
     for (int i = 0; i < nk; i++) {
       const int s = i % STAGES;
       if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 2); ok = false; break; }
@@ -323,6 +329,37 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
   return JG_OK;
 }
 
+// Encoded maps are kept per (base, rows, cols, box rows): a model's weights and workspaces keep their addresses, so a
+// step after the first finds all of its maps here instead of encoding three per launch.
+struct MapKey { const void* base; uint64_t rows, cols; uint32_t box_rows; };
+struct MapSlot { MapKey k; CUtensorMap m; bool used; };
+constexpr int MAP_SLOTS = 1024;
+static MapSlot g_maps[MAP_SLOTS];
+
+static int cached_map(const CUtensorMap** out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what) {
+  uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull ^ (rows * 0xBF58476D1CE4E5B9ull) ^ (cols << 20) ^ box_rows;
+  h ^= h >> 29;
+  for (int probe = 0; probe < 8; probe++) {
+    MapSlot& s = g_maps[(h + probe) % MAP_SLOTS];
+    if (s.used && s.k.base == base && s.k.rows == rows && s.k.cols == cols && s.k.box_rows == box_rows) { *out = &s.m; return JG_OK; }
+    if (!s.used) {
+      int rc = make_map(&s.m, base, rows, cols, box_rows, what);
+      if (rc) return rc;
+      s.k = MapKey{base, rows, cols, box_rows};
+      s.used = true;
+      *out = &s.m;
+      return JG_OK;
+    }
+  }
+  MapSlot& s = g_maps[h % MAP_SLOTS];  // neighbourhood full: replace
+  int rc = make_map(&s.m, base, rows, cols, box_rows, what);
+  if (rc) { s.used = false; return rc; }
+  s.k = MapKey{base, rows, cols, box_rows};
+  s.used = true;
+  *out = &s.m;
+  return JG_OK;
+}
+
 template <int TN, int EPI>
 static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
   using Cfg = TcCfg<TN, EPI>;
@@ -333,13 +370,14 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
     JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     attr_set[slot] = true;
   }
-  CUtensorMap tw0, tw1, tx;
-  int rc = make_map(&tw0, w0, a.N, a.K, TC_BM, "weights");
+  const CUtensorMap *pw0, *pw1, *px;
+  int rc = cached_map(&pw0, w0, a.N, a.K, TC_BM, "weights");
   if (rc) return rc;
-  rc = make_map(&tw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
+  rc = cached_map(&pw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
   if (rc) return rc;
-  rc = make_map(&tx, x, a.M, a.K, TN, "activations");
+  rc = cached_map(&px, x, a.M, a.K, TN, "activations");
   if (rc) return rc;
+  const CUtensorMap tw0 = *pw0, tw1 = *pw1, tx = *px;
   // split K over a cluster until the launch has CTAs for about two thirds of the SMs, keeping at least 8 k-blocks
   // per CTA and the peers' partial sums within rank 0's pipeline buffers
   const int tiles = ((a.M + TN - 1) / TN) * (a.N / TC_BM), n_kb = a.K / TC_BK;

@@ -21,14 +21,23 @@
 //             LOGITS    y <- half(acc) and (value, lowest index) folded into a 64-bit max key per row
 //             PARTIAL   y32 <- acc (fp32): one rank's share of a row-parallel projection, reduced by a later call
 //             PEER      y <- residual + half(sum over ranks of acc): the same share, all-reduced inside this kernel
-//                       over NVLink peer memory — CTA c of every rank owns the same output rows, so it pushes its
-//                       partial sums into the peers' buffers, raises a flag per peer, waits (bounded) for the peers'
-//                       CTA c and finishes its rows itself; no grid-wide step and no second launch
+//                       over NVLink peer memory — CTA c of every rank owns the same output rows, so it stores its
+//                       partial sums, each paired with the exchange number (flag-in-data, peer.cuh), into the peers'
+//                       buffers, waits (bounded) for the peers' entries of its own rows and finishes them itself; no
+//                       grid-wide step and no second launch
+//             PUSH      the first half of that exchange only: the entries go to every rank's buffer (this rank's
+//                       included) and the kernel ends without waiting for anybody
+//   prologue  GATHER    the second half, in the kernel that consumes the sum (the next norm + projection of the block):
+//                       x <- h_in + half(sum over ranks of the pushed entries), then NORM on it.  The NVLink crossing
+//                       of the entries thus overlaps the producer's tail, this kernel's launch and its weight
+//                       prefetch instead of stalling the producer.  The CTAs of a thread-block cluster split the
+//                       reduction and hand each other their slices through distributed shared memory, so each CTA
+//                       reads only 1/cluster of the entries; the first cluster also writes the new residual stream
 #include "common.cuh"
 #include "peer.cuh"
 #include "transcendental.cuh"
 
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3, EPI_PARTIAL = 4, EPI_PEER = 5 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_LOGITS = 3, EPI_PARTIAL = 4, EPI_PEER = 5, EPI_PUSH = 6 };
 
 struct GemvArgs {
   const __half* x;       // [M][K]
@@ -44,7 +53,9 @@ struct GemvArgs {
   int row_offset;           // LOGITS: vocabulary index of weight row 0 (vocabulary-sharded output layer)
   float eps, recip_k;
   int M, N, K;
-  PeerArgs peer;            // PEER: exchange buffers of the ranks, exchange counter, error word
+  PeerArgs peer;            // PEER / PUSH / GATHER: exchange buffers of the ranks, exchange counter, error word
+  const __half* h_in;       // GATHER: residual stream before the exchanged sum is added ([M][K])
+  __half* h_out;            // GATHER: residual stream after it (a different buffer: other clusters still read h_in)
 };
 
 constexpr int GEMV_THREADS = 256;
@@ -75,8 +86,17 @@ __device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) 
 
 constexpr uint32_t GEMV_PREFETCH_BYTES = 4096;  // per weight row and warp, ahead of the dependency wait
 
-template <int MT, bool W8, int EPI, bool NORM, int RW, int U>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a) {
+// Rank of this CTA in its cluster / size of the cluster (1 when the launch carries no cluster dimension).
+__device__ __forceinline__ uint32_t cluster_cta_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t cluster_cta_count() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void st_cluster_u32(uint32_t local_addr, uint32_t cta, uint32_t v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta));
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(remote), "r"(v) : "memory");
+}
+
+template <int MT, bool W8, int EPI, bool NORM, int RW, int U, bool GATHER>
+__global__ void __launch_bounds__(GEMV_THREADS, 2) jg_matvec_kernel(const GemvArgs a) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __half* xs = reinterpret_cast<__half*>(smem_raw);  // [MT][K]
   constexpr int NW = (EPI == EPI_SWIGLU) ? 2 : 1;
@@ -123,10 +143,47 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
   uint32_t peer_epoch = 0;
   int peer_parity = 0;
   float* peer_mine = nullptr;
-  if (EPI == EPI_PEER) {
+  if (EPI == EPI_PEER || EPI == EPI_PUSH) {
     peer_epoch = a.peer.epoch[0] + 1;
     peer_parity = (int)(peer_epoch & 1u);
     peer_mine = peer_slot(a.peer.buf[a.peer.rank], peer_parity, a.peer.rank);
+  }
+
+  if (GATHER) {
+    // ---- finish the exchange the preceding kernel of every rank started: h_out = h_in + half(sum over ranks), in
+    //      rank order so that all ranks hold identical bits.  That kernel has completed on this rank (dependency wait
+    //      above), so the counter already carries the exchange's number; the peers' entries may still be in flight.
+    //      Each CTA of the cluster reduces its slice (pairs of values) and writes the fp16 results into the
+    //      activation rows of every CTA of the cluster.
+    const uint32_t ex = a.peer.epoch[0];
+    const int par = (int)(ex & 1u);
+    const uint32_t cr = cluster_cta_rank(), cs = cluster_cta_count();
+    const int pairs = a.M * K / 2;
+    const int per = (pairs + (int)cs - 1) / (int)cs;
+    const int p_lo = (int)cr * per, p_hi = min(pairs, p_lo + per);
+    const bool writer = (blockIdx.x < cs);  // the first cluster stores the new residual stream
+    bool ok = true;
+    for (int pi = p_lo + tid; pi < p_hi; pi += GEMV_THREADS) {
+      float s0 = 0.f, s1 = 0.f;
+      for (int r = 0; r < a.peer.world && ok; r++) {
+        float v0 = 0.f, v1 = 0.f;
+        const uint2* e = peer_ll(a.peer.buf[a.peer.rank], par, r) + 2 * (size_t)pi;
+        ok = peer_ll_load2(e, ex, a.peer.timeout_ns, &v0, &v1);
+        s0 = __fadd_rn(s0, v0);
+        s1 = __fadd_rn(s1, v1);
+      }
+      const __half2 old = *reinterpret_cast<const __half2*>(a.h_in + 2 * (size_t)pi);
+      __half2 nw;
+      nw.x = hadd1(old.x, __float2half_rn(s0));
+      nw.y = hadd1(old.y, __float2half_rn(s1));
+      const uint32_t bits = *reinterpret_cast<const uint32_t*>(&nw);
+      if (writer) *reinterpret_cast<uint32_t*>(a.h_out + 2 * (size_t)pi) = bits;
+      const uint32_t local = (uint32_t)__cvta_generic_to_shared(xs + 2 * (size_t)pi);
+      for (uint32_t c = 0; c < cs; c++) st_cluster_u32(local, c, bits);
+    }
+    if (!ok) atomicCAS(a.peer.err, 0, 1);  // a peer never arrived: the step's results are void, nobody is waited for
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
 
   // ---- prologue: activation rows -> shared memory (normalised when NORM); rows beyond M are zero
@@ -136,7 +193,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
       for (int c = tid; c < K / 8; c += GEMV_THREADS) reinterpret_cast<uint4*>(xm)[c] = make_uint4(0, 0, 0, 0);
       continue;
     }
-    const __half* xg = a.x + (size_t)m * K;
+    const __half* xg = GATHER ? xm : a.x + (size_t)m * K;  // GATHER: the rows are in place already
     if (NORM) {
       float ss = 0.f;
       for (int c = tid; c < K / 8; c += GEMV_THREADS) {
@@ -166,7 +223,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
         for (int k = 0; k < 8; k++) o[k] = hmul1(__float2half_rn(__fmul_rn(v[k], rs)), gh[k]);
         reinterpret_cast<uint4*>(xm)[c] = *reinterpret_cast<uint4*>(o);
       }
-    } else {
+    } else if (!GATHER) {
       for (int c = tid; c < K / 8; c += GEMV_THREADS) reinterpret_cast<uint4*>(xm)[c] = ld_128(xg + (size_t)c * 8);
     }
   }
@@ -204,6 +261,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
     const size_t o = (size_t)m * N + (size_t)row;
     if (EPI == EPI_PARTIAL) { a.y32[o] = s_a; return; }
     if (EPI == EPI_PEER) { peer_mine[o] = s_a; return; }
+    if (EPI == EPI_PUSH) {  // flag-in-data entry for every rank, this one included; nothing is awaited here
+      for (int p = 0; p < a.peer.world; p++) peer_ll_store(peer_ll(a.peer.buf[p], peer_parity, a.peer.rank) + o, s_a, peer_epoch);
+      return;
+    }
     __half v = __float2half_rn(s_a);
     if (EPI == EPI_RESIDUAL) v = hadd1(a.residual[o], v);
     if (EPI == EPI_SWIGLU) v = jg_silu_mul(v, __float2half_rn(s_b));
@@ -329,6 +390,8 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
       if (ok) a.y[o] = hadd1(a.residual[o], __float2half_rn(sum));
     }
     if (!ok) atomicCAS(a.peer.err, 0, 1);
+  }
+  if (EPI == EPI_PEER || EPI == EPI_PUSH) {
     __syncthreads();
     if (tid == 0) {
       __threadfence();
@@ -356,13 +419,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) gemv_kernel(const GemvArgs a)
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-template <int MT, bool W8, int EPI, bool NORM>
+template <int MT, bool W8, int EPI, bool NORM, bool GATHER = false>
 static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
   // one unit = RW rows of one matrix, or one row of each SwiGLU matrix: two weight rows either way, with U chunks
   // of each in flight per lane in the warp-private part
   constexpr int RW = (EPI == EPI_SWIGLU) ? 1 : 2;
   constexpr int U = W8 ? (MT == 1 ? 4 : 2) : (MT == 1 ? 8 : (MT == 2 ? 4 : 2));
-  auto kern = gemv_kernel<MT, W8, EPI, NORM, RW, U>;
+  auto kern = jg_matvec_kernel<MT, W8, EPI, NORM, RW, U, GATHER>;
   const size_t smem = (size_t)MT * a.K * sizeof(__half);
   if (smem + 2048 > (size_t)dev->prop.sharedMemPerBlockOptin) {
     jg_set_error("%s: %d activation rows of K=%d need %zu B of shared memory (limit %zu)", name, MT, a.K, smem,
@@ -372,6 +435,8 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
   static size_t smem_set[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // per device ordinal, per instantiation
   static int occ_for[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   static size_t occ_smem[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  static int cluster_for[8] = {0, 0, 0, 0, 0, 0, 0, 0};  // GATHER: cluster size and how many CTAs of it fit at once
+  static int cluster_ctas[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int slot = dev->ordinal & 7;
   if (smem > 48 * 1024 && smem > smem_set[slot]) {
     JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dev->prop.sharedMemPerBlockOptin - 2048));
@@ -382,13 +447,43 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
     JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, GEMV_THREADS, smem));
     occ_for[slot] = occ < 1 ? 1 : (occ > 4 ? 4 : occ);
     occ_smem[slot] = smem;
+    if (GATHER) {
+      // the largest cluster (8, 4, 2) that still lets (nearly) as many CTAs run at once as an unclustered launch:
+      // a cluster must fit inside one GPC, so big clusters can leave SMs of a GPC without a CTA
+      const int want = dev->sm_count * occ_for[slot];
+      int best_cs = 1, best_ctas = want;
+      static int forced = -1;
+      if (forced < 0) { const char* e = getenv("JG_TP_CLUSTER"); forced = e ? atoi(e) : 0; }
+      for (int cs = 8; cs >= 2; cs >>= 1) {
+        if (forced > 0 && cs != forced) continue;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(want / cs * cs));
+        cfg.blockDim = dim3(GEMV_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = (unsigned)cs; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); continue; }
+        if (n * cs * 100 >= want * 93 || forced > 0) { best_cs = cs; best_ctas = n * cs < want ? n * cs : want / cs * cs; break; }
+      }
+      cluster_for[slot] = best_cs;
+      cluster_ctas[slot] = best_ctas;
+    }
   }
   const int n_units = (a.N + RW - 1) / RW;
   long long blocks = (long long)dev->sm_count * occ_for[slot];
   if (blocks > n_units) blocks = n_units;
   if (EPI == EPI_PEER && blocks > PEER_MAX_CTAS) blocks = PEER_MAX_CTAS;  // one flag row per CTA
   if (blocks < 1) blocks = 1;
-  return jg_launch(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, a);
+  int cs = 1;
+  if (GATHER) {
+    cs = cluster_for[slot] > 0 ? cluster_for[slot] : 1;
+    if (cs > 1 && blocks > cluster_ctas[slot]) blocks = cluster_ctas[slot];
+    blocks = (blocks + cs - 1) / cs * cs;  // whole clusters; a CTA without units still takes part in the gather
+  }
+  return jg_launch_cluster(dev, name, kern, dim3((unsigned)blocks), dim3(GEMV_THREADS), smem, cs, a);
 }
 
 // gemm_small.cu: mma.sync projection for up to 64 rows (fp16 or int8 weights, activations already normalised)
@@ -420,7 +515,7 @@ static bool w8_mma() {
 
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
-  if (EPI == EPI_PEER) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
+  if (EPI == EPI_PEER || EPI == EPI_PUSH) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
     if (a.M == 1) return launch_gemv<1, W8, EPI, NORM>(dev, a, name);
     if (a.M == 2) return launch_gemv<2, W8, EPI, NORM>(dev, a, name);
     if (a.M <= 4) return launch_gemv<4, W8, EPI, NORM>(dev, a, name);
@@ -465,6 +560,7 @@ JG_API int jg_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t w, uint64_t s
   GemvArgs a = {};
   a.x = (const __half*)x; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)y;
   a.residual = (const __half*)residual; a.M = M; a.N = N; a.K = K;
+  jg_mark_fresh(dev, y, (uint64_t)M * N * 2);  // an output may be the next call's weight matrix
   if (residual) {
     JG_REQUIRE(jg_aligned(residual, 2), "linear: misaligned residual pointer");
     return scale ? dispatch_m<true, EPI_RESIDUAL, false>(dev, a, "linear") : dispatch_m<false, EPI_RESIDUAL, false>(dev, a, "linear");
@@ -481,6 +577,7 @@ JG_API int jg_norm_linear(jg_dev* dev, uint64_t y, uint64_t x, uint64_t norm_w, 
   GemvArgs a = {};
   a.x = (const __half*)x; a.norm_w = (const __half*)norm_w; a.eps = eps; a.recip_k = (float)(1.0 / (double)K);
   a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)y; a.M = M; a.N = N; a.K = K;
+  jg_mark_fresh(dev, y, (uint64_t)M * N * 2);
   return scale ? dispatch_m<true, EPI_STORE, true>(dev, a, "norm_linear") : dispatch_m<false, EPI_STORE, true>(dev, a, "norm_linear");
 }
 
@@ -561,4 +658,95 @@ JG_API int jg_linear_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t x, u
   if (rc) return rc;
   return scale ? dispatch_m<true, EPI_PEER, false>(dev, a, "linear_allreduce_residual")
                : dispatch_m<false, EPI_PEER, false>(dev, a, "linear_allreduce_residual");
+}
+
+// ------------------------------------------------------------------------------------------------ split exchange
+// The same all-reduce cut in two, so that no kernel waits for another rank while it has nothing else to do:
+//   jg_tp_linear_push        a row-parallel projection whose epilogue stores this rank's fp32 partial sums, paired with
+//                            the exchange number, into every rank's buffer and returns;
+//   jg_tp_norm_linear /      the projection that consumes the sum (the next norm + projection of the block, or the
+//   jg_tp_norm_swiglu /      output layer): its prologue adds the ranks' entries in rank order, rounds once, adds the
+//   jg_tp_norm_logits_argmax residual stream h_in, leaves the new stream in h_out and normalises it.
+// Every push must be followed, on every rank, by exactly one consuming call with the same M and K = the push's N before
+// the next exchange of any kind.  h_in and h_out must be different buffers.
+template <bool W8, int EPI>
+static int dispatch_gather(jg_dev* dev, const GemvArgs& a, const char* name) {
+  if (a.M == 1) return launch_gemv<1, W8, EPI, true, true>(dev, a, name);
+  if (a.M == 2) return launch_gemv<2, W8, EPI, true, true>(dev, a, name);
+  if (a.M <= 4) return launch_gemv<4, W8, EPI, true, true>(dev, a, name);
+  if (a.M <= 8) return launch_gemv<8, W8, EPI, true, true>(dev, a, name);
+  jg_set_error("%s: the projection that gathers a pushed sum takes at most 8 rows (M=%d)", name, a.M);
+  return JG_ENOTSUP;
+}
+
+static int check_gather(const char* name, jg_comm* comm, uint64_t h_out, uint64_t h_in, uint64_t norm_w, int M, int K, GemvArgs* a) {
+  JG_REQUIRE(jg_aligned(h_out, 4) && jg_aligned(h_in, 4) && h_out != h_in, "%s: h_in and h_out must be two distinct, 4-byte aligned buffers", name);
+  JG_REQUIRE(jg_aligned(norm_w, 16), "%s: null or misaligned norm weight", name);
+  JG_REQUIRE(M <= 8 && (size_t)M * K <= PEER_LL_VALUES, "%s: M=%d K=%d exceed 8 rows / %zu exchanged values", name, M, K, (size_t)PEER_LL_VALUES);
+  a->h_in = (const __half*)h_in; a->h_out = (__half*)h_out; a->norm_w = (const __half*)norm_w;
+  a->recip_k = (float)(1.0 / (double)K);
+  return jg_peer_fill_args(comm, &a->peer);
+}
+
+JG_API int jg_tp_linear_push(jg_comm* comm, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K) {
+  JG_REQUIRE(comm != nullptr, "tp_linear_push: null communicator");
+  jg_dev* dev = jg_comm_device(comm);
+  JG_ENTER(dev);
+  int rc = check_common("tp_linear_push", x, x, w, scale, M, N, K);
+  if (rc) return rc;
+  JG_REQUIRE(M <= 8 && (size_t)M * N <= PEER_LL_VALUES && N % 2 == 0, "tp_linear_push: M=%d N=%d exceed 8 rows / %zu outputs (N even)", M, N,
+             (size_t)PEER_LL_VALUES);
+  GemvArgs a = {};
+  a.x = (const __half*)x; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.M = M; a.N = N; a.K = K;
+  rc = jg_peer_fill_args(comm, &a.peer);
+  if (rc) return rc;
+  return scale ? dispatch_m<true, EPI_PUSH, false>(dev, a, "tp_linear_push") : dispatch_m<false, EPI_PUSH, false>(dev, a, "tp_linear_push");
+}
+
+JG_API int jg_tp_norm_linear(jg_comm* comm, uint64_t y, uint64_t h_out, uint64_t h_in, uint64_t norm_w, float eps, uint64_t w,
+                             uint64_t scale, int32_t M, int32_t N, int32_t K) {
+  JG_REQUIRE(comm != nullptr, "tp_norm_linear: null communicator");
+  jg_dev* dev = jg_comm_device(comm);
+  JG_ENTER(dev);
+  int rc = check_common("tp_norm_linear", y, h_in, w, scale, M, N, K);
+  if (rc) return rc;
+  GemvArgs a = {};
+  rc = check_gather("tp_norm_linear", comm, h_out, h_in, norm_w, M, K, &a);
+  if (rc) return rc;
+  a.eps = eps; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)y; a.M = M; a.N = N; a.K = K;
+  jg_mark_fresh(dev, y, (uint64_t)M * N * 2);
+  return scale ? dispatch_gather<true, EPI_STORE>(dev, a, "tp_norm_linear") : dispatch_gather<false, EPI_STORE>(dev, a, "tp_norm_linear");
+}
+
+JG_API int jg_tp_norm_swiglu(jg_comm* comm, uint64_t y, uint64_t h_out, uint64_t h_in, uint64_t norm_w, float eps, uint64_t w_gate,
+                             uint64_t s_gate, uint64_t w_up, uint64_t s_up, int32_t M, int32_t N, int32_t K) {
+  JG_REQUIRE(comm != nullptr, "tp_norm_swiglu: null communicator");
+  jg_dev* dev = jg_comm_device(comm);
+  JG_ENTER(dev);
+  int rc = check_common("tp_norm_swiglu", y, h_in, w_gate, s_gate, M, N, K);
+  if (rc) return rc;
+  JG_REQUIRE(jg_aligned(w_up, 16), "tp_norm_swiglu: null or misaligned up-projection weight");
+  JG_REQUIRE((s_gate == 0) == (s_up == 0), "tp_norm_swiglu: gate and up projections must share a weight format");
+  GemvArgs a = {};
+  rc = check_gather("tp_norm_swiglu", comm, h_out, h_in, norm_w, M, K, &a);
+  if (rc) return rc;
+  a.eps = eps; a.w0 = (const void*)w_gate; a.w1 = (const void*)w_up; a.s0 = (const __half*)s_gate; a.s1 = (const __half*)s_up;
+  a.y = (__half*)y; a.M = M; a.N = N; a.K = K;
+  return s_gate ? dispatch_gather<true, EPI_SWIGLU>(dev, a, "tp_norm_swiglu") : dispatch_gather<false, EPI_SWIGLU>(dev, a, "tp_norm_swiglu");
+}
+
+JG_API int jg_tp_norm_logits_argmax(jg_comm* comm, uint64_t logits, uint64_t key, uint64_t h_out, uint64_t h_in, uint64_t norm_w,
+                                    float eps, uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset) {
+  JG_REQUIRE(comm != nullptr, "tp_norm_logits_argmax: null communicator");
+  jg_dev* dev = jg_comm_device(comm);
+  JG_ENTER(dev);
+  int rc = check_common("tp_norm_logits_argmax", logits, h_in, w, scale, M, V_local, K);
+  if (rc) return rc;
+  JG_REQUIRE(jg_aligned(key, 8) && row_offset >= 0, "tp_norm_logits_argmax: misaligned key buffer or negative row offset");
+  GemvArgs a = {};
+  rc = check_gather("tp_norm_logits_argmax", comm, h_out, h_in, norm_w, M, K, &a);
+  if (rc) return rc;
+  a.eps = eps; a.w0 = (const void*)w; a.s0 = (const __half*)scale; a.y = (__half*)logits; a.key = (unsigned long long*)key;
+  a.M = M; a.N = V_local; a.K = K; a.row_offset = row_offset;
+  return scale ? dispatch_gather<true, EPI_LOGITS>(dev, a, "tp_norm_logits_argmax") : dispatch_gather<false, EPI_LOGITS>(dev, a, "tp_norm_logits_argmax");
 }

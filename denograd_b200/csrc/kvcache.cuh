@@ -29,4 +29,18 @@ __device__ __forceinline__ const __half* kv_row(const __half* layer, const int32
   return layer + (((size_t)pg * G + g) * page + slot) * hd;
 }
 
+// The same for a caller-owned pool of `n_pages` pages whose block table nobody validated: an entry outside the pool
+// yields a null pointer, which the callers read as a row of zeros (what an unwritten cache position holds).
+// n_pages = 0 means the table was validated on the host (jg_kvcache_set_block_table) and is followed as is.
+__device__ __forceinline__ const __half* kv_row_checked(const __half* layer, const int32_t* bt_row, int t, int g, int G,
+                                                        int page, int page_shift, int hd, int n_pages) {
+  const int pg = bt_row[t >> page_shift];
+  if (n_pages > 0 && (unsigned)pg >= (unsigned)n_pages) return nullptr;
+  const int slot = t & (page - 1);
+  return layer + (((size_t)pg * G + g) * page + slot) * hd;
+}
+__device__ __forceinline__ uint4 ld_kv_128(const __half* row, int off) {
+  return row ? *reinterpret_cast<const uint4*>(row + off) : make_uint4(0, 0, 0, 0);
+}
+
 static inline int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }

@@ -166,9 +166,18 @@ class Buffer:
         self.nbytes = size * _DTYPE_SIZE[dtype]
         self.base, self.offset = base, offset
         self._buf: int | None = None
+        self._owned = True
         if base is not None:
             assert offset + self.nbytes <= base.nbytes, "view outside its base buffer"
             self._buf = CUDAAllocator._offset(base.ptr, self.nbytes, offset)
+
+    @staticmethod
+    def external(device: "str | CUDA", ptr: int, size: int, dtype: str) -> "Buffer":
+        """A buffer over device memory somebody else owns (a region of the library's exchange buffer): never freed
+        or cached by this allocator."""
+        b = Buffer(device, size, dtype)
+        b._buf, b._owned = ptr, False
+        return b
 
     def allocate(self) -> "Buffer":
         if self._buf is None:
@@ -199,7 +208,7 @@ class Buffer:
 
     def __del__(self):
         try:
-            if self.base is None and self._buf is not None and self.dev.handle is not None:
+            if self.base is None and self._owned and self._buf is not None and self.dev.handle is not None:
                 self.dev.allocator.free(self._buf, self.nbytes)
         except Exception:
             pass

@@ -80,7 +80,7 @@ SIGNATURES: dict[str, list] = {
     "jg_rope_kvwrite_rows": [_vp, _vp, _i32, _u64, _u64, _i32, _u64, _u64, _i32, _i32],
     "jg_attn_rows": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32],
     "jg_attn_chunk": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
-    "jg_attn_decode_noalloc": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32, _i32, _i32, _i32, _i32],
+    "jg_attn_decode_noalloc": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32],
     "jg_pos_advance": [_vp, _u64, _i32],
     "jg_dequant_i8_f16": [_vp, _u64, _u64, _u64, _i64, _i64],
     "jg_fill_normal_f16": [_vp, _u64, _u64, _u64, _u64, _f32],
@@ -100,6 +100,15 @@ SIGNATURES: dict[str, list] = {
     "jg_peer_allreduce_residual": [_vp, _u64, _u64, _u64],
     "jg_peer_allreduce_max_u64": [_vp, _u64, _u64],
     "jg_linear_allreduce_residual": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
+    "jg_tp_linear_push": [_vp, _u64, _u64, _u64, _i32, _i32, _i32],
+    "jg_tp_norm_linear": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32],
+    "jg_tp_norm_swiglu": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
+    "jg_tp_norm_logits_argmax": [_vp, _u64, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32, _i32],
+    "jg_comm_peer_partial": [_vp, _P(_u64), _P(_u64)],
+    "jg_peer_allreduce2_residual": [_vp, _u64, _u64],
+    "jg_comm_init_all": [_i32, _P(_vp), C.c_char_p, _P(_vp)],
+    "jg_comm_group_begin": [],
+    "jg_comm_group_end": [],
     "jg_linear_partial": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_residual_add_f32": [_vp, _u64, _u64, _i64],
     "jg_norm_logits_argmax_shard": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32, _i32],

@@ -158,10 +158,18 @@ class TransformerBlock:
         a, f, dev, B = self.attention, self.feed_forward, ws.h.dev, ws.B
         d = ws.h.shape[-1]
         wqkv = a._wqkv
+        int8 = wqkv.scale_ptr != 0
+        # tensor parallelism, 1-2 rows: the row-parallel projections push their partial sums and the norm + projection
+        # that follows gathers them (and writes the new residual stream into the workspace's other h buffer)
+        split = tp is not None and B <= tp.split_rows(int8)
         # from 3 rows on (fp16 weights) normalise into ws.xn and project on the tensor cores; the fused-norm kernels
         # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: never)
-        big = _norm_first(B, wqkv.scale_ptr != 0)
-        if big:
+        big = _norm_first(B, int8) and not split
+        if split and ws.pending:  # the previous block's w2 left its sum on the wire
+            h_in, h_out = ws.flip()
+            ffi.call("jg_tp_norm_linear", tp.handle, ws.qkv.ptr, h_out.ptr, h_in.ptr, self.attention_norm.weight.ptr,
+                     self.attention_norm.eps, wqkv.weight.ptr, wqkv.scale_ptr, B, wqkv.out_features, d)
+        elif big:
             self.attention_norm.call(ws.h, out=ws.xn)
             dev.call("jg_linear", ws.qkv.ptr, ws.xn.ptr, wqkv.weight.ptr, wqkv.scale_ptr, 0, B, wqkv.out_features, d)
         else:
@@ -178,23 +186,32 @@ class TransformerBlock:
         if not a._kv.fused_attention:
             apply_rotary_emb_kvwrite(ws.qkv, freqs_cis, pos, a._kv, a._layer, a.n_heads)
             dev.call("jg_attn_decode", a._kv.handle, a._layer, ws.attn.ptr, ws.qkv.ptr, pos.ptr, B, a.n_heads)
-        self._row_parallel(a.wo, ws.attn, ws, tp)
-        if big:
+        self._row_parallel(a.wo, ws.attn, ws, tp, split=split)
+        if split:
+            h_in, h_out = ws.flip()
+            ffi.call("jg_tp_norm_swiglu", tp.handle, ws.ffn.ptr, h_out.ptr, h_in.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps,
+                     f.w1.weight.ptr, f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
+        elif big:
             self.ffn_norm.call(ws.h, out=ws.xn)
             dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.xn.ptr, 0, self.ffn_norm.eps, f.w1.weight.ptr,
                      f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
         else:
             dev.call("jg_norm_swiglu", ws.ffn.ptr, ws.h.ptr, self.ffn_norm.weight.ptr, self.ffn_norm.eps, f.w1.weight.ptr,
                      f.w1.scale_ptr, f.w3.weight.ptr, f.w3.scale_ptr, B, f.w1.out_features, d)
-        self._row_parallel(f.w2, ws.ffn, ws, tp)
+        self._row_parallel(f.w2, ws.ffn, ws, tp, split=split)
 
     @staticmethod
-    def _row_parallel(lin, x: Tensor, ws: "_Workspace", tp, w=None) -> None:
+    def _row_parallel(lin, x: Tensor, ws: "_Workspace", tp, w=None, split: bool = False) -> None:
         """h <- h + lin(x).  On one device the add is the projection's epilogue; under tensor parallelism `lin` holds a
         K-slice, so its fp32 partial sums are all-reduced first and rounded + added afterwards.  `w` = (weight pointer,
-        scale pointer) replaces lin's own (a dequantised copy of int8 weights)."""
+        scale pointer) replaces lin's own (a dequantised copy of int8 weights).  With `split` only the first half of
+        the exchange happens here: the sum is completed by the next projection's prologue (ws.pending says so)."""
         wp, sp = w if w is not None else (lin.weight.ptr, lin.scale_ptr)
         dev = ws.h.dev
+        if split:
+            tp.linear_push(x, lin, ws.B)
+            ws.pending = True
+            return
         if tp is None:
             dev.call("jg_linear", ws.h.ptr, x.ptr, wp, sp, ws.h.ptr, ws.B, lin.out_features, lin.in_features)
             return
@@ -231,13 +248,19 @@ class _Workspace:
     """Activation buffers of one decode step for a fixed batch size (what the memory planner would assign,
     jsgrad/engine/memory.ts:8-58): reused by every layer and every step, so a captured step never allocates."""
 
-    def __init__(self, dev: CUDA, B: int, dim: int, qkv_dim: int, q_dim: int, hidden: int, vocab: int):
+    def __init__(self, dev: CUDA, B: int, dim: int, qkv_dim: int, q_dim: int, hidden: int, vocab: int, tp=None):
         """`vocab` = 0 leaves out the logits (a multi-position chunk only projects its last rows, elsewhere)."""
         self.B = B
         self.tokens = Tensor.zeros((B,), "int32", dev)
         self.pos = Tensor.zeros((B,), "int32", dev)
         self.seq = Tensor.zeros((B,), "int32", dev)  # row -> sequence, for multi-position chunks
-        self.h = Tensor.empty((B, dim), "float16", dev)
+        # the residual stream; under tensor parallelism a second buffer, because the projection that completes a pushed
+        # all-reduce writes the new stream while other CTAs still read the old one (`flip`)
+        self._h = [Tensor.empty((B, dim), "float16", dev)]
+        if tp is not None:
+            self._h.append(Tensor.empty((B, dim), "float16", dev))
+        self.cur = 0
+        self.pending = False  # a row-parallel projection has pushed partial sums that nobody has gathered yet
         self.xn = Tensor.empty((B, dim), "float16", dev)
         self.qkv = Tensor.empty((B, qkv_dim), "float16", dev)
         self.attn = Tensor.empty((B, q_dim), "float16", dev)
@@ -245,12 +268,25 @@ class _Workspace:
         self.logits = Tensor.empty((B, vocab), "float16", dev) if vocab else None
         self.key = Tensor.zeros((B,), "uint64", dev)
         self.next_tokens = Tensor.zeros((B,), "int32", dev)
-        self.part32 = Tensor.empty((B, dim), "float32", dev)  # fp32 partial sums of a row-parallel projection
+        # fp32 partial sums of a row-parallel projection: inside the exchange buffer when they fit there, so that the
+        # peers can read them (two-shot exchange)
+        self.part32 = (tp.partial_tensor(B, dim) if tp is not None else None) or Tensor.empty((B, dim), "float32", dev)
         # page-locked staging for the per-step token / position upload and the result read-back
         self._pinned = C.c_void_p()
         ffi.call("jg_host_alloc", 3 * 4 * B, C.byref(self._pinned))
         arr = np.ctypeslib.as_array((C.c_int32 * (3 * B)).from_address(self._pinned.value))
         self.h_tokens, self.h_pos, self.h_next = arr[:B], arr[B:2 * B], arr[2 * B:]
+
+    @property
+    def h(self) -> Tensor:
+        return self._h[self.cur]
+
+    def flip(self) -> tuple[Tensor, Tensor]:
+        """(stream before the pending sum, buffer that receives the stream after it); the latter becomes `h`."""
+        old = self._h[self.cur]
+        self.cur ^= 1
+        self.pending = False
+        return old, self._h[self.cur]
 
     def __del__(self):
         try:
@@ -350,19 +386,26 @@ class Transformer:
         if key not in self._ws:
             qkv_dim = (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
             self._ws[key] = _Workspace(self.dev, B, self.dim, qkv_dim, self.n_heads * self.head_dim, self.hidden_dim,
-                                       self.vocab_local if key > 0 else 0)
+                                       self.vocab_local if key > 0 else 0, tp=self._tp)
         return self._ws[key]
 
     def _step(self, ws: _Workspace, advance: bool = False) -> None:
         """One token per row: reads ws.tokens / ws.pos, writes ws.logits and ws.next_tokens.  With `advance` the step
         also feeds its own output back (tokens <- next, pos += 1) so that it can be replayed with no host input."""
         dev, B = self.dev, ws.B
+        cur0 = ws.cur
         self.tok_embeddings.call(ws.tokens, out=ws.h)
         if self.fused:
             for layer in self.layers:
                 layer.call_fused(ws, ws.pos, self.freqs_cis, self._tp)
             out = self.output
-            if _norm_first(B, out.scale_ptr != 0):
+            if ws.pending:  # the last block's w2 pushed its sum: the output layer's prologue completes it
+                h_in, h_out = ws.flip()
+                ffi.call("jg_tp_norm_logits_argmax", self._tp.handle, ws.logits.ptr, ws.key.ptr, h_out.ptr, h_in.ptr,
+                         self.norm.weight.ptr, self.norm.eps, out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim,
+                         self.vocab_offset)
+                assert ws.cur == cur0, "a captured step must end on the residual buffer it started on"
+            elif _norm_first(B, out.scale_ptr != 0):
                 self.norm.call(ws.h, out=ws.xn)
                 dev.call("jg_norm_logits_argmax_shard", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
                          out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)

@@ -4,10 +4,16 @@ weight is split on (jsgrad/models/llama3.ts:239-249); `shard_plan` follows it wi
 from the workload definition (all-reduce only after the attention-output and FFN-down projections): wq/wk/wv are split
 by heads on their output axis instead of their input axis, so attention needs no exchange at all.
 
-One rank is one process with one GPU.  The only exchanges per layer are two fp32 all-reduces (after `wo` and `w2`),
-plus one max-reduction of the packed greedy keys per step when the output layer is sharded over the vocabulary.
-Small messages (a decode step's) go through one kernel per rank over NVLink peer memory that also applies the
-residual add (`open_peers`); larger ones (prompt chunks) and ranks whose memory cannot be mapped use NCCL.
+One rank is one process with one GPU (`TensorParallel`), or all ranks live in one process as in the reference engine
+(`TensorParallel.init_all`).  The only exchanges per layer are two fp32 all-reduces (after `wo` and `w2`), plus one
+max-reduction of the packed greedy keys per step when the output layer is sharded over the vocabulary.  All of them
+run over NVLink peer memory once `open_peers` has mapped the ranks' exchange buffers:
+  * 1-2 rows: the row-parallel projection only *pushes* its partial sums to the peers and the projection that consumes
+    the sum (next norm + projection) adds them up in its prologue — nothing waits for another rank while idle;
+  * up to 32 K values: one kernel in which every rank sends everything to everybody (flag-in-data entries);
+  * up to 256 K values (a batch of 32-64 decode rows): a two-shot kernel, each rank reducing 1/world of the values
+    straight out of the peers' partial-sum buffers;
+  * beyond that (prompt chunks), or when a peer's memory cannot be mapped: NCCL all-reduce + a separate add.
 """
 from __future__ import annotations
 
@@ -107,12 +113,50 @@ def exchange_via_directory(path: str, rank: int, world: int, tag: str = "ipc", t
 class TensorParallel:
     """Rank handle: NCCL communicator bound to this process's device stream."""
 
-    def __init__(self, dev: CUDA, rank: int, world: int, unique_id: bytes):
+    def __init__(self, dev: CUDA, rank: int, world: int, unique_id: bytes | None, handle=None):
         self.dev, self.rank, self.world = dev, rank, world
-        self.peer_capacity = 0  # fp32 elements the peer-memory exchange takes; 0 until open_peers succeeded
+        self.peer_capacity = 0  # fp32 elements the one-shot peer-memory exchange takes; 0 until open_peers succeeded
+        self.twoshot_capacity = 0  # fp32 elements of the two-shot exchange (its partial sums live in the exchange buffer)
+        self._partial_ptr = 0
+        if handle is not None:  # made by init_all: buffers and peers are in place already
+            self.handle = handle
+            self._query_capacity()
+            return
         self.handle = C.c_void_p()
         buf = C.create_string_buffer(unique_id, 128)
         ffi.call("jg_comm_init", dev.handle, nccl_library_path().encode(), buf, rank, world, C.byref(self.handle))
+
+    @staticmethod
+    def init_all(devs: list[CUDA]) -> "list[TensorParallel]":
+        """All ranks in this process (one thread drives every device, as the reference engine does): devs[r] is rank
+        r.  The exchange buffers are addressed directly; NCCL collectives need `group()` around the per-rank calls."""
+        ffi.load()
+        n = len(devs)
+        arr = (C.c_void_p * n)(*[d.handle for d in devs])
+        out = (C.c_void_p * n)()
+        ffi.call("jg_comm_init_all", n, arr, nccl_library_path().encode(), out)
+        return [TensorParallel(devs[r], r, n, None, handle=C.c_void_p(out[r])) for r in range(n)]
+
+    class group:
+        """`with TensorParallel.group(): ...` brackets NCCL collectives one thread issues for several ranks."""
+
+        def __enter__(self):
+            ffi.call("jg_comm_group_begin")
+
+        def __exit__(self, *a):
+            ffi.call("jg_comm_group_end")
+            return False
+
+    def _query_capacity(self) -> None:
+        cap = C.c_uint64(0)
+        ffi.call("jg_comm_peer_capacity", self.handle, C.byref(cap))
+        # one-shot exchange: every rank sends its whole message to every peer, which pays off only while latency
+        # dominates: up to 32 K values (128 KB)
+        self.peer_capacity = min(int(cap.value), 32 * 1024)
+        if self.peer_capacity > 0:
+            ptr, n = C.c_uint64(0), C.c_uint64(0)
+            ffi.call("jg_comm_peer_partial", self.handle, C.byref(ptr), C.byref(n))
+            self._partial_ptr, self.twoshot_capacity = int(ptr.value), int(n.value)
 
     @staticmethod
     def unique_id() -> bytes:
@@ -138,21 +182,42 @@ class TensorParallel:
             if e.status != 95:  # anything but "not supported" is a real error
                 raise
             return False
-        cap = C.c_uint64(0)
-        ffi.call("jg_comm_peer_capacity", self.handle, C.byref(cap))
-        # one-shot exchange: every rank sends its whole message to every peer, which pays off only while latency
-        # dominates; beyond 128 KB NCCL's bandwidth-optimal algorithms win (measured at 512 KB on two GPUs)
-        self.peer_capacity = min(int(cap.value), 32 * 1024)
+        self._query_capacity()
         return self.peer_capacity > 0
 
+    def partial_tensor(self, rows: int, dim: int) -> Tensor | None:
+        """fp32 [rows, dim] over the region of the exchange buffer the peers can read, for the partial sums of a
+        row-parallel projection that the two-shot exchange reduces in place; None when it does not fit."""
+        if rows * dim > self.twoshot_capacity or os.environ.get("JG_TP_TWOSHOT", "1") == "0":
+            return None
+        from .device import Buffer
+        return Tensor(Buffer.external(self.dev, self._partial_ptr, rows * dim, "float32"), shape=(rows, dim))
+
     def reduce_into_residual(self, h: Tensor, part32: Tensor) -> None:
-        """h <- h + half(sum over ranks of part32): the peer-memory kernel when the message fits, else NCCL + add."""
+        """h <- h + half(sum over ranks of part32): one of the peer-memory kernels when the message fits, else NCCL + add."""
         n = part32.numel()
         if 0 < n <= self.peer_capacity:
             ffi.call("jg_peer_allreduce_residual", self.handle, h.ptr, part32.ptr, n)
+        elif part32.ptr == self._partial_ptr and n <= self.twoshot_capacity and n % 4 == 0:
+            ffi.call("jg_peer_allreduce2_residual", self.handle, h.ptr, n)
         else:
             self.all_reduce_sum(part32)
             self.dev.call("jg_residual_add_f32", h.ptr, part32.ptr, n)
+
+    def split_rows(self, int8: bool) -> int:
+        """Most rows for which a row-parallel projection only pushes its partial sums and the next projection gathers
+        them (`linear_push` + the `*_gather` calls).  fp16 weights: the matrix-vector kernels' range, 2 rows.  int8
+        weights go through the tensor-core kernels, which have no such prologue (JG_TP_SPLIT=1 forces the CUDA-core
+        kernels for them, up to 8 rows)."""
+        if self.peer_capacity <= 0 or os.environ.get("JG_TP_SPLIT", "") == "0":
+            return 0
+        if int8:
+            return 8 if os.environ.get("JG_TP_SPLIT", "") == "1" else 0
+        return 2
+
+    def linear_push(self, x: Tensor, lin, rows: int) -> None:
+        """First half of h <- h + half(sum over ranks of lin(x)): project and push the partial sums, wait for nobody."""
+        ffi.call("jg_tp_linear_push", self.handle, x.ptr, lin.weight.ptr, lin.scale_ptr, rows, lin.out_features, lin.in_features)
 
     def fused_rows(self, int8: bool) -> int:
         """Most rows for which a row-parallel projection runs fused with its exchange (`linear_into_residual`):

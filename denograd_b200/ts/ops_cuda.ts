@@ -65,7 +65,7 @@ export const SYMBOLS = {
   jg_rope_kvwrite_rows: fn([ptr, ptr, i32, u64, u64, i32, u64, u64, i32, i32]),
   jg_attn_rows: fn([ptr, ptr, i32, u64, u64, u64, u64, i32, i32]),
   jg_attn_chunk: fn([ptr, ptr, i32, u64, u64, u64, u64, i32, i32, i32]),
-  jg_attn_decode_noalloc: fn([ptr, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32]),
+  jg_attn_decode_noalloc: fn([ptr, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32, i32]),
   jg_pos_advance: fn([ptr, u64, i32]),
   jg_dequant_i8_f16: fn([ptr, u64, u64, u64, 'i64', 'i64']),
   jg_fill_normal_f16: fn([ptr, u64, u64, u64, u64, f32]),
@@ -85,6 +85,15 @@ export const SYMBOLS = {
   jg_peer_allreduce_residual: fn([ptr, u64, u64, u64]),
   jg_peer_allreduce_max_u64: fn([ptr, u64, u64]),
   jg_linear_allreduce_residual: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
+  jg_tp_linear_push: fn([ptr, u64, u64, u64, i32, i32, i32]),
+  jg_tp_norm_linear: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32]),
+  jg_tp_norm_swiglu: fn([ptr, u64, u64, u64, u64, f32, u64, u64, u64, u64, i32, i32, i32]),
+  jg_tp_norm_logits_argmax: fn([ptr, u64, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32, i32]),
+  jg_comm_peer_partial: fn([ptr, buf, buf]),
+  jg_peer_allreduce2_residual: fn([ptr, u64, u64]),
+  jg_comm_init_all: fn([i32, buf, buf, buf]),
+  jg_comm_group_begin: fn([]),
+  jg_comm_group_end: fn([]),
   jg_linear_partial: fn([ptr, u64, u64, u64, u64, i32, i32, i32]),
   jg_residual_add_f32: fn([ptr, u64, u64, 'i64']),
   jg_norm_logits_argmax_shard: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32, i32]),

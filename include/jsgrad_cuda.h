@@ -203,16 +203,19 @@ int jg_attn_chunk(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint
  * places every buffer itself (jsgrad's memory planner / LRU allocator), or a loop that cannot take the device-wide
  * synchronisation of cudaMalloc / cudaFree.  The caller passes every input and output: the layer's K and V pools
  * ([n_pages][G][page_size][head_dim] fp16), the int32 block table [B][max_pages_per_seq], pos[B], qkv and out as in
- * jg_attn_decode (Q already rotated, K/V already stored).  Scores, split statistics and partial outputs live in a
+ * jg_attn_decode (Q already rotated, K/V already stored), and n_pages, the number of pages the two pools hold: the
+ * block table is the caller's and nobody validated it, so an entry outside [0, n_pages) is not followed — that
+ * position reads as a row of zeros, like an unwritten one.  Scores, split statistics and partial outputs live in a
  * fixed 8 MiB array inside the library image (held by every GPU that loads the library, until the process exits);
  * shapes that need more are rejected with JG_EINVAL:
  *     4*B*H*(max_pages_per_seq*page_size) + 4*B*H*n_split*(2 + head_dim) + 4*B*G  bytes (each part rounded to 256).
- * The first call on a device looks up the array's device address; make that call before any stream capture begins.
+ * The first call on a device looks up the array's device address; make that call before any stream capture begins
+ * (a first call made during jg_graph_begin .. jg_graph_end is rejected with JG_EINVAL).
  * All calls share the array, which keeps the previous call's contents (the call clears the part that must start at
  * zero): two calls that overlap on the GPU — different streams, or different devices' handles on one GPU — race. */
 int jg_attn_decode_noalloc(jg_dev* dev, uint64_t out, uint64_t qkv, uint64_t k_layer, uint64_t v_layer,
                            uint64_t block_table, uint64_t pos, int32_t B, int32_t H, int32_t G, int32_t head_dim,
-                           int32_t page_size, int32_t max_pages_per_seq, int32_t n_split);
+                           int32_t page_size, int32_t max_pages_per_seq, int32_t n_split, int32_t n_pages);
 
 /* pos[b] += 1 for b < B (the host-side `start_pos++` of the decode loop, jsgrad/models/llama3.ts:284-295,
  * kept on the device so a captured step can be replayed without host input). */
@@ -235,7 +238,7 @@ int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count);  /* greed
  * h[i] <- h[i] + half(sum over ranks of part32[i]) in one launch: each partial sum is stored, paired with the number
  * of the exchange, into every peer's buffer with one 8-byte store; the peers' entries are awaited on this rank's own
  * buffer (bounded: JG_ETIMEDOUT at the next synchronisation if a peer never arrives; JG_PEER_TIMEOUT_MS, default
- * 20000) and added in rank order.  All ranks must issue the same sequence of peer reductions.
+ * 5000) and added in rank order.  All ranks must issue the same sequence of peer reductions.
  * jg_comm_peer_capacity reports the largest n (0 while the peer path is not open). */
 int jg_comm_peer_export(jg_comm* comm, void* handle64);
 int jg_comm_peer_open(jg_comm* comm, const void* handles);
@@ -244,10 +247,41 @@ int jg_peer_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t part32, uint6
 int jg_peer_allreduce_max_u64(jg_comm* comm, uint64_t keys, uint64_t n);
 /* A row-parallel Linear (this rank holds a K-slice of W, nn/index.ts:411) fused with that exchange and the residual
  * add: h <- h + half(sum over ranks of x . W^T) in one launch per rank, for up to 8 rows.  CTA c of every rank owns
- * the same output rows: it stores its partial sums into the peers' buffers, raises one flag per peer, waits (bounded)
- * for the peers' CTA c and finishes its rows. */
+ * the same output rows: it stores its partial sums, each paired with the exchange number, into the peers' buffers,
+ * waits (bounded) for the peers' entries of its rows and finishes them. */
 int jg_linear_allreduce_residual(jg_comm* comm, uint64_t h, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N,
                                  int32_t K);
+/* The same all-reduce cut in two so that no kernel sits waiting for another rank (up to 8 rows, M * N <= 32768):
+ * jg_tp_linear_push is the row-parallel Linear whose epilogue stores the partial sums into every rank's buffer and
+ * returns at once; the projection that consumes the sum — the next RMSNorm + Linear of the block
+ * (jsgrad/models/llama.ts:125-126: ffn_norm -> w1/w3 after wo, the next block's attention_norm -> wq|wk|wv after w2,
+ * norm -> output after the last block, :210) — adds the ranks' entries in rank order in its prologue (bounded wait),
+ * rounds once, adds the residual stream h_in and leaves the new stream in h_out (a different buffer), then normalises
+ * and projects as jg_norm_linear / jg_norm_swiglu / jg_norm_logits_argmax_shard do.  Every push must be followed, on
+ * every rank, by exactly one of the three consuming calls (same M, K = the push's N) before any other exchange. */
+int jg_tp_linear_push(jg_comm* comm, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K);
+int jg_tp_norm_linear(jg_comm* comm, uint64_t y, uint64_t h_out, uint64_t h_in, uint64_t norm_w, float eps, uint64_t w,
+                      uint64_t scale, int32_t M, int32_t N, int32_t K);
+int jg_tp_norm_swiglu(jg_comm* comm, uint64_t y, uint64_t h_out, uint64_t h_in, uint64_t norm_w, float eps, uint64_t w_gate,
+                      uint64_t s_gate, uint64_t w_up, uint64_t s_up, int32_t M, int32_t N, int32_t K);
+int jg_tp_norm_logits_argmax(jg_comm* comm, uint64_t logits, uint64_t key, uint64_t h_out, uint64_t h_in, uint64_t norm_w,
+                             float eps, uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K,
+                             int32_t row_offset);
+/* Larger sums (a batch of decode rows, a short prompt chunk; n <= 262144 values, n % 4 == 0) as a two-shot exchange:
+ * jg_linear_partial writes this rank's fp32 partial sums into the region jg_comm_peer_partial names (part of the
+ * exchange buffer, readable by the peers); jg_peer_allreduce2_residual then has each rank add 1/world of the values
+ * over all ranks (plain peer loads, rank order), round, add the residual and send the finished fp16 values to every
+ * peer: h[i] <- h[i] + half(sum over ranks of partial[i]). */
+int jg_comm_peer_partial(jg_comm* comm, uint64_t* ptr, uint64_t* floats);
+int jg_peer_allreduce2_residual(jg_comm* comm, uint64_t h, uint64_t n);
+/* All ranks in ONE process, the reference engine's own threading model (one JS thread drives every device:
+ * Tensor.shard, jsgrad/tensor.ts:676-687; jsgrad/models/llama3.ts:239-249): devs[r] becomes rank r, out[r] its
+ * communicator.  The exchange buffers are addressed directly (cudaDeviceEnablePeerAccess), so no id and no handles
+ * are exchanged and jg_comm_peer_export / _open are not used.  NCCL collectives issued for several ranks by one
+ * thread must be bracketed by jg_comm_group_begin / jg_comm_group_end (ncclGroupStart / ncclGroupEnd). */
+int jg_comm_init_all(int32_t n, jg_dev** devs, const char* nccl_path, jg_comm** out);
+int jg_comm_group_begin(void);
+int jg_comm_group_end(void);
 /* y32[m][n] = sum_k x[m][k] W[n][k] left in fp32 (this rank's K-slice of a row-parallel Linear, nn/index.ts:411). */
 int jg_linear_partial(jg_dev* dev, uint64_t y32, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K);
 /* h <- h + half(p32): rounding + residual add of jsgrad/models/llama.ts:125-126 after the all-reduce. */
@@ -257,8 +291,13 @@ int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint
                                 uint64_t w, uint64_t scale, int32_t M, int32_t V_local, int32_t K, int32_t row_offset);
 
 /* Int8Linear's dequantised matrix (jsgrad/models/llama3.ts:35: weight.cast(half) * scale, fp16 [N][K]) written out
- * once, so that a call with many rows can use the fp16 tensor-core projection on it.  The projection entry points
- * notice a weight pointer inside a recently written copy and do not read it ahead of their dependency wait. */
+ * once, so that a call with many rows can use the fp16 tensor-core projection on it.
+ * Weights written on the device: the tensor-core projections start loading weight tiles while the preceding launch
+ * is still draining.  The library remembers the destinations of its own last 16 device-side writes since the stream
+ * was last synchronised (this function, the jg_fill_* family, jg_linear / jg_norm_linear outputs, jg_copy, jg_memset,
+ * jg_copyin_async) and holds those loads back when a weight pointer falls inside one of them.  A matrix written in
+ * any other way (another stream, more than 16 launches ago without a synchronisation in between) needs a
+ * jg_device_sync before it is used as `w`. */
 int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t N, int64_t K);
 
 /* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the

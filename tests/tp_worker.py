@@ -89,6 +89,14 @@ def missing_peer(dev, tp, rank: int, work: str) -> None:
         dev.call("jg_fill_const_f16", z.ptr, 8, 2.0)
         dev.synchronize()
         usable = bool((z.numpy() == 2).all())
+        with open(os.path.join(work, "rank0_done"), "w") as f:  # nothing of rank 0 addresses rank 1's memory any more
+            f.write("1")
+    else:
+        # rank 1 has nothing in flight and launches nothing more, but it stays alive — its exchange buffer is mapped
+        # into rank 0, whose abandoned exchange still stores into it — until rank 0 is through (host-side wait, bounded)
+        deadline = time.time() + 60
+        while not os.path.exists(os.path.join(work, "rank0_done")) and time.time() < deadline:
+            time.sleep(0.05)
     np.savez(os.path.join(work, f"out_{rank}.npz"), ok_first=ok_first, status=status, usable=usable)
 
 
