@@ -26,6 +26,9 @@
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 
 typedef _Float16 h16;
 
@@ -462,6 +465,23 @@ ORC_API void orc_model_destroy(orc_model* m) {
 ORC_API void orc_model_set_weight(orc_model* m, int layer, int which, const void* w, const void* scale) {
   if (layer < 0) { m->glob_w[which] = w; m->glob_s[which] = scale; }
   else { m->layer_w[(size_t)layer * ORC_PER_LAYER + which] = w; m->layer_s[(size_t)layer * ORC_PER_LAYER + which] = scale; }
+}
+/* Thread count of the OpenMP loops (the reference's generated C is single-threaded, jsgrad/renderer/cstyle.ts:206; the
+ * loops over output rows here are split over threads only to make the checker usable at full width).  A caller that
+ * times the checker sets the count explicitly instead of inheriting OMP_NUM_THREADS from a launcher. */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n >= 1) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+ORC_API int orc_max_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
 }
 ORC_API const uint16_t* orc_model_table(orc_model* m) { return (const uint16_t*)m->table; }
 ORC_API uint16_t* orc_model_cache(orc_model* m) { return (uint16_t*)m->cache; }

@@ -64,6 +64,7 @@ def lib() -> C.CDLL:
             "orc_model_set_weight": (None, [vp, i32, i32, vp, vp]),
             "orc_model_table": (vp, [vp]),
             "orc_model_cache": (vp, [vp]),
+            "orc_set_threads": (None, [i32]), "orc_max_threads": (i32, []),
             "orc_model_forward": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
             "orc_synth_normal_f16": (None, [u64, u64, u64, f32, vp]),
             "orc_synth_uniform_i8": (None, [u64, u64, u64, vp]),
@@ -76,6 +77,12 @@ def lib() -> C.CDLL:
             fn.restype, fn.argtypes = res, args
         _lib = L
     return _lib
+
+
+def set_threads(n: int) -> int:
+    """Thread count of the checker's OpenMP loops from now on; returns the count in force."""
+    lib().orc_set_threads(int(n))
+    return int(lib().orc_max_threads())
 
 
 def _p(a: np.ndarray | None):
@@ -257,6 +264,15 @@ class OracleModel:
         n = 2 * self.cfg.max_context * hd
         buf = (C.c_uint16 * n).from_address(lib().orc_model_table(self._m))
         return np.frombuffer(buf, dtype=np.float16).reshape(2 * self.cfg.max_context, hd // 2, 2)
+
+    def cache(self) -> np.ndarray:
+        """The KV cache as a writable fp16 view [L][2][B][max_context][G][hd] (timing runs fill it with stand-in rows
+        instead of computing a long prompt)."""
+        c = self.cfg
+        hd = c.dim // c.n_heads
+        shape = (c.n_layers, 2, c.max_batch, c.max_context, c.n_kv_heads, hd)
+        buf = (C.c_uint16 * int(np.prod(shape))).from_address(lib().orc_model_cache(self._m))
+        return np.frombuffer(buf, dtype=np.float16).reshape(shape)
 
     def forward(self, tokens, start_pos: int, want_hidden: bool = False):
         tokens = np.ascontiguousarray(tokens, dtype=np.int32)

@@ -418,6 +418,74 @@ def test_peer_exchange_entry_points_with_a_single_rank(dev):
     ffi.call("jg_peer_allreduce_max_u64", tp.handle, kt.ptr, keys.size)
     assert (kt.numpy() == keys).all()
     dev.synchronize()
+    tp.close()  # frees the exchange buffer: a later communicator on this device starts afresh
+
+
+def test_weights_written_just_before_a_projection_are_seen(dev):
+    """A weight matrix filled by one of the library's kernels and used by the very next call, with no synchronisation
+    in between: the tensor-core projections, which load weight tiles ahead of their dependency wait, must hold those
+    loads back.  The buffer is reused with another seed so that a stale read would show."""
+    M, N, K = 6, 256, 1024
+    rng = np.random.default_rng(3)
+    x = (rng.standard_normal((M, K)) * 0.5).astype(np.float16)
+    xt = Tensor(x, device=dev)
+    w = Tensor.empty((N, K), "float16", dev)
+    y = Tensor.empty((M, N), "float16", dev)
+    for seed in (101, 202, 303):
+        dev.call("jg_fill_normal_f16", w.ptr, seed, 0, N * K, 0.05)
+        dev.call("jg_linear", y.ptr, xt.ptr, w.ptr, 0, 0, M, N, K)  # 6 rows: tcgen05 kernel
+        want = O.linear_f16(x, O.synth_normal_f16(seed, N * K, 0.05).reshape(N, K))
+        assert_reduction_close(y.numpy(), want, max_ulp=1, max_frac=0.08, what=f"projection right after fill, seed {seed}")
+    # the same with a projection's output used as the next projection's weights
+    a = Tensor((rng.standard_normal((N, K)) * 0.05).astype(np.float16), device=dev)
+    b = Tensor((rng.standard_normal((K, K)) * 0.05).astype(np.float16), device=dev)
+    w2 = Tensor.zeros((N, K), "float16", dev)
+    dev.synchronize()
+    dev.call("jg_linear", w2.ptr, a.ptr, b.ptr, 0, 0, N, K, K)   # w2 = a . b^T, written by a kernel ...
+    dev.call("jg_linear", y.ptr, xt.ptr, w2.ptr, 0, 0, M, N, K)  # ... and read as weights by the next one
+    w2_host = w2.numpy()
+    assert_reduction_close(y.numpy(), O.linear_f16(x, w2_host), max_ulp=1, max_frac=0.08, what="projection over a fresh output")
+
+
+def test_rows_mapped_to_a_missing_sequence_are_skipped(dev):
+    """A row->sequence entry outside the block table is never followed: the row's K/V are not stored, its attention
+    output is left alone, and the cache pages of the real sequences stay as they were."""
+    rng = np.random.default_rng(12)
+    H, G, hd, B, max_ctx = 4, 2, 64, 2, 128
+    kv = KVCache(dev, 1, H, G, hd, max_ctx, B, page_size=16)
+    freqs = precompute_freqs_cis(hd, 2 * max_ctx, 500000.0, dev)
+    stride = (H + 2 * G) * hd
+    R = 4
+    rows = (rng.standard_normal((R, stride)) * 0.7).astype(np.float16)
+    qkv = Tensor(rows.copy(), device=dev)
+    pos = Tensor(np.array([0, 0, 1, 1], np.int32), device=dev)
+    good = Tensor(np.array([0, 1, 0, 1], np.int32), device=dev)
+    bad = Tensor(np.array([0, 7, -1, 1], np.int32), device=dev)  # rows 1 and 2 name sequences that do not exist
+    out_good = Tensor.zeros((R, H * hd), "float16", dev)
+    dev.call("jg_rope_kvwrite_rows", kv.handle, 0, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, good.ptr, R, H)
+    dev.call("jg_attn_rows", kv.handle, 0, out_good.ptr, qkv.ptr, pos.ptr, good.ptr, R, H)
+    want = out_good.numpy()
+    # second cache, same rows, with the bad map: rows 0 and 3 behave as before, 1 and 2 leave no trace
+    kv2 = KVCache(dev, 1, H, G, hd, max_ctx, B, page_size=16)
+    qkv2 = Tensor(rows.copy(), device=dev)
+    sentinel = np.full((R, H * hd), 3.0, np.float16)
+    out_bad = Tensor(sentinel.copy(), device=dev)
+    dev.call("jg_rope_kvwrite_rows", kv2.handle, 0, qkv2.ptr, freqs.ptr, freqs.shape[0], pos.ptr, bad.ptr, R, H)
+    dev.call("jg_attn_rows", kv2.handle, 0, out_bad.ptr, qkv2.ptr, pos.ptr, bad.ptr, R, H)
+    got = out_bad.numpy()
+    assert (got[0].view(np.uint16) == want[0].view(np.uint16)).all()
+    assert (got[1] == 3.0).all() and (got[2] == 3.0).all(), "a skipped row's output was written"
+    # row 3 (sequence 1, position 1) now sees a zero K/V at position 0, where row 1 was skipped: compare with the checker
+    q_rot = qkv2.numpy()[3, :H * hd].reshape(1, 1, H, hd)
+    k_ref = np.zeros((1, max_ctx, G, hd), np.float16)
+    v_ref = np.zeros_like(k_ref)
+    k_ref[0, 1] = O.rope(rows[3, H * hd:(H + G) * hd].reshape(1, G, hd), freqs.numpy(), [1])[0]
+    v_ref[0, 1] = rows[3, (H + G) * hd:].reshape(G, hd)
+    assert_reduction_close(got[3:4], O.attention(q_rot, k_ref, v_ref, 1).reshape(1, H * hd), max_ulp=2, max_frac=0.2, what="row after a skipped one")
+    # the skipped rows' projections are untouched (Q not rotated)
+    assert (qkv2.numpy()[1] == rows[1]).all() and (qkv2.numpy()[2] == rows[2]).all()
+    kv.close()
+    kv2.close()
 
 
 def test_int8_dequantised_copy_is_bit_exact(dev):
