@@ -284,7 +284,7 @@ class Rig:
 
     def llama(self, model: str, quant: str, max_ctx: int, max_batch: int, n_layers=None, args=None, tied=None):
         from denograd_b200.llama3 import Llama3
-        return Llama3(size=model, quantize=quant, max_context=max_ctx, max_batch=max_batch, device=self.dev_name,
+        return Llama3(size=model, quantize=quant, max_context=max_ctx, max_batch=max_batch, device=self.dev_name, temperature=0.0,
                       n_layers=n_layers, tp=self.tp, args=args or {}, tied_output=tied).load_synthetic()
 
     def release(self):

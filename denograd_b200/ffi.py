@@ -69,6 +69,7 @@ SIGNATURES: dict[str, list] = {
     "jg_norm_logits_argmax": [_vp, _u64, _u64, _u64, _u64, _f32, _u64, _u64, _i32, _i32, _i32],
     "jg_argmax_finalize": [_vp, _u64, _u64, _i32],
     "jg_argmax": [_vp, _u64, _u64, _i32, _i32],
+    "jg_sample": [_vp, _u64, _u64, _u64, _u64, _i32, _i32, _f32, _i32, _f32, _f32, _f32],
     "jg_freqs_cis": [_vp, _u64, _i32, _i32, _f64],
     "jg_kvcache_create": [_vp, _P(KvDesc), _P(_vp)],
     "jg_kvcache_destroy": [_vp],

@@ -224,14 +224,35 @@ class TransformerBlock:
     __call__ = call
 
 
-def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float) -> Tensor:
-    """Greedy branch of `sample` (jsgrad/models/llama.ts:131-137): argmax with the lowest index among equals, per
-    row.  The stochastic branches (top-k / top-p / alpha penalties) are not part of this device's path."""
-    if temp >= 1e-6:
-        raise NotImplementedError("only temperature < 1e-6 (greedy) is implemented on the CUDA device path")
-    rows = logits.numel() // logits.shape[-1]
-    out = Tensor.empty((rows,), "int32", logits.dev)
-    logits.dev.call("jg_argmax", out.ptr, logits.ptr, rows, logits.shape[-1])
+_alpha_counter: dict[tuple, Tensor] = {}  # the reference keeps one module-level counter (jsgrad/models/llama.ts:130)
+
+
+def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float, u: Tensor | None = None,
+           out: Tensor | None = None) -> Tensor:
+    """`sample` (jsgrad/models/llama.ts:131-185) per row of fp16 logits [rows, V]: argmax with the lowest index among
+    equals when temp < 1e-6, else alpha penalties, softmax(logits / temp), top-k, approximate top-p and the multinomial
+    draw in one kernel.  `u`: float32 [rows] uniform samples for the draw; by default they come from the restated
+    Tensor.rand stream (denograd_b200.rand, seeded by rand.manual_seed)."""
+    V = logits.shape[-1]
+    rows = logits.numel() // V
+    if p < 0 or p > 1:
+        raise ValueError("p must be between 0 and 1")
+    if k < 0 or k > V:
+        raise ValueError("k must be between 0 and numel")
+    out = out if out is not None else Tensor.empty((rows,), "int32", logits.dev)
+    if temp < 1e-6:
+        logits.dev.call("jg_argmax", out.ptr, logits.ptr, rows, V)
+        return out
+    if u is None:
+        from . import rand
+        u = Tensor(rand.rand(rows, logits.dev.device), device=logits.dev)
+    counter_ptr = 0
+    if af or ap:
+        key = (logits.dev.device, rows, V)
+        if key not in _alpha_counter:
+            _alpha_counter[key] = Tensor.zeros((rows, V), "int32", logits.dev)
+        counter_ptr = _alpha_counter[key].ptr
+    logits.dev.call("jg_sample", out.ptr, logits.ptr, u.ptr, counter_ptr, rows, V, float(temp), int(k), float(p), float(af), float(ap))
     return out
 
 
@@ -433,8 +454,6 @@ class Transformer:
         tcgen05 kernel or the weights are int8): one pass over the weights per chunk, every row
         attending to the cache up to its own position — what the reference's additive causal mask (:208) computes.
         Returns the greedy next token of every batch row after the last position ([B] int32)."""
-        if temperature >= 1e-6:
-            raise NotImplementedError("only greedy decoding (temperature < 1e-6) is implemented on the CUDA device path")
         toks = tokens.numpy() if isinstance(tokens, Tensor) else np.asarray(tokens, dtype=np.int32)
         B, S = toks.shape
         if start_pos + S > self.max_context:
@@ -445,12 +464,21 @@ class Transformer:
             sc = max(1, max_rows // B)
             for s0 in range(0, S, sc):
                 self._forward_rows(toks[:, s0:s0 + sc], start_pos + s0, last=(s0 + sc >= S))
-            return ws.next_tokens
+            return self._pick(ws, temperature, top_k, top_p, alpha_f, alpha_p)
         for s in range(S):
             ws.tokens.assign(toks[:, s])
             ws.pos.assign(np.full((B,), start_pos + s, np.int32))
             self._step(ws)
-        return ws.next_tokens
+        return self._pick(ws, temperature, top_k, top_p, alpha_f, alpha_p)
+
+    def _pick(self, ws: _Workspace, temperature: float, top_k: int, top_p: float, alpha_f: float, alpha_p: float) -> Tensor:
+        """The token of the last step: the greedy pick the logits kernel already made, or — temperature >= 1e-6 —
+        `sample` over the step's logits (jsgrad/models/llama.ts:212)."""
+        if temperature < 1e-6:
+            return ws.next_tokens
+        if self._tp is not None:
+            raise NotImplementedError("stochastic sampling over a vocabulary-sharded output layer: gather the logits first")
+        return sample(ws.logits, temperature, top_k, top_p, alpha_f, alpha_p, out=ws.next_tokens)
 
     def _max_chunk_rows(self) -> int:
         """Rows one projection call takes: 64 on the mma.sync kernel (int8 weights, or fp16 shapes off the tile grid),
@@ -536,8 +564,6 @@ class Transformer:
         toks = tokens.numpy() if isinstance(tokens, Tensor) else np.asarray(tokens, dtype=np.int32)
         B, S = toks.shape
         if S == 1 and self._jit_enabled and start_pos != 0:
-            if temperature >= 1e-6:
-                raise NotImplementedError("only greedy decoding (temperature < 1e-6) is implemented on the CUDA device path")
             if start_pos + 1 > self.max_context:
                 raise ValueError(f"start_pos {start_pos} + 1 exceeds max_context {self.max_context}")
             ws = self._workspace(B)
@@ -546,7 +572,7 @@ class Transformer:
             if B not in self._forward_jit:
                 self._forward_jit[B] = TinyJit(lambda: self._step(ws), self.dev)
             self._forward_jit[B].call()
-            return ws.next_tokens
+            return self._pick(ws, temperature, top_k, top_p, alpha_f, alpha_p)
         return self.forward(toks, start_pos, temperature, top_k, top_p, alpha_f, alpha_p)
 
     __call__ = call

@@ -1,7 +1,7 @@
 """Llama3 driver on the CUDA device — Python mirror of jsgrad/models/llama3.ts (MODEL_PARAMS :119-132, the Llama3
-class :170-338) for the parts on the forward path: construction per size / quantisation, weight loading into the
-device, token-at-a-time prefill and greedy generation.  Tokenizer, chat templating and checkpoint download are not
-part of this path (the workloads use seeded token ids and seeded weights).
+class :170-338): construction per size / quantisation with the reference's defaults, weight loading into the device,
+prefill with prefix reuse, the chat loop with stop tokens and usage accounting, and greedy generation for the seeded
+workloads.  Checkpoint download is not part of this path (no network); the tokenizer's vocabulary file is passed in.
 """
 from __future__ import annotations
 
@@ -40,14 +40,18 @@ class Llama3Usage:
 @dataclass
 class Llama3:
     """``Llama3(size=..., quantize=...)`` builds the Transformer with the reference's class injection
-    (Int8Linear / Int8Embedding for 'int8', jsgrad/models/llama3.ts:190-200).  ``temperature`` defaults to 0 here:
-    only the greedy branch of `sample` runs on this device (the reference's default of 0.95 selects the stochastic
-    branch, which is outside this path)."""
+    (Int8Linear / Int8Embedding for 'int8', NF4Linear(64) for 'nf4': jsgrad/models/llama3.ts:190-200) and its defaults:
+    temperature 0.95, top_k 0, top_p 0, alpha_f 0, alpha_p 0, max_context 8192.  Greedy decoding, which the benchmark
+    workloads prescribe, is ``temperature=0``."""
     size: str = "1B"
-    quantize: str | None = "float16"  # 'float16' | 'int8'
+    quantize: str | None = "float16"  # 'float16' | 'int8' | 'nf4'
     max_context: int = 8192
     device: str | None = None
-    temperature: float = 0.0
+    temperature: float = 0.95
+    top_k: int = 0
+    top_p: float = 0.0
+    alpha_f: float = 0.0
+    alpha_p: float = 0.0
     max_batch: int = 1
     page_size: int = 64
     fused: bool = True
@@ -57,6 +61,7 @@ class Llama3:
     tp: object | None = None  # denograd_b200.multi.TensorParallel: this process is one rank of a sharded model
     args: dict = field(default_factory=dict)
     last_seen_toks: list = field(default_factory=list)
+    tokenizer: object | None = None  # denograd_b200.tokenizer.Tokenizer, needed by _system / chat only
 
     def __post_init__(self):
         if self.quantize not in ("float16", "int8", None):
@@ -119,19 +124,82 @@ class Llama3:
     def reset(self) -> None:
         self.start_pos, self.last_seen_toks = 0, []
 
-    def _prefill(self, toks: np.ndarray) -> Tensor:
-        """Feed prompt tokens one position at a time (Llama3._prefill, jsgrad/models/llama3.ts:307-311); returns the
-        greedy token after the last prompt position.  toks: int32 [B, n]."""
+    def _prefill(self, toks, batched: bool = False) -> Tensor | None:
+        """Llama3._prefill (jsgrad/models/llama3.ts:298-312).  toks: a list of ids (one conversation) or int32 [B, n].
+        At start_pos 0 the part of the prompt that equals what this object saw last is skipped — its K/V rows are
+        still in the cache — exactly under the reference's rule: only when one of the two token lists is a prefix of
+        the other.  The rest is fed one position per call as the reference does, or, with `batched`, in one
+        multi-position forward.  Returns the token picked after the last position fed (None if nothing was fed)."""
+        arr = np.asarray(toks, dtype=np.int32)
+        if arr.ndim == 1:
+            arr = arr[None, :]
+        if self.start_pos == 0 and arr.shape[0] == 1:
+            cur, last = arr[0].tolist(), list(self.last_seen_toks)
+            n = min(len(cur), len(last))
+            i = n if cur[:n] == last[:n] else 0
+            self.start_pos += i
+            self.last_seen_toks = cur
+            arr = arr[:, i:]
         out = None
-        for i in range(toks.shape[1]):
-            out = self.model.call(toks[:, i:i + 1], self.start_pos, self.temperature)
+        if arr.shape[1] == 0:
+            return out
+        if batched:
+            out = self.model.forward(arr, self.start_pos, self.temperature, self.top_k, self.top_p, self.alpha_f, self.alpha_p)
+            self.start_pos += arr.shape[1]
+            return out
+        for i in range(arr.shape[1]):
+            out = self.model.call(arr[:, i:i + 1], self.start_pos, self.temperature, self.top_k, self.top_p, self.alpha_f, self.alpha_p)
             self.start_pos += 1
         return out
+
+    def _call(self, tok: int) -> int:
+        """One token in, the sampled next token out (Llama3._call, jsgrad/models/llama3.ts:334-337)."""
+        res = self.model.call(np.array([[tok]], np.int32), self.start_pos, self.temperature, self.top_k, self.top_p,
+                              self.alpha_f, self.alpha_p)
+        return int(res.numpy()[0])
+
+    def _system(self, msg: str = "You are an helpful assistant.") -> None:
+        """Llama3._system (jsgrad/models/llama3.ts:266-269): begin-of-text + the system turn go through the model."""
+        if self.tokenizer is None:
+            raise ValueError("no tokenizer: pass tokenizer=Tokenizer.llama(path) (the vocabulary file is not bundled)")
+        self._prefill([self.tokenizer.bos_id, *self.tokenizer.encode_message("system", msg)], batched=True)
+
+    def chat(self, messages: list[dict], on_token=None, max_tokens: int | None = None) -> dict:
+        """Llama3.chat (jsgrad/models/llama3.ts:270-297): frame the turns, prefill all but the last prompt token, then
+        feed tokens back one by one until a stop token comes out.  Returns {'message', 'stop_reason', 'usage'}.  The
+        reference loops until a stop token; `max_tokens` and the context length bound the loop here
+        (stop_reason 'max_tokens' / 'max_context')."""
+        if self.tokenizer is None:
+            raise ValueError("no tokenizer: pass tokenizer=Tokenizer.llama(path) (the vocabulary file is not bundled)")
+        tk = self.tokenizer
+        toks = [t for m in messages for t in tk.encode_message(m["role"], m["content"])] + tk.encode_role("assistant")
+        st = time.perf_counter()
+        self._prefill(toks[:-1], batched=True)
+        usage = Llama3Usage(input_tokens=len(toks) - 1, time_to_first_token=time.perf_counter() - st)
+        last_tok, message = toks[-1], {"role": "assistant", "content": ""}
+        st = time.perf_counter()
+        while True:
+            if self.start_pos + 1 > self.max_context:
+                return {"message": message, "stop_reason": "max_context", "usage": usage}
+            tok = self._call(last_tok)
+            self.start_pos += 1
+            usage.output_tokens += 1
+            usage.tokens_per_second = usage.output_tokens / max(time.perf_counter() - st, 1e-9)
+            last_tok = tok
+            if tok in tk.stop_tokens:
+                return {"message": message, "stop_reason": "end_turn", "usage": usage}
+            token = tk.decode([tok])
+            message["content"] += token
+            if on_token is not None:
+                on_token({"message": message, "usage": usage, "token": token})
+            if max_tokens is not None and usage.output_tokens >= max_tokens:
+                return {"message": message, "stop_reason": "max_tokens", "usage": usage}
 
     def prefill(self, toks: np.ndarray) -> Tensor:
         """The whole prompt in one multi-position forward (Transformer.forward with S > 1, jsgrad/models/llama.ts:
         201-213) instead of one call per token; returns the greedy token after the last prompt position."""
-        out = self.model.forward(np.asarray(toks, dtype=np.int32), self.start_pos, self.temperature)
+        out = self.model.forward(np.asarray(toks, dtype=np.int32), self.start_pos, self.temperature, self.top_k, self.top_p,
+                                 self.alpha_f, self.alpha_p)
         self.start_pos += toks.shape[1]
         return out
 
@@ -139,11 +207,15 @@ class Llama3:
         """Greedy continuation through the public per-token API: every step copies the token ids to the device, runs
         the (graph-replayed) step and reads the chosen ids back — the `.item()` round trip of the reference's chat
         loop (jsgrad/models/llama3.ts:284-295,334-337).  prompt: int32 [B, n] -> int32 [B, max_new_tokens]."""
+        if self.temperature >= 1e-6:
+            raise ValueError("generate() is the greedy loop of the benchmark workloads: construct with temperature=0 "
+                             "(sampling runs through chat() / _call())")
         prompt = np.asarray(prompt, dtype=np.int32)
         if prompt.ndim == 1:
             prompt = prompt[None, :]
         B = prompt.shape[0]
         st = time.perf_counter()
+        self.last_seen_toks = []  # a seeded workload prompt is always fed whole
         tok = self._prefill(prompt).numpy()
         self.usage.time_to_first_token = time.perf_counter() - st
         out = np.empty((B, max_new_tokens), np.int32)

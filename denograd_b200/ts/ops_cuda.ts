@@ -54,6 +54,7 @@ export const SYMBOLS = {
   jg_norm_logits_argmax: fn([ptr, u64, u64, u64, u64, f32, u64, u64, i32, i32, i32]),
   jg_argmax_finalize: fn([ptr, u64, u64, i32]),
   jg_argmax: fn([ptr, u64, u64, i32, i32]),
+  jg_sample: fn([ptr, u64, u64, u64, u64, i32, i32, f32, i32, f32, f32, f32]),
   jg_freqs_cis: fn([ptr, u64, i32, i32, f64]),
   jg_kvcache_create: fn([ptr, buf, buf]),
   jg_kvcache_destroy: fn([ptr]),

@@ -137,6 +137,18 @@ int jg_argmax_finalize(jg_dev* dev, uint64_t tokens_out, uint64_t key, int32_t M
 /* Tensor.argmax over the last axis of fp16 [rows][n]: jsgrad/tensor.ts:2314-2320. */
 int jg_argmax(jg_dev* dev, uint64_t out_idx, uint64_t x, int32_t rows, int32_t n);
 
+/* `sample` beyond its greedy branch (jsgrad/models/llama.ts:131-185): alpha penalties (:142-147), NaN -> -inf, softmax
+ * of logits / temp (:150-153), k rounds of largest-probability-with-lowest-index (:160-167), the approximate top-p cut
+ * on those k (:171-173) and the multinomial draw (:176-179; Tensor.multinomial, jsgrad/tensor.ts:1164-1172).  The draw
+ * needs one uniform sample in [0, 1) per row, u[B] (float32, device) — what Tensor.rand delivers in the reference; the
+ * caller supplies it.  logits: fp16 [B][V] (widened to fp32 as jsgrad/models/llama.ts:210 does); tokens_out: int32 [B];
+ * alpha_counter: int32 [B][V] (the reference's module-level counter, zero-initialised by the caller; incremented at
+ * the chosen token) or 0 when af = ap = 0.  k = 0 draws from the whole distribution; k <= 512.  temp >= 1e-6 (below
+ * that `sample` is jg_argmax).  Every float32 sum is added in the order the reference's kernels add it, so the token
+ * is a function of (logits, u) only. */
+int jg_sample(jg_dev* dev, uint64_t tokens_out, uint64_t logits, uint64_t u, uint64_t alpha_counter, int32_t B, int32_t V,
+              float temp, int32_t k, float p, float af, float ap);
+
 /* precompute_freqs_cis cast to fp16: jsgrad/models/llama.ts:10-14,205. table: fp16 [end][head_dim/2][2]. */
 int jg_freqs_cis(jg_dev* dev, uint64_t table, int32_t head_dim, int32_t end, double theta);
 

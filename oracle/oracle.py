@@ -22,7 +22,7 @@ TOK_EMB, OUTPUT, NORM = range(3)
 
 def build(force: bool = False) -> str:
     """Compile the checker with the committed Makefile; returns the library path."""
-    srcs = [os.path.join(_HERE, f) for f in ("llama_oracle.c", "synth.c", "Makefile")]
+    srcs = [os.path.join(_HERE, f) for f in ("llama_oracle.c", "sample_oracle.c", "synth.c", "Makefile")]
     stale = (not os.path.exists(_LIB_PATH)) or any(
         os.path.getmtime(s) > os.path.getmtime(_LIB_PATH) for s in srcs)
     if force or stale:
@@ -65,6 +65,10 @@ def lib() -> C.CDLL:
             "orc_model_table": (vp, [vp]),
             "orc_model_cache": (vp, [vp]),
             "orc_set_threads": (None, [i32]), "orc_max_threads": (i32, []),
+            "orc_sample": (i32, [vp, i32, f32, i32, f32, f32, f32, vp, f32]),
+            "orc_sum_f32": (f32, [vp, i32]),
+            "orc_threefry2x32": (u64, [u64, u64]),
+            "orc_threefry_rand_f32": (None, [C.c_uint32, C.c_uint32, C.c_uint32, u64, vp]),
             "orc_model_forward": (i32, [vp, vp, i32, i32, i32, vp, vp, vp]),
             "orc_synth_normal_f16": (None, [u64, u64, u64, f32, vp]),
             "orc_synth_uniform_i8": (None, [u64, u64, u64, vp]),
@@ -197,6 +201,28 @@ def swiglu(g, u) -> np.ndarray:
 def argmax_f16(x) -> int:
     x = _h(x)
     return int(lib().orc_argmax_f16(_p(x), x.size))
+
+
+def sample(logits, temp: float, k: int, p: float, af: float, ap: float, u: float, alpha_counter: np.ndarray | None = None) -> int:
+    """`sample` of jsgrad/models/llama.ts:131-185 on one row of float32 logits with the uniform sample `u`;
+    `alpha_counter` (int32 [n]) is updated in place when a penalty is active."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    if alpha_counter is not None:
+        assert alpha_counter.dtype == np.int32 and alpha_counter.flags["C_CONTIGUOUS"] and alpha_counter.size == logits.size
+    return int(lib().orc_sample(_p(logits), logits.size, temp, k, p, af, ap, _p(alpha_counter), u))
+
+
+def sum_f32(x) -> float:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    return float(lib().orc_sum_f32(_p(x), x.size))
+
+
+def threefry_rand(seed0: int, seed1: int, counter: int, num: int) -> np.ndarray:
+    """float32 [num] in [0, 1): the values one Tensor.rand call of `num` float32 elements produces
+    (jsgrad/tensor.ts:796-843) for the seed pair (device hash, Tensor._seed) and the device's counter."""
+    out = np.empty((num,), np.float32)
+    lib().orc_threefry_rand_f32(seed0 & 0xFFFFFFFF, seed1 & 0xFFFFFFFF, counter & 0xFFFFFFFF, num, _p(out))
+    return out
 
 
 # ---------------------------------------------------------------- seeded generator

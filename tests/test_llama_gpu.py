@@ -20,6 +20,7 @@ LOGIT_TOL = 2e-2
 
 
 def make(size="1B", args=None, **kw) -> Llama3:
+    kw.setdefault("temperature", 0)  # the workloads decode greedily
     return Llama3(size=size, args=args or {}, **kw).load_synthetic()
 
 
@@ -168,7 +169,7 @@ def test_load_state_dict_from_host_arrays():
     sd["tok_embeddings.weight"] = synth_weight("tok_embeddings", (TINY["vocab_size"], TINY["dim"]), False)[0]
     sd["output.weight"] = sd["tok_embeddings.weight"]
     sd["norm.weight"] = np.ones(TINY["dim"], np.float16)
-    a = Llama3(size="1B", args=TINY, max_context=64, tied_output=True).load_state_dict(sd)
+    a = Llama3(size="1B", args=TINY, max_context=64, tied_output=True, temperature=0).load_state_dict(sd)
     b = make("1B", args=TINY, max_context=64, tied_output=True)
     prompt = synth.prompt_tokens(5, TINY["vocab_size"], seed=8)
     assert (a.generate(prompt, 10) == b.generate(prompt, 10)).all()
@@ -315,7 +316,7 @@ def test_weights_from_a_sharded_safetensors_checkpoint(tmp_path, quant):
     index = tmp_path / "model.safetensors.index.json"
     index.write_text(_json.dumps({"weight_map": {k: ("model-00001-of-00002.safetensors" if i < half else
                                                       "model-00002-of-00002.safetensors") for i, k in enumerate(names)}}))
-    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=2, tied_output=True).load_weights(str(index))
+    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=2, tied_output=True, temperature=0).load_weights(str(index))
     sd = get_state_dict(llm.model)
     prompt = synth.prompt_tokens(6, p["vocab_size"], batch=2, seed=17)
     if quant == "float16":

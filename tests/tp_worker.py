@@ -50,12 +50,12 @@ def main() -> None:
     if quant == "missing-peer":
         missing_peer(dev, tp, rank, work)
         return
-    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
     ids = llm.generate(prompt, n_new)
     logits = llm.model.last_logits(batch)
     # the graph-replayed device loop must agree with the per-token API under sharding too
-    llm2 = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    llm2 = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     first = llm2._prefill(prompt).numpy()
     loop = llm2.model.decode_loop(first, llm2.start_pos, n_new - 1)
     np.savez(os.path.join(work, f"out_{rank}.npz"), ids=ids, logits=logits, offset=llm.model.vocab_offset,
