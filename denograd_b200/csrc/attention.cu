@@ -751,7 +751,7 @@ static int launch_attn_fused(jg_dev* dev, const AttnFusedArgs& a, int B, int cs,
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = dev->pdl ? 2 : 1;
+  cfg.numAttrs = (dev->pdl && dev->pdl_attn) ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
   if (e != cudaSuccess) return jg_cuda_fail(e, "attn_decode_fused", __FILE__, __LINE__);
   return jg_after_launch(dev, "attn_decode_fused");

@@ -151,14 +151,19 @@ JG_API int jg_allreduce_max_u64(jg_comm* comm, uint64_t buf, uint64_t count) {
 // every rank, so all ranks hold bit-identical sums) and applies the residual add of TransformerBlock.call
 // (jsgrad/models/llama.ts:125-126) in the same pass.  gemv.cu runs the same exchange inside the projection kernel for
 // up to 8 rows (jg_linear_allreduce_residual).  The max-reduction of the greedy keys uses data + one flag per peer.
-// Buffers alternate between two parities (of one exchange counter per rank, kept on the device so that graph replays
-// advance it): a rank can be at most one exchange ahead of a peer (it needs that peer's entries of the current exchange
+// Exchanges are numbered 1, 2, 3, ... identically on every rank.  The number is a device word (exchanges completed
+// before the current run of launches) plus the launch's ordinal within the run, which the host counts; the word is
+// advanced by a one-thread kernel that the library inserts at the borders of a graph capture (the whole run's count is
+// added at the end of the captured list, so every replay moves on by as many exchanges as it contains).  No kernel
+// spends a fence and an atomic on advancing a counter, and the number is known before the dependency wait.
+// Buffers alternate between the two parities of the exchange number: a rank can be at most one exchange ahead of a peer (it needs that peer's entries of the current exchange
 // to finish it, and the peer writes them only after its previous exchange has completed), so the slots a slow peer is
 // still reading are never overwritten.
 struct jg_peer {
   unsigned char* local;                   // this rank's buffer: slots [2][world][PEER_SLOT_FLOATS], then the flags
   unsigned char* mapped[PEER_MAX_WORLD];  // every rank's buffer as mapped here (own entry = local)
-  uint32_t* epoch;                        // [0] exchanges done so far, kept on the device (graph replays); [1] CTA ticket
+  uint32_t* epoch;                        // [0] exchanges completed before the current run of launches (device word)
+  uint32_t pending;                       // exchanges launched in the current run (host count)
   int* err;                               // device word: 0 = fine, 1 = a wait for a peer's flag ran out
   unsigned long long timeout_ns;
   bool open;
@@ -187,7 +192,7 @@ static void peer_release(jg_comm* comm) {
 __global__ void __launch_bounds__(256) peer_sum_residual_kernel(const PeerArgs a) {
   pdl_launch();
   pdl_wait();
-  const uint32_t epoch = a.epoch[0] + 1;  // advanced below by the last CTA of this launch to finish
+  const uint32_t epoch = a.epoch[0] + a.ord;
   const int parity = (int)(epoch & 1u);
   const long long stride = (long long)gridDim.x * blockDim.x, first = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   for (long long i = first; i < a.n; i += stride) {
@@ -206,14 +211,6 @@ __global__ void __launch_bounds__(256) peer_sum_residual_kernel(const PeerArgs a
     if (ok) a.h[i] = hadd1(a.h[i], __float2half_rn(sum));
   }
   if (!ok) atomicCAS(a.err, 0, 1);
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    __threadfence();
-    if (atomicAdd(&a.epoch[1], 1u) == gridDim.x - 1) {
-      a.epoch[1] = 0;
-      a.epoch[0] = epoch;
-    }
-  }
 }
 
 // keys <- max over ranks of keys (u64): data into the upper half of every peer's slot, one flag per peer, bounded wait.
@@ -221,8 +218,8 @@ __global__ void __launch_bounds__(256) peer_max_kernel(const PeerArgs a) {
   __shared__ int s_fail;
   const int tid = threadIdx.x;
   pdl_launch();
+  const uint32_t epoch = a.epoch[0] + a.ord;
   pdl_wait();
-  const uint32_t epoch = a.epoch[0] + 1;
   const int parity = (int)(epoch & 1u);
   if (tid == 0) s_fail = 0;
   for (long long i = tid; i < a.n; i += blockDim.x) {
@@ -256,8 +253,6 @@ __global__ void __launch_bounds__(256) peer_max_kernel(const PeerArgs a) {
       a.keys[i] = best;
     }
   }
-  __syncthreads();
-  if (tid == 0) { __threadfence(); a.epoch[0] = epoch; }  // single CTA
 }
 
 // h <- h + half(sum over ranks of partial), two-shot: for messages too large for every rank to send everything to
@@ -272,8 +267,8 @@ __global__ void __launch_bounds__(256) peer_sum2_residual_kernel(const PeerArgs 
   __shared__ int s_fail;
   const int tid = threadIdx.x, cta = blockIdx.x, nct = gridDim.x;
   pdl_launch();
+  const uint32_t epoch = a.epoch[0] + a.ord;
   pdl_wait();
-  const uint32_t epoch = a.epoch[0] + 1;
   const int parity = (int)(epoch & 1u);
   const int rank = a.rank, world = a.world;
   if (tid == 0) s_fail = 0;
@@ -333,14 +328,6 @@ __global__ void __launch_bounds__(256) peer_sum2_residual_kernel(const PeerArgs 
       }
     }
     if (!ok) atomicCAS(a.err, 0, 1);
-  }
-  __syncthreads();
-  if (tid == 0) {
-    __threadfence();
-    if (atomicAdd(&a.epoch[1], 1u) == gridDim.x - 1) {
-      a.epoch[1] = 0;
-      a.epoch[0] = epoch;
-    }
   }
 }
 
@@ -403,15 +390,36 @@ JG_API int jg_comm_peer_capacity(jg_comm* comm, uint64_t* floats) {
   return JG_OK;
 }
 
-int jg_peer_fill_args(jg_comm* comm, PeerArgs* a) {
+int jg_peer_fill_args(jg_comm* comm, PeerArgs* a, bool consume) {
   jg_dev* dev = comm->dev;
   JG_REQUIRE(dev->ordinal >= 0 && dev->ordinal < 64 && g_peer[dev->ordinal].open,
              "peer reduction: the peer buffers are not open (jg_comm_peer_export / jg_comm_peer_open)");
   jg_peer& p = g_peer[dev->ordinal];
+  JG_REQUIRE(!consume || p.pending > 0, "peer reduction: nothing has been pushed that this call could gather");
   for (int r = 0; r < comm->world; r++) a->buf[r] = p.mapped[r];
   a->epoch = p.epoch; a->err = p.err; a->timeout_ns = p.timeout_ns; a->rank = comm->rank; a->world = comm->world;
+  a->ord = consume ? p.pending : ++p.pending;
   dev->peer_pending = true;
   return JG_OK;
+}
+
+// One thread: the exchanges of the run that ends here are done; later launches number theirs from the new base.
+__global__ void peer_advance_kernel(uint32_t* base, uint32_t n) {
+  pdl_launch();
+  pdl_wait();
+  base[0] += n;
+}
+
+// Called by jg_graph_begin (before the capture starts) and jg_graph_end (as the last captured launch): fold the
+// exchanges launched so far into the device word, so that a captured list starts from ordinal 1 and every replay
+// advances the word by the number of exchanges it holds.
+int jg_peer_run_boundary(jg_dev* dev) {
+  if (dev->ordinal < 0 || dev->ordinal >= 64) return JG_OK;
+  jg_peer& p = g_peer[dev->ordinal];
+  if (p.epoch == nullptr || p.pending == 0) return JG_OK;
+  const uint32_t n = p.pending;
+  p.pending = 0;
+  return jg_launch(dev, "peer_advance", peer_advance_kernel, dim3(1), dim3(1), 0, p.epoch, n);
 }
 
 static int peer_launch(jg_comm* comm, int mode, uint64_t h, uint64_t part, uint64_t keys, long long n) {

@@ -20,6 +20,8 @@ struct jg_dev {
   void* pinned_stage;  // small page-locked staging area for jg_copyin of tiny payloads
   size_t pinned_stage_bytes;
   bool pdl;  // launch kernels with programmatic stream serialization (JG_PDL=0 turns it off)
+  bool pdl_cluster;  // ... also the thread-block-cluster launches of the gathering projections (JG_PDL_CLUSTER=1; default off)
+  bool pdl_attn;     // ... also the decode-attention cluster launches (JG_PDL_ATTN=1; default off)
   int* err_word;    // device word written by kernels whose bounded waits gave up (0 = fine); allocated on first use
   bool tc_pending;  // such kernels were launched since the word was last checked
   bool peer_pending;  // peer-memory reductions (comm.cu) were launched since their error word was last checked
@@ -118,7 +120,7 @@ static inline int jg_launch_cluster(jg_dev* dev, const char* name, void (*kern)(
     attr[na].val.clusterDim.z = 1;
     na++;
   }
-  if (dev->pdl) {
+  if (dev->pdl && (cluster_x <= 1 || dev->pdl_cluster)) {
     attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[na].val.programmaticStreamSerializationAllowed = 1;
     na++;

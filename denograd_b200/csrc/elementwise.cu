@@ -333,6 +333,50 @@ JG_API int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t sca
                    (const int8_t*)w, (const __half*)scale, n16, (int)(K / 16));
 }
 
+// NF4Linear's dequantised matrix (jsgrad/models/llama3.ts:88-94): element i of the flattened [out][in] matrix is
+// half(CODE[code_i] * scale[i / block]) with code_2j in the high nibble of byte j and code_2j+1 in the low one, the 16
+// code values rounded to fp16 first (:81).  One thread turns 16 packed bytes into 32 halves.
+__constant__ float c_nf4_code[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                     -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                     0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f,
+                                     0.33791524171829224f, 0.44070982933044434f, 0.5626170039176941f,
+                                     0.7229568362236023f, 1.0f};
+__global__ void dequant_nf4_f16_kernel(__half* __restrict__ dst, const uint8_t* __restrict__ w, const __half* __restrict__ scale,
+                                       long long n32, int block) {
+  __shared__ __half code[16];
+  if (threadIdx.x < 16) code[threadIdx.x] = __float2half_rn(c_nf4_code[threadIdx.x]);
+  pdl_launch();
+  pdl_wait();
+  __syncthreads();
+  for (long long c = blockIdx.x * (long long)blockDim.x + threadIdx.x; c < n32; c += (long long)gridDim.x * blockDim.x) {
+    const uint4 raw = ld_stream_128(reinterpret_cast<const uint4*>(w) + c);
+    const uint8_t* q = reinterpret_cast<const uint8_t*>(&raw);
+    __align__(16) __half o[32];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const long long e = c * 32 + 2 * i;  // blocks hold an even number of elements: both nibbles share a scale
+      const __half s = scale[e / block];
+      o[2 * i] = hmul1(code[q[i] >> 4], s);
+      o[2 * i + 1] = hmul1(code[q[i] & 15], s);
+    }
+#pragma unroll
+    for (int v = 0; v < 4; v++) reinterpret_cast<uint4*>(dst)[4 * c + v] = *reinterpret_cast<uint4*>(&o[8 * v]);
+  }
+}
+
+JG_API int jg_dequant_nf4_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t n, int32_t block) {
+  JG_ENTER(dev);
+  JG_REQUIRE(n > 0 && n % 32 == 0 && block >= 2 && block % 2 == 0 && n % block == 0,
+             "dequant_nf4_f16: n=%lld must be a multiple of 32 and of the (even) block size %d", (long long)n, block);
+  JG_REQUIRE(jg_aligned(dst, 16) && jg_aligned(w, 16) && jg_aligned(scale, 2), "dequant_nf4_f16: null or misaligned pointer");
+  const long long n32 = n / 32;
+  jg_mark_fresh(dev, dst, (uint64_t)n * 2);
+  long long blocks = (n32 + 255) / 256;
+  if (blocks > (long long)dev->sm_count * 16) blocks = (long long)dev->sm_count * 16;
+  return jg_launch(dev, "dequant_nf4_f16", dequant_nf4_f16_kernel, dim3((unsigned)blocks), dim3(256), 0, (__half*)dst,
+                   (const uint8_t*)w, (const __half*)scale, n32, (int)block);
+}
+
 // ------------------------------------------------------------------------------------------------ tensor-parallel helpers
 // h <- h + half(p): the residual add of TransformerBlock.call (jsgrad/models/llama.ts:125-126) applied to the fp32 sum
 // of a row-parallel projection after its all-reduce: one rounding of the full sum to fp16, then the fp16 add, exactly

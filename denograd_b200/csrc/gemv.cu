@@ -136,27 +136,29 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) jg_matvec_kernel(const GemvAr
     }
   }
 
-  // ---- everything below reads what the previous kernel wrote
-  pdl_wait();
-  // PEER: this exchange's number and buffer parity (the counter is advanced by the last CTA of this launch to finish);
-  // the partial sums land in this rank's own slot first
+  // PEER / PUSH / GATHER: the exchange's number (base + ordinal; the base word only changes between runs of launches,
+  // never while one is in flight, so it is read ahead of the dependency wait) and the buffer parity it selects
   uint32_t peer_epoch = 0;
   int peer_parity = 0;
-  float* peer_mine = nullptr;
-  if (EPI == EPI_PEER || EPI == EPI_PUSH) {
-    peer_epoch = a.peer.epoch[0] + 1;
+  if (EPI == EPI_PEER || EPI == EPI_PUSH || GATHER) {
+    peer_epoch = a.peer.epoch[0] + a.peer.ord;
     peer_parity = (int)(peer_epoch & 1u);
-    peer_mine = peer_slot(a.peer.buf[a.peer.rank], peer_parity, a.peer.rank);
   }
+
+  // ---- everything below reads what the previous kernel wrote
+  pdl_wait();
+  // PEER: the partial sums land in this rank's own slot first
+  float* peer_mine = nullptr;
+  if (EPI == EPI_PEER || EPI == EPI_PUSH) peer_mine = peer_slot(a.peer.buf[a.peer.rank], peer_parity, a.peer.rank);
 
   if (GATHER) {
     // ---- finish the exchange the preceding kernel of every rank started: h_out = h_in + half(sum over ranks), in
     //      rank order so that all ranks hold identical bits.  That kernel has completed on this rank (dependency wait
-    //      above), so the counter already carries the exchange's number; the peers' entries may still be in flight.
+    //      above) and carried the same exchange number; the peers' entries may still be in flight.
     //      Each CTA of the cluster reduces its slice (pairs of values) and writes the fp16 results into the
     //      activation rows of every CTA of the cluster.
-    const uint32_t ex = a.peer.epoch[0];
-    const int par = (int)(ex & 1u);
+    const uint32_t ex = peer_epoch;
+    const int par = peer_parity;
     const uint32_t cr = cluster_cta_rank(), cs = cluster_cta_count();
     const int pairs = a.M * K / 2;
     const int per = (pairs + (int)cs - 1) / (int)cs;
@@ -260,7 +262,12 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) jg_matvec_kernel(const GemvAr
   auto finish = [&](int row, int m, float s_a, float s_b) {
     const size_t o = (size_t)m * N + (size_t)row;
     if (EPI == EPI_PARTIAL) { a.y32[o] = s_a; return; }
-    if (EPI == EPI_PEER) { peer_mine[o] = s_a; return; }
+    if (EPI == EPI_PEER) {  // own slot (read back in the tail) and, right away, the peers' buffers: the NVLink crossing
+      peer_mine[o] = s_a;   // overlaps whatever this CTA still has to compute
+      for (int p = 0; p < a.peer.world; p++)
+        if (p != a.peer.rank) peer_ll_store(peer_ll(a.peer.buf[p], peer_parity, a.peer.rank) + o, s_a, peer_epoch);
+      return;
+    }
     if (EPI == EPI_PUSH) {  // flag-in-data entry for every rank, this one included; nothing is awaited here
       for (int p = 0; p < a.peer.world; p++) peer_ll_store(peer_ll(a.peer.buf[p], peer_parity, a.peer.rank) + o, s_a, peer_epoch);
       return;
@@ -375,12 +382,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) jg_matvec_kernel(const GemvAr
     bool ok = true;
     for (int i = tid; i < nr * a.M; i += GEMV_THREADS) {
       const size_t o = (size_t)(i / nr) * N + r_lo + (i % nr);
-      const float v = peer_mine[o];
-      for (int p = 0; p < world; p++)
-        if (p != rank) peer_ll_store(peer_ll(a.peer.buf[p], peer_parity, rank) + o, v, peer_epoch);
-    }
-    for (int i = tid; i < nr * a.M; i += GEMV_THREADS) {
-      const size_t o = (size_t)(i / nr) * N + r_lo + (i % nr);
       float sum = 0.f;
       for (int r = 0; r < world && ok; r++) {  // rank order on every rank: identical sums everywhere
         float v = peer_mine[o];
@@ -390,16 +391,6 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) jg_matvec_kernel(const GemvAr
       if (ok) a.y[o] = hadd1(a.residual[o], __float2half_rn(sum));
     }
     if (!ok) atomicCAS(a.peer.err, 0, 1);
-  }
-  if (EPI == EPI_PEER || EPI == EPI_PUSH) {
-    __syncthreads();
-    if (tid == 0) {
-      __threadfence();
-      if (atomicAdd(&a.peer.epoch[1], 1u) == gridDim.x - 1) {  // every CTA of the launch has read the counter by now
-        a.peer.epoch[1] = 0;
-        a.peer.epoch[0] = peer_epoch;
-      }
-    }
   }
 
   if (EPI == EPI_LOGITS) {
@@ -490,6 +481,11 @@ static int launch_gemv(jg_dev* dev, const GemvArgs& a, const char* name) {
 int jg_gemm_small(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, const void* s0, const void* s1,
                   void* y, const void* residual, void* key, int M, int N, int K, int row_offset);
 
+// matvec_w8.cu: int8 weights, up to 8 rows, activations resident in shared memory (optionally normalised there)
+int jg_matvec_w8(jg_dev* dev, int epi, const void* x, const void* norm_w, float eps, const void* w0, const void* w1,
+                 const void* s0, const void* s1, void* y, const void* residual, void* key, int M, int N, int K, int row_offset);
+bool jg_matvec_w8_fits(const jg_dev* dev, int M, int K);
+
 // gemm_tc.cu: tcgen05 / TMA projection (fp16 weights, N % 128 == 0, K % 64 == 0), any number of rows
 int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K);
 bool jg_gemm_tc_fits(int N, int K);
@@ -525,6 +521,11 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   }
   if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
+  // int8 weights, up to 8 rows: the kernel that keeps the rows in shared memory and streams the weights through the
+  // tensor cores without a barrier in its k loop; it also takes the norm in its prologue
+  if (W8 && a.M <= 8 && w8_mma() && jg_matvec_w8_fits(dev, a.M, a.K) && getenv("JG_W8_RESIDENT_X") == nullptr)
+    return jg_matvec_w8(dev, EPI, a.x, NORM ? a.norm_w : nullptr, a.eps, a.w0, a.w1, a.s0, a.s1,
+                        EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.key, a.M, a.N, a.K, a.row_offset);
   // int8 weights: the CUDA-core kernel spends its issue slots on dequantisation (half(q) * scale, widen, FMA: about 80
   // instructions per 16 bytes) and reaches half of the HBM rate; on the tensor cores the widening and the FMAs are
   // gone, so pre-normalised int8 projections of any row count go to the mma.sync kernel (JG_W8_MMA=0 keeps the
@@ -685,7 +686,7 @@ static int check_gather(const char* name, jg_comm* comm, uint64_t h_out, uint64_
   JG_REQUIRE(M <= 8 && (size_t)M * K <= PEER_LL_VALUES, "%s: M=%d K=%d exceed 8 rows / %zu exchanged values", name, M, K, (size_t)PEER_LL_VALUES);
   a->h_in = (const __half*)h_in; a->h_out = (__half*)h_out; a->norm_w = (const __half*)norm_w;
   a->recip_k = (float)(1.0 / (double)K);
-  return jg_peer_fill_args(comm, &a->peer);
+  return jg_peer_fill_args(comm, &a->peer, /*consume=*/true);
 }
 
 JG_API int jg_tp_linear_push(jg_comm* comm, uint64_t x, uint64_t w, uint64_t scale, int32_t M, int32_t N, int32_t K) {

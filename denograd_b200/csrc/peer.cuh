@@ -20,7 +20,8 @@ constexpr size_t PEER_BYTES = PEER_PARTIAL_OFFSET + PEER_TWOSHOT_VALUES * sizeof
 
 struct PeerArgs {
   unsigned char* buf[PEER_MAX_WORLD];
-  uint32_t* epoch;
+  const uint32_t* epoch;  // device word: exchanges completed before the current run of launches (see comm.cu)
+  uint32_t ord;           // this exchange's number within the run: its exchange number is epoch[0] + ord
   int* err;
   const float* part;  // [n] this rank's partial sums (fp32) / packed keys (as 2 x u32 per key)
   __half* h;          // [n] residual stream, updated in place (sum mode)
@@ -96,6 +97,7 @@ __device__ __forceinline__ bool peer_ll_load2(const uint2* p, uint32_t epoch, un
 
 
 struct jg_comm;
-// Fill the exchange-related fields of `a` (buffers, counters, rank, world, timeout) for this communicator; JG_EINVAL
-// when the peer buffers are not open.
-int jg_peer_fill_args(jg_comm* comm, PeerArgs* a);
+// Fill the exchange-related fields of `a` (buffers, counters, rank, world, timeout) for this communicator and give the
+// launch the next exchange number — or, with `consume`, the number of the exchange the preceding push started.
+// JG_EINVAL when the peer buffers are not open.
+int jg_peer_fill_args(jg_comm* comm, PeerArgs* a, bool consume = false);

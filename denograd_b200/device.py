@@ -21,8 +21,8 @@ import numpy as np
 
 from . import ffi
 
-_DTYPE_SIZE = {"float16": 2, "int8": 1, "int32": 4, "float32": 4, "uint64": 8}
-_NP = {"float16": np.float16, "int8": np.int8, "int32": np.int32, "float32": np.float32, "uint64": np.uint64}
+_DTYPE_SIZE = {"float16": 2, "int8": 1, "uint8": 1, "int32": 4, "float32": 4, "uint64": 8}
+_NP = {"float16": np.float16, "int8": np.int8, "uint8": np.uint8, "int32": np.int32, "float32": np.float32, "uint64": np.uint64}
 
 
 class CUDAAllocator:
@@ -224,7 +224,7 @@ class Tensor:
         arr = np.asarray(data)
         if dtype is not None:
             arr = arr.astype(_NP[dtype])
-        dtype = {np.dtype(np.float16): "float16", np.dtype(np.int8): "int8", np.dtype(np.int32): "int32",
+        dtype = {np.dtype(np.float16): "float16", np.dtype(np.int8): "int8", np.dtype(np.uint8): "uint8", np.dtype(np.int32): "int32",
                  np.dtype(np.float32): "float32", np.dtype(np.uint64): "uint64"}.get(arr.dtype)
         if dtype is None:
             raise TypeError(f"dtype {arr.dtype} is not used on the CUDA device's Llama path")

@@ -84,6 +84,7 @@ SIGNATURES: dict[str, list] = {
     "jg_attn_decode_noalloc": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32],
     "jg_pos_advance": [_vp, _u64, _i32],
     "jg_dequant_i8_f16": [_vp, _u64, _u64, _u64, _i64, _i64],
+    "jg_dequant_nf4_f16": [_vp, _u64, _u64, _u64, _i64, _i32],
     "jg_fill_normal_f16": [_vp, _u64, _u64, _u64, _u64, _f32],
     "jg_fill_uniform_i8": [_vp, _u64, _u64, _u64, _u64],
     "jg_fill_scale_f16": [_vp, _u64, _u64, _u64, _u64, _f32],

@@ -164,7 +164,7 @@ class TransformerBlock:
         split = tp is not None and B <= tp.split_rows(int8)
         # from 3 rows on (fp16 weights) normalise into ws.xn and project on the tensor cores; the fused-norm kernels
         # stream through the CUDA cores and only keep up with the weights for 1-2 rows (int8 weights: never)
-        big = _norm_first(B, int8) and not split
+        big = _norm_first(B, int8, d) and not split
         if split and ws.pending:  # the previous block's w2 left its sum on the wire
             h_in, h_out = ws.flip()
             ffi.call("jg_tp_norm_linear", tp.handle, ws.qkv.ptr, h_out.ptr, h_in.ptr, self.attention_norm.weight.ptr,
@@ -256,12 +256,15 @@ def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float, 
     return out
 
 
-def _norm_first(rows: int, int8: bool) -> bool:
+def _norm_first(rows: int, int8: bool, dim: int = 0) -> bool:
     """Whether RMSNorm runs as its own kernel ahead of a projection.  The matrix-vector kernels fuse the norm into
-    their prologue; the tensor-core kernels take normalised rows: fp16 weights from 3 rows on, int8 weights always
-    (their CUDA-core kernel is bound by dequantisation, not by HBM; JG_W8_MMA=0 restores it up to 8 rows)."""
+    their prologue; the tensor-core kernels take normalised rows: fp16 weights from 3 rows on; int8 weights beyond 8
+    rows, or when `rows` rows of `dim` halves are too many to stay in shared memory next to a second CTA (the int8
+    matrix-vector kernel keeps them there; `dim` = 0: unknown, normalise first)."""
     if int8:
-        return rows > 8 or os.environ.get("JG_W8_MMA", "1") != "0"
+        if os.environ.get("JG_W8_RESIDENT_X") is not None:  # the kernel is switched off: k-tiled tensor-core kernel
+            return rows > 8 or os.environ.get("JG_W8_MMA", "1") != "0"
+        return rows > 8 or dim <= 0 or dim % 64 != 0 or 2 * (rows * (2 * dim + 16) + 4096) > 228 * 1024
     return rows >= 3
 
 
@@ -426,7 +429,7 @@ class Transformer:
                          self.norm.weight.ptr, self.norm.eps, out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim,
                          self.vocab_offset)
                 assert ws.cur == cur0, "a captured step must end on the residual buffer it started on"
-            elif _norm_first(B, out.scale_ptr != 0):
+            elif _norm_first(B, out.scale_ptr != 0, self.dim):
                 self.norm.call(ws.h, out=ws.xn)
                 dev.call("jg_norm_logits_argmax_shard", ws.logits.ptr, ws.key.ptr, ws.xn.ptr, 0, self.norm.eps,
                          out.weight.ptr, out.scale_ptr, B, self.vocab_local, self.dim, self.vocab_offset)

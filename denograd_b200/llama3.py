@@ -91,14 +91,18 @@ class Llama3:
 
     def load_weights(self, path: str) -> "Llama3":
         """Weights from a checkpoint on disk, the tail of Llama3.load (jsgrad/models/llama3.ts:220-260) without the
-        download: read the .safetensors file (or the shards named by its .index.json), map Hugging Face names and
-        q/k row layout to the model's, narrow bf16 to fp16, cast to fp16 or quantise to int8 with the reference's
+        download: read the .safetensors file (or the shards named by its .index.json) or the .gguf file (ggml
+        blocks dequantised on the host), map Hugging Face / llama.cpp names and the Hugging Face q/k row layout to the model's, narrow bf16 to fp16, cast to fp16 or quantise to int8 with the reference's
         arithmetic, cut this rank's windows under tensor parallelism, and copy by name (non-strict)."""
         from .state import convert_from_huggingface, load_checkpoint
         p = self.params
         w = load_checkpoint(path)
         if "model.embed_tokens.weight" in w:
             w = convert_from_huggingface(w, p["n_layers"], p["n_heads"], p["n_kv_heads"])
+        elif "token_embd.weight" in w:  # llama.cpp naming (a .gguf file)
+            from .gguf import convert_from_gguf
+            w = convert_from_gguf(w, p["n_layers"])
+            w.pop("rope_freqs.weight", None)
         w = {k: np.asarray(v).astype(np.float16) for k, v in w.items()}
         if self.quantize == "int8":
             w = Int8Linear.quantize(w, quantize_embeds=self.quantize_embeds)

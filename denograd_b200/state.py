@@ -1,5 +1,5 @@
 """Checkpoint files for the Llama path: the safetensors container and the Hugging Face -> Llama name / layout
-conversion, on host arrays.  Counterpart of jsgrad/nn/state.ts:22-96 (safe_load / safe_save) and
+conversion, on host arrays (GGUF files: gguf.py).  Counterpart of jsgrad/nn/state.ts:22-96 (safe_load / safe_save) and
 jsgrad/models/llama.ts:224-253,272-279 (convert_from_huggingface, fix_bf16); `Llama3.load_weights` in llama3.py strings
 them together the way Llama3.load does (jsgrad/models/llama3.ts:201-258), minus the download.
 
@@ -89,7 +89,10 @@ def load_checkpoint(path: str) -> dict[str, np.ndarray]:
         return {k: parts[fn][k] for k, fn in weight_map.items()}
     if path.endswith(".safetensors"):
         return safe_load(path)
-    raise ValueError(f"{path}: only .safetensors files and their .index.json are read on this device (no gguf)")
+    if path.endswith(".gguf"):
+        from .gguf import gguf_load
+        return gguf_load(np.memmap(path, dtype=np.uint8, mode="r"))[1]
+    raise ValueError(f"{path}: expected a .safetensors file, a *.index.json of safetensors shards, or a .gguf file")
 
 
 def _permute(v: np.ndarray, n_heads: int) -> np.ndarray:

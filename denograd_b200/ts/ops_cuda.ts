@@ -69,6 +69,7 @@ export const SYMBOLS = {
   jg_attn_decode_noalloc: fn([ptr, u64, u64, u64, u64, u64, u64, i32, i32, i32, i32, i32, i32, i32, i32]),
   jg_pos_advance: fn([ptr, u64, i32]),
   jg_dequant_i8_f16: fn([ptr, u64, u64, u64, 'i64', 'i64']),
+  jg_dequant_nf4_f16: fn([ptr, u64, u64, u64, 'i64', i32]),
   jg_fill_normal_f16: fn([ptr, u64, u64, u64, u64, f32]),
   jg_fill_uniform_i8: fn([ptr, u64, u64, u64, u64]),
   jg_fill_scale_f16: fn([ptr, u64, u64, u64, u64, f32]),

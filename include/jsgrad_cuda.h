@@ -312,6 +312,12 @@ int jg_norm_logits_argmax_shard(jg_dev* dev, uint64_t logits, uint64_t key, uint
  * jg_device_sync before it is used as `w`. */
 int jg_dequant_i8_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t N, int64_t K);
 
+/* NF4Linear's dequantised matrix (jsgrad/models/llama3.ts:79-94): element i of the flattened [out][in] matrix is
+ * half(CODE[code_i] * scale[i / block]); byte j of `w` holds code_2j in its high nibble and code_2j+1 in its low one;
+ * scale: fp16 [n / block].  dst: fp16 [n].  The fp16 projection entry points then run on the copy, which is how this
+ * device serves NF4 weights (the packed form stays the resident one; the copy is a per-call scratch). */
+int jg_dequant_nf4_f16(jg_dev* dev, uint64_t dst, uint64_t w, uint64_t scale, int64_t n, int32_t block);
+
 /* ---- Seeded synthetic tensors (stand-in for Tensor.randn/uniform, jsgrad/tensor.ts:796-843, which the
  *      workloads replace by fixed distributions).  Counter-based, so any sub-range can be generated. */
 int jg_fill_normal_f16(jg_dev* dev, uint64_t dst, uint64_t seed, uint64_t first, uint64_t n, float std);

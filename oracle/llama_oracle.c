@@ -301,6 +301,52 @@ ORC_API void orc_quantize_w8(const uint16_t* w_, int8_t* wq, uint16_t* s_, int N
   }
 }
 
+/* NF4Linear — jsgrad/models/llama3.ts:79-117.  The 16 code values are rounded to fp16 (:81); a weight is
+ * half(CODE[c] * scale) with one fp16 scale per block of `block` consecutive elements of the flattened matrix (:92-93);
+ * the packed byte holds element 2i in its high nibble and element 2i+1 in its low one (:91,:105).
+ * quantize (:96-106): scale = max|block| (fp16), code = argmin_c |half(half(v * half(1/scale)) - CODE[c])|, lowest index
+ * among equals. */
+static const float ORC_NF4_CODE[16] = {-1.0f, -0.6961928009986877f, -0.5250730514526367f, -0.39491748809814453f,
+                                        -0.28444138169288635f, -0.18477343022823334f, -0.09105003625154495f, 0.0f,
+                                        0.07958029955625534f, 0.16093020141124725f, 0.24611230194568634f,
+                                        0.33791524171829224f, 0.44070982933044434f, 0.5626170039176941f,
+                                        0.7229568362236023f, 1.0f};
+ORC_API void orc_nf4_dequant(const uint8_t* packed, const uint16_t* s_, uint16_t* out_, int64_t n, int block) {
+  const h16* s = (const h16*)s_;
+  h16* out = (h16*)out_;
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; i++) {
+    const uint8_t b = packed[i / 2];
+    const int c = (i & 1) ? (b & 15) : (b >> 4);
+    out[i] = hmul((h16)ORC_NF4_CODE[c], s[i / block]);
+  }
+}
+ORC_API void orc_nf4_quantize(const uint16_t* w_, uint8_t* packed, uint16_t* s_, int64_t n, int block) {
+  const h16* w = (const h16*)w_;
+  h16* s = (h16*)s_;
+#pragma omp parallel for schedule(static)
+  for (int64_t g = 0; g < n / block; g++) {
+    float mx = 0.0f;
+    for (int j = 0; j < block; j++) { float a = fabsf((float)w[g * block + j]); if (a > mx) mx = a; }
+    const h16 sc = (h16)mx, rsc = hrecip(sc);
+    s[g] = sc;
+    for (int j = 0; j < block; j += 2) {
+      int code[2];
+      for (int e = 0; e < 2; e++) {
+        const h16 v = hmul(w[g * block + j + e], rsc);
+        int best = 0;
+        float bd = INFINITY;
+        for (int c = 0; c < 16; c++) {
+          const float dist = fabsf((float)hsub(v, (h16)ORC_NF4_CODE[c]));
+          if (dist < bd) { bd = dist; best = c; }
+        }
+        code[e] = best;
+      }
+      packed[(g * block + j) / 2] = (uint8_t)(code[0] * 16 + code[1]);
+    }
+  }
+}
+
 /* ------------------------------------------------------------------------------------------------------------
  * Embedding — jsgrad/nn/index.ts:607-619 (one-hot sum == row gather, exact);
  * Int8Embedding — jsgrad/models/llama3.ts:71-77: row = half(Wq[v,:]) * scale[v] (fp16 product).

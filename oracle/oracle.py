@@ -53,6 +53,8 @@ def lib() -> C.CDLL:
             "orc_linear_f16": (None, [vp, vp, vp, i32, i32, i32]),
             "orc_linear_w8": (None, [vp, vp, vp, vp, i32, i32, i32]),
             "orc_quantize_w8": (None, [vp, vp, vp, i32, i32]),
+            "orc_nf4_dequant": (None, [vp, vp, vp, C.c_int64, i32]),
+            "orc_nf4_quantize": (None, [vp, vp, vp, C.c_int64, i32]),
             "orc_embed_f16": (None, [vp, vp, vp, i32, i32]),
             "orc_embed_w8": (None, [vp, vp, vp, vp, i32, i32]),
             "orc_rope": (None, [vp, vp, vp, i32, i32, i32]),
@@ -154,6 +156,24 @@ def quantize_w8(w):
     s = np.empty((N,), np.float16)
     lib().orc_quantize_w8(_p(w), _p(wq), _p(s), N, K)
     return wq, s
+
+
+def nf4_quantize(w, block: int = 64):
+    """NF4Linear.quantize on one fp16 matrix: (packed uint8 [n/2], scale fp16 [n/block, 1])."""
+    w = _h(w)
+    n = w.size
+    packed = np.empty((n // 2,), np.uint8)
+    scale = np.empty((n // block, 1), np.float16)
+    lib().orc_nf4_quantize(_p(w), _p(packed), _p(scale), n, block)
+    return packed, scale
+
+
+def nf4_dequant(packed, scale, shape, block: int = 64) -> np.ndarray:
+    """The fp16 matrix NF4Linear.call multiplies by: half(CODE[code] * scale), reshaped to [out, in]."""
+    packed, scale = np.ascontiguousarray(packed, dtype=np.uint8), _h(scale)
+    out = np.empty((packed.size * 2,), np.float16)
+    lib().orc_nf4_dequant(_p(packed), _p(scale), _p(out), out.size, block)
+    return out.reshape(shape)
 
 
 def embed_f16(idx, w) -> np.ndarray:
