@@ -48,7 +48,7 @@ def test_sharded_checkpoint_through_its_index(tmp_path):
     w = load_checkpoint(str(idx))
     assert set(w) == {"x", "y", "z"} and (w["x"] == a["x"]).all() and (w["y"] == b["y"]).all()
     with pytest.raises(ValueError):
-        load_checkpoint(str(tmp_path / "model.gguf"))
+        load_checkpoint(str(tmp_path / "model.bin"))  # neither safetensors, an index, nor gguf
 
 
 def test_malformed_files_are_rejected(tmp_path):
