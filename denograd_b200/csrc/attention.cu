@@ -338,19 +338,6 @@ struct AttnFusedArgs {
   float scale;
 };
 
-__device__ __forceinline__ uint4 rope8(const uint4& xraw, const uint4& traw) {
-  const __half* x = reinterpret_cast<const __half*>(&xraw);
-  const __half* t = reinterpret_cast<const __half*>(&traw);
-  __align__(16) __half o[8];
-#pragma unroll
-  for (int i = 0; i < 4; i++) {
-    const __half xa = x[2 * i], xb = x[2 * i + 1], co = t[2 * i], si = t[2 * i + 1];
-    o[2 * i] = hsub1(hmul1(xa, co), hmul1(xb, si));
-    o[2 * i + 1] = hadd1(hmul1(xa, si), hmul1(xb, co));
-  }
-  return *reinterpret_cast<uint4*>(o);
-}
-
 template <int HD, int NREP>
 __global__ void __launch_bounds__(ATT_THREADS) attn_decode_fused_kernel(const AttnFusedArgs a) {
   constexpr int LPR = HD / 8;

@@ -114,8 +114,9 @@ int jg_check_device_errors(jg_dev* dev) {
   JG_CUDA(cudaMemcpy(&code, dev->err_word, sizeof(int), cudaMemcpyDeviceToHost));
   if (code != 0) {
     cudaMemset(dev->err_word, 0, sizeof(int));
-    jg_set_error("a device-side wait gave up (code %d: 1 = TMA producer, 2 = MMA issuer, 3 = epilogue); results of the "
-                 "tensor-core projections since the last synchronisation are invalid", code);
+    jg_set_error("a device-side wait gave up (code %d: 1 = TMA producer, 2 = MMA issuer, 3 = epilogue of a tensor-core "
+                 "projection, 4 = grid barrier of the single-kernel decode step); results since the last synchronisation "
+                 "are invalid", code);
     return JG_ETIMEDOUT;
   }
   return JG_OK;

@@ -43,4 +43,20 @@ __device__ __forceinline__ uint4 ld_kv_128(const __half* row, int off) {
   return row ? *reinterpret_cast<const uint4*>(row + off) : make_uint4(0, 0, 0, 0);
 }
 
+#ifdef __CUDACC__
+// apply_rotary_emb on eight halves = four (re, im) pairs against four (cos, sin) pairs (jsgrad/models/llama.ts:23-32)
+__device__ __forceinline__ uint4 rope8(const uint4& xraw, const uint4& traw) {
+  const __half* x = reinterpret_cast<const __half*>(&xraw);
+  const __half* t = reinterpret_cast<const __half*>(&traw);
+  __align__(16) __half o[8];
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const __half xa = x[2 * i], xb = x[2 * i + 1], co = t[2 * i], si = t[2 * i + 1];
+    o[2 * i] = hsub1(hmul1(xa, co), hmul1(xb, si));
+    o[2 * i + 1] = hadd1(hmul1(xa, si), hmul1(xb, co));
+  }
+  return *reinterpret_cast<uint4*>(o);
+}
+#endif
+
 static inline int ilog2(int v) { int s = 0; while ((1 << s) < v) s++; return s; }

@@ -32,6 +32,12 @@ class KvDesc(C.Structure):
                                           "max_pages_per_seq", "n_heads", "n_split")]
 
 
+class StepDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layers", "dim", "hidden_dim", "n_heads", "vocab_size", "freqs_rows")] + \
+               [("norm_eps", C.c_float), ("reserved", C.c_int32)] + \
+               [(n, C.c_uint64) for n in ("layers", "tok_embeddings", "out_norm", "output", "freqs_cis")]
+
+
 _vp, _i32, _i64, _u64, _f32, _f64, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_double, C.c_size_t
 _P = C.POINTER
 
@@ -82,6 +88,9 @@ SIGNATURES: dict[str, list] = {
     "jg_attn_rows": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32],
     "jg_attn_chunk": [_vp, _vp, _i32, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_attn_decode_noalloc": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32],
+    "jg_step_create": [_vp, _vp, _P(StepDesc), _P(_vp)],
+    "jg_step_destroy": [_vp],
+    "jg_step_run": [_vp, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _u64, _i32, _i32, _i32],
     "jg_pos_advance": [_vp, _u64, _i32],
     "jg_dequant_i8_f16": [_vp, _u64, _u64, _u64, _i64, _i64],
     "jg_dequant_nf4_f16": [_vp, _u64, _u64, _u64, _i64, _i32],

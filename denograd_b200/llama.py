@@ -94,18 +94,9 @@ class Attention:
         # reference's WQKV option concatenates them the same way, jsgrad/models/llama.ts:63-66); each Linear's
         # weight is a row view of it.
         self._wqkv = linear(dim, q_out + 2 * kv_out, False, device=dev)
-        w = self._wqkv.weight
-        views = [w.view_rows(0, q_out), w.view_rows(q_out, q_out + kv_out), w.view_rows(q_out + kv_out, q_out + 2 * kv_out)]
-        if hasattr(self._wqkv, "scale"):
-            s = self._wqkv.scale
-            sv = [s.view_rows(0, q_out), s.view_rows(q_out, q_out + kv_out), s.view_rows(q_out + kv_out, q_out + 2 * kv_out)]
-            self.wq = linear(dim, q_out, False, weight=views[0], scale=sv[0])
-            self.wk = linear(dim, kv_out, False, weight=views[1], scale=sv[1])
-            self.wv = linear(dim, kv_out, False, weight=views[2], scale=sv[2])
-        else:
-            self.wq = linear(dim, q_out, False, weight=views[0])
-            self.wk = linear(dim, kv_out, False, weight=views[1])
-            self.wv = linear(dim, kv_out, False, weight=views[2])
+        self.wq = linear(dim, q_out, False, **self._wqkv.row_views(0, q_out))
+        self.wk = linear(dim, kv_out, False, **self._wqkv.row_views(q_out, q_out + kv_out))
+        self.wv = linear(dim, kv_out, False, **self._wqkv.row_views(q_out + kv_out, q_out + 2 * kv_out))
         self.wo = linear(q_out, dim, False, device=dev)
         self._kv: KVCache | None = None
         self._layer = 0
@@ -258,13 +249,14 @@ def sample(logits: Tensor, temp: float, k: int, p: float, af: float, ap: float, 
 
 def _norm_first(rows: int, int8: bool, dim: int = 0) -> bool:
     """Whether RMSNorm runs as its own kernel ahead of a projection.  The matrix-vector kernels fuse the norm into
-    their prologue; the tensor-core kernels take normalised rows: fp16 weights from 3 rows on; int8 weights beyond 8
-    rows, or when `rows` rows of `dim` halves are too many to stay in shared memory next to a second CTA (the int8
+    their prologue; the tensor-core kernels take normalised rows: fp16 weights from 3 rows on; int8 weights beyond 1
+    row, or when `rows` rows of `dim` halves are too many to stay in shared memory next to a second CTA (the int8
     matrix-vector kernel keeps them there; `dim` = 0: unknown, normalise first)."""
     if int8:
         if os.environ.get("JG_W8_RESIDENT_X") is not None:  # the kernel is switched off: k-tiled tensor-core kernel
             return rows > 8 or os.environ.get("JG_W8_MMA", "1") != "0"
-        return rows > 8 or dim <= 0 or dim % 64 != 0 or 2 * (rows * (2 * dim + 16) + 4096) > 228 * 1024
+        max_m = int(os.environ.get("JG_W8_RESIDENT_MAX_M", "1"))
+        return rows > max_m or dim <= 0 or dim % 512 != 0 or 2 * (rows * (2 * dim + 16) + 4096) > 228 * 1024
     return rows >= 3
 
 
@@ -275,8 +267,10 @@ class _Workspace:
     def __init__(self, dev: CUDA, B: int, dim: int, qkv_dim: int, q_dim: int, hidden: int, vocab: int, tp=None):
         """`vocab` = 0 leaves out the logits (a multi-position chunk only projects its last rows, elsewhere)."""
         self.B = B
+        self._dev = dev
         self.tokens = Tensor.zeros((B,), "int32", dev)
         self.pos = Tensor.zeros((B,), "int32", dev)
+        self.hist = None  # picks of a run of steps made by one launch ([n_steps][B] int32)
         self.seq = Tensor.zeros((B,), "int32", dev)  # row -> sequence, for multi-position chunks
         # the residual stream; under tensor parallelism a second buffer, because the projection that completes a pushed
         # all-reduce writes the new stream while other CTAs still read the old one (`flip`)
@@ -314,8 +308,35 @@ class _Workspace:
 
     def __del__(self):
         try:
-            if self._pinned:
+            if self._pinned and self._dev.handle is not None:
                 ffi.call("jg_host_free", self._pinned)
+        except Exception:
+            pass
+
+
+class _StepPlan:
+    """Handle of the single-kernel decode step of one model (jg_step_create): the table of the layers' tensors and
+    the kernel's scratch.  The tensors' addresses are fixed at creation, like those a captured graph holds."""
+
+    def __init__(self, model: "Transformer"):
+        rows = []
+        for layer in model.layers:
+            a, f = layer.attention, layer.feed_forward
+            rows.append([layer.attention_norm.weight.ptr, a._wqkv.weight.ptr, a.wo.weight.ptr, layer.ffn_norm.weight.ptr,
+                         f.w1.weight.ptr, f.w3.weight.ptr, f.w2.weight.ptr])
+        table = np.ascontiguousarray(rows, dtype=np.uint64)
+        d = ffi.StepDesc(len(model.layers), model.dim, model.hidden_dim, model.n_heads, model.vocab_size,
+                         model.freqs_cis.shape[0], model.norm.eps, 0, table.ctypes.data, model.tok_embeddings.weight.ptr,
+                         model.norm.weight.ptr, model.output.weight.ptr, model.freqs_cis.ptr)
+        self._dev = model.dev
+        self.handle = C.c_void_p()
+        ffi.call("jg_step_create", model.dev.handle, model._kv.handle, C.byref(d), C.byref(self.handle))
+
+    def __del__(self):
+        try:
+            if self.handle and self._dev.handle is not None:
+                ffi.call("jg_step_destroy", self.handle)
+                self.handle = None
         except Exception:
             pass
 
@@ -400,6 +421,7 @@ class Transformer:
         self._jit_enabled = jit
         self._forward_jit: dict[int, TinyJit] = {}
         self._loop_graph: dict[int, CUDAGraph] = {}
+        self._step_plan = None  # None: not tried yet, False: this model keeps the launch-per-op step
 
     # ------------------------------------------------------------------------------------------ internals
     def _workspace(self, B: int, rows: bool = False) -> _Workspace:
@@ -413,11 +435,35 @@ class Transformer:
                                        self.vocab_local if key > 0 else 0, tp=self._tp)
         return self._ws[key]
 
+    def _single_kernel_step(self, B: int):
+        """The step plan (jg_step_create) when this model and batch can run the decode step as one persistent kernel:
+        fp16 weights, fused path, one device, 1-2 rows, a shape the kernel is instantiated for; else None."""
+        if B > 2 or self._step_plan is False:
+            return None
+        if self._step_plan is None:
+            self._step_plan = False
+            a0 = self.layers[0].attention
+            plain = (self.fused and self._tp is None and os.environ.get("JG_STEP_KERNEL", "0") != "0"
+                     and type(a0.wo) is Linear and type(self.output) is Linear and type(self.tok_embeddings) is Embedding
+                     and type(self.layers[0].feed_forward) is FeedForward)
+            if plain:
+                try:
+                    self._step_plan = _StepPlan(self)
+                except ffi.JgError as e:
+                    if e.status != ffi.JG_ENOTSUP:
+                        raise
+        return self._step_plan or None
+
     def _step(self, ws: _Workspace, advance: bool = False) -> None:
         """One token per row: reads ws.tokens / ws.pos, writes ws.logits and ws.next_tokens.  With `advance` the step
         also feeds its own output back (tokens <- next, pos += 1) so that it can be replayed with no host input."""
         dev, B = self.dev, ws.B
         cur0 = ws.cur
+        plan = self._single_kernel_step(B)
+        if plan is not None:  # the whole step as one persistent kernel
+            ffi.call("jg_step_run", plan.handle, ws.tokens.ptr, ws.pos.ptr, ws.h.ptr, ws.qkv.ptr, ws.attn.ptr, ws.ffn.ptr,
+                     ws.logits.ptr, ws.next_tokens.ptr, B, 1, 1 if advance else 0)
+            return
         self.tok_embeddings.call(ws.tokens, out=ws.h)
         if self.fused:
             for layer in self.layers:
@@ -618,6 +664,18 @@ class Transformer:
         if not resume:
             ws.tokens.assign(toks)
             ws.pos.assign(np.full((B,), start_pos, np.int32))
+        plan = self._single_kernel_step(B)
+        if plan is not None:
+            # the persistent kernel loops over the steps itself: one launch for the whole run, picks land in `hist`
+            if ws.hist is None or ws.hist.shape[0] < n_steps:
+                ws.hist = Tensor.empty((max(n_steps, 64), B), "int32", self.dev)
+            ffi.call("jg_step_run", plan.handle, ws.tokens.ptr, ws.pos.ptr, ws.h.ptr, ws.qkv.ptr, ws.attn.ptr, ws.ffn.ptr,
+                     ws.logits.ptr, ws.hist.ptr, B, n_steps, 1)
+            if not collect:
+                return None
+            out = ws.hist.numpy()[:n_steps].T.copy()
+            self.dev.call("jg_copy", ws.next_tokens.ptr, ws.hist.ptr + 4 * B * (n_steps - 1), 4 * B)
+            return out
         if B not in self._loop_graph:
             if resume:
                 raise ValueError("nothing to resume: run decode_loop once without `resume` first")

@@ -13,7 +13,7 @@ import numpy as np
 from . import synth
 from .device import Device, Tensor
 from .llama import Transformer
-from .nn import Embedding, Int8Embedding, Int8Linear, Linear, load_state_dict
+from .nn import Embedding, Int8Embedding, Int8Linear, Linear, NF4Linear, load_state_dict
 
 MODEL_PARAMS = {
     "1B": {"args": {"dim": 2048, "n_heads": 32, "n_kv_heads": 8, "n_layers": 16, "norm_eps": 1e-5, "rope_theta": 500000,
@@ -64,15 +64,19 @@ class Llama3:
     tokenizer: object | None = None  # denograd_b200.tokenizer.Tokenizer, needed by _system / chat only
 
     def __post_init__(self):
-        if self.quantize not in ("float16", "int8", None):
-            raise NotImplementedError(f"quantize={self.quantize!r}: only 'float16' and 'int8' are on this device path")
+        if self.quantize not in ("float16", "int8", "nf4", None):
+            raise ValueError(f"quantize={self.quantize!r}: expected 'float16', 'int8' or 'nf4'")
+        if self.quantize == "nf4":
+            if self.tp is not None:
+                raise NotImplementedError("NF4 weights under tensor parallelism")
+            self.fused = False  # NF4 layers dequantise per call: the per-op block path
         p = dict(MODEL_PARAMS[self.size]["args"])
         p.update(self.args)
         if self.n_layers is not None:
             p["n_layers"] = self.n_layers
         self.params = p
         int8 = self.quantize == "int8"
-        self.linear = Int8Linear if int8 else Linear
+        self.linear = Int8Linear if int8 else (NF4Linear(64) if self.quantize == "nf4" else Linear)
         self.embedding = Int8Embedding if int8 else Embedding
         self.quantize_embeds = int8
         tied = MODEL_PARAMS[self.size]["tied"] if self.tied_output is None else self.tied_output
@@ -106,6 +110,8 @@ class Llama3:
         w = {k: np.asarray(v).astype(np.float16) for k, v in w.items()}
         if self.quantize == "int8":
             w = Int8Linear.quantize(w, quantize_embeds=self.quantize_embeds)
+        elif self.quantize == "nf4":
+            w = self.linear.quantize(w)
         shards = self.model._shards
         if shards:
             if "output.weight" not in w:  # tied: the output layer is a window of the embedding table

@@ -15,6 +15,10 @@ import type { MemoryView } from '../helpers/memoryview.ts'
 import { env } from '../env/index.ts'
 import { vars } from '../helpers/helpers.ts'
 import { Renderer } from '../renderer/index.ts'
+import type { Buffer } from '../device.ts'
+import { type ExecItem } from '../engine/realize.ts'
+import { GraphRunner } from '../engine/jit.ts'
+import type { Variable } from '../ops.ts'
 
 const u64 = 'u64', i32 = 'i32', f32 = 'f32', f64 = 'f64', ptr = 'pointer', buf = 'buffer', usize = 'usize'
 const fn = (parameters: readonly string[], nonblocking = false) => ({ parameters, result: 'i32', nonblocking } as const)
@@ -70,6 +74,9 @@ export const SYMBOLS = {
   jg_pos_advance: fn([ptr, u64, i32]),
   jg_dequant_i8_f16: fn([ptr, u64, u64, u64, 'i64', 'i64']),
   jg_dequant_nf4_f16: fn([ptr, u64, u64, u64, 'i64', i32]),
+  jg_step_create: fn([ptr, ptr, buf, buf]),
+  jg_step_destroy: fn([ptr]),
+  jg_step_run: fn([ptr, u64, u64, u64, u64, u64, u64, u64, u64, i32, i32, i32]),
   jg_fill_normal_f16: fn([ptr, u64, u64, u64, u64, f32]),
   jg_fill_uniform_i8: fn([ptr, u64, u64, u64, u64]),
   jg_fill_scale_f16: fn([ptr, u64, u64, u64, u64, f32]),
@@ -104,10 +111,19 @@ export const SYMBOLS = {
 type Lib = { symbols: Record<keyof typeof SYMBOLS, (...a: any[]) => any> }
 let lib: Lib | undefined
 
-const check = (status: number) => {
+export const check = (status: number) => {
   if (status !== 0) throw new Error(`[jsgrad_cuda status ${status}] ${env.getCString(lib!.symbols.jg_last_error())}`)
 }
 const out64 = () => new BigUint64Array(1)
+
+/** One kernel entry point on one device: `cu(dev, 'jg_linear', y, x, ...)`.  Arguments may be device addresses
+ *  (bigint), numbers, or anything with a `.ptr` (the layers' tensors): the address is taken here, so the call sites read
+ *  like the argument lists of include/jsgrad_cuda.h.  The first C argument (the device handle) is supplied here. */
+export const cu = (dev: CUDA, entry: keyof typeof SYMBOLS, ...args: (bigint | number | { ptr: bigint } | undefined)[]) =>
+  check(lib!.symbols[entry](dev.handle, ...args.map((a) => a === undefined ? 0n : (typeof a === 'object' ? a.ptr : a))))
+/** The same for entry points whose first argument is another handle (a kv cache, a communicator). */
+export const cu_h = (entry: keyof typeof SYMBOLS, handle: Deno.PointerValue, ...args: (bigint | number | { ptr: bigint } | undefined)[]) =>
+  check(lib!.symbols[entry](handle, ...args.map((a) => a === undefined ? 0n : (typeof a === 'object' ? a.ptr : a))))
 
 /** Buf = device address (bigint).  Allocator contract: jsgrad/runtime/allocator.ts:28-47. */
 export class CUDAAllocator extends Allocator<bigint> {
@@ -127,58 +143,88 @@ export class CUDAAllocator extends Allocator<bigint> {
     check(lib!.symbols.jg_transfer(dest_dev.handle, dest, src_dev.handle, src, BigInt(sz)))
 }
 
-/** A kernel of the library addressed by name.  `lib` bytes are the UTF-8 descriptor the renderer emitted (which entry
- *  point, which scalar arguments); nothing is compiled at run time.  Program contract: allocator.ts:98-107. */
+/** A kernel of the library addressed by name.  `lib` bytes are a UTF-8 descriptor `{entry, order}`: which entry point,
+ *  and how its arguments interleave buffer slots (numbers), symbolic variables from args.vals ('v0', 'v1', ...) and
+ *  literals.  Nothing is compiled at run time.  Program contract: allocator.ts:98-107.  The class is created per
+ *  device (`CUDAProgram.bind(dev)`), because `Runtime.init(name, lib)` carries no device (engine/realize.ts:52-54). */
 export class CUDAProgram extends Program {
-  static device: CUDA
-  static override init = (name: string, lib: Uint8Array) => new CUDAProgram(name, lib)
+  static bind = (dev: CUDA): typeof Program =>
+    class extends CUDAProgram {
+      static override init = (name: string, lib: Uint8Array) => new this(name, lib, dev)
+    } as unknown as typeof Program
+  constructor(name: string, lib: Uint8Array, public dev: CUDA) {
+    super(name, lib)
+  }
   override call = async (bufs: bigint[], args: ProgramCallArgs, wait = false) => {
     const d = JSON.parse(new TextDecoder().decode(this.lib)) as { entry: keyof typeof SYMBOLS; order: (number | string)[] }
-    const dev = CUDAProgram.device
-    if (wait) check(lib!.symbols.jg_timer_start(dev.handle))
-    // `order` interleaves buffer slots (numbers), symbolic variables from args.vals ('v0', 'v1', ...) and literals
+    if (wait) check(lib!.symbols.jg_timer_start(this.dev.handle))
     const argv = d.order.map((o) => typeof o === 'number' ? bufs[o] : (o.startsWith('v') ? args.vals![Number(o.slice(1))] : Number(o)))
-    check(lib!.symbols[d.entry](dev.handle, ...argv))
+    check(lib!.symbols[d.entry](this.dev.handle, ...argv))
     if (wait) {
       const s = new Float64Array(1)
-      check(await lib!.symbols.jg_timer_stop(dev.handle, s))
+      check(await lib!.symbols.jg_timer_stop(this.dev.handle, s))
       return s[0]
     }
   }
 }
 
-/** Emits kernel descriptors instead of source text (precedent: PythonRenderer in ops_js.ts:249-268). */
+/** Kernel descriptors for CUDAProgram, written by the layers of llama_cuda.ts (one per entry point they call): the
+ *  device has no code generator; an AST that reaches `render` has no hand-written kernel behind it. */
 export class CUDADescriptorRenderer extends Renderer {
   override device = 'CUDA'
   override has_local = true
-  override render = (name: string, _uops: unknown[]) => JSON.stringify({ entry: name, order: [] })
+  static descriptor = (entry: keyof typeof SYMBOLS, order: (number | string)[]) => JSON.stringify({ entry, order })
+  override render = (name: string, _uops: unknown[]): string => {
+    throw new Error(`CUDA device: no hand-written kernel for the scheduled AST '${name}'; build the model from models/llama_cuda.ts`)
+  }
 }
 
-/** Captured decode step replayed with one launch (GraphRunner, engine/jit.ts:71-141). */
-export class CUDAGraph {
+/** A captured kernel list replayed with one launch: the GraphRunner TinyJit asks `Compiled.graph` for
+ *  (engine/jit.ts:21-29,71-141).  Varying values (tokens, start_pos) live in device memory, so `input_replace` /
+ *  `var_vals_replace` have nothing to patch; `capture` records the launches of `body`, `call` replays them. */
+export class CUDAGraph extends GraphRunner {
   handle: Deno.PointerValue = null
-  constructor(public dev: CUDA) {}
-  capture = async (body: () => Promise<void>) => {
-    check(lib!.symbols.jg_graph_begin(this.dev.handle))
+  cuda!: CUDA
+  static capture = async (dev: CUDA, jit_cache: ExecItem[], input_rawbuffers: Buffer[], var_vals: Map<Variable, number>, body: () => Promise<void>) => {
+    const g = new CUDAGraph(jit_cache, input_rawbuffers, var_vals)
+    g.cuda = dev
+    check(lib!.symbols.jg_graph_begin(dev.handle))
     try {
       await body()
     } finally {
       const o = out64()
-      check(lib!.symbols.jg_graph_end(this.dev.handle, o))
-      this.handle = Deno.UnsafePointer.create(o[0])
+      check(lib!.symbols.jg_graph_end(dev.handle, o))
+      g.handle = Deno.UnsafePointer.create(o[0])
     }
+    return g
   }
-  launch = () => check(lib!.symbols.jg_graph_launch(this.dev.handle, this.handle))
+  override call = (_rawbufs: Buffer[], _var_vals: Map<Variable, number>, wait = false) => {
+    if (wait) check(lib!.symbols.jg_timer_start(this.cuda.handle))
+    check(lib!.symbols.jg_graph_launch(this.cuda.handle, this.handle))
+    if (!wait) return undefined
+    const s = new Float64Array(1)
+    check(lib!.symbols.jg_timer_stop(this.cuda.handle, s))
+    return s[0]
+  }
+  destroy = () => {
+    if (this.handle) check(lib!.symbols.jg_graph_destroy(this.handle))
+    this.handle = null
+  }
 }
 
 export class CUDA extends Compiled {
   handle: Deno.PointerValue = null
   ordinal: number
   constructor(device: string) {
-    super(device, undefined, new CUDADescriptorRenderer(), new Compiler(), CUDAProgram)
+    super(device, undefined, new CUDADescriptorRenderer(), new Compiler(), undefined, undefined)
     this.ordinal = device.includes(':') ? Number(device.split(':')[1]) : 0
     this.allocator = new CUDAAllocator(this)
-    CUDAProgram.device = this
+    this.runtime = CUDAProgram.bind(this) // per device: two CUDA:n devices in one process keep their own handles
+    // TinyJit batches this device's CompiledRunners through `graph` (engine/jit.ts:40-58)
+    this.graph = (jit_cache: ExecItem[], input_rawbuffers: Buffer[], var_vals: Map<Variable, number>) =>
+      CUDAGraph.capture(this, jit_cache, input_rawbuffers, var_vals, async () => {
+        for (const ji of jit_cache) await ji.run(var_vals)
+      })
   }
   // awaited before every lower / run (engine/realize.ts:133,157): idempotent
   override init = async () => {

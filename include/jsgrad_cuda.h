@@ -38,6 +38,7 @@ typedef struct jg_dev jg_dev;         /* one opened CUDA device + its stream */
 typedef struct jg_graph jg_graph;     /* a captured, replayable list of launches */
 typedef struct jg_kvcache jg_kvcache; /* paged K/V pool of one model on one device */
 typedef struct jg_comm jg_comm;       /* tensor-parallel communicator of one rank */
+typedef struct jg_step jg_step;       /* one model's decode step as a single persistent kernel */
 
 /* ---- Compiled: jsgrad/runtime/allocator.ts:166-191 (ctor/init/synchronize), device lookup
  *      jsgrad/device.ts:26-35 (`new DEVICES['CUDA']('CUDA:3')`: the ordinal is parsed from the device name). */
@@ -209,6 +210,41 @@ int jg_attn_rows(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint6
  * Same result as jg_attn_rows up to the summation order of the fp32 accumulations. */
 int jg_attn_chunk(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint64_t qkv, uint64_t pos, uint64_t seq,
                   int32_t B, int32_t Sc, int32_t H);
+
+/* The whole decode step — embedding, every TransformerBlock, final norm, output projection and greedy pick
+ * (Transformer.forward for one token per row, jsgrad/models/llama.ts:201-220) — as ONE persistent cooperative kernel:
+ * what the reference replays as a captured batch of kernels (TinyJit / GraphRunner, jsgrad/engine/jit.ts:71-141,
+ * 273-353).  One CTA per SM stays resident; the former kernels are phases separated by grid-wide barriers, and the
+ * first weights of the next projection are already in flight when a CTA arrives at a barrier, so the HBM stream does
+ * not drain at every kernel boundary.  fp16 weights, 1 or 2 rows, head_dim 64 / 128 with up to 4 query heads per kv
+ * head, n_heads * head_dim == dim; other shapes: JG_ENOTSUP (the caller keeps the launch-per-op path).
+ * `layers` is a HOST pointer to n_layers x 7 device addresses: attention_norm.weight, wq|wk|wv (one allocation),
+ * wo, ffn_norm.weight, w1, w3, w2.  The cache object supplies the K/V pools and the block table (identity row map). */
+typedef struct jg_step_desc {
+  int32_t n_layers;
+  int32_t dim;
+  int32_t hidden_dim;
+  int32_t n_heads;
+  int32_t vocab_size;
+  int32_t freqs_rows;      /* rows of the RoPE table */
+  float norm_eps;
+  int32_t reserved;
+  uint64_t layers;         /* host pointer, see above */
+  uint64_t tok_embeddings; /* fp16 [vocab][dim] */
+  uint64_t out_norm;       /* fp16 [dim] */
+  uint64_t output;         /* fp16 [vocab][dim] */
+  uint64_t freqs_cis;      /* fp16 [freqs_rows][head_dim/2][2] from jg_freqs_cis */
+} jg_step_desc;
+int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc, jg_step** out);
+int jg_step_destroy(jg_step* step);
+/* n_steps decode steps for B rows.  tokens / pos: device int32 [B] (pos = index of the new token); h, qkv, attn, ffn:
+ * the step's activation buffers ([B][dim], [B][(H+2G)*hd], [B][dim], [B][hidden] fp16); logits: fp16 [B][vocab] of
+ * the last step; next_tokens: int32 [n_steps][B].  With `advance` the picks are fed back
+ * (tokens <- pick, pos += 1) between steps and stored to tokens / pos at the end; n_steps > 1 requires it.
+ * Every wait on another CTA is bounded (JG_STEP_TIMEOUT_MS, default 2000): a launch whose CTAs are not all making
+ * progress ends with JG_ETIMEDOUT at the next synchronising call. */
+int jg_step_run(jg_step* step, uint64_t tokens, uint64_t pos, uint64_t h, uint64_t qkv, uint64_t attn, uint64_t ffn,
+                uint64_t logits, uint64_t next_tokens, int32_t B, int32_t n_steps, int32_t advance);
 
 /* jg_attn_decode without any allocation by the library.  It has no counterpart in the reference; it exists for hosts
  * that must keep a kernel library from allocating device memory: an engine whose allocator owns the whole device and

@@ -177,13 +177,64 @@ def test_load_state_dict_from_host_arrays():
         a.load_state_dict({"norm.weight": np.ones(3, np.float16)})
 
 
+def test_nf4_weights_match_the_checker_over_the_dequantised_matrices():
+    """quantize='nf4' (NF4Linear(64), jsgrad/models/llama3.ts:79-117): the host quantiser equals the checker's, the device
+    dequantisation is bit-exact, and the model's greedy ids / logits equal the checker run on the dequantised fp16
+    matrices — which is what NF4Linear.call multiplies by."""
+    from denograd_b200.device import Tensor
+    from denograd_b200.nn import NF4Linear
+    from oracle import oracle as O
+    from tests.util import synth_weight, tensor_shapes
+    shapes = tensor_shapes(TINY)
+    sd = {}
+    for l in range(TINY["n_layers"]):
+        for suffix, shape in shapes.items():
+            sd[f"layers.{l}.{suffix}.weight"] = synth_weight(f"layers.{l}.{suffix}", shape, False)[0]
+        sd[f"layers.{l}.attention_norm.weight"] = np.ones(TINY["dim"], np.float16)
+        sd[f"layers.{l}.ffn_norm.weight"] = np.ones(TINY["dim"], np.float16)
+    sd["tok_embeddings.weight"] = synth_weight("tok_embeddings", (TINY["vocab_size"], TINY["dim"]), False)[0]
+    sd["output.weight"] = sd["tok_embeddings.weight"]
+    sd["norm.weight"] = np.ones(TINY["dim"], np.float16)
+    q = NF4Linear(64).quantize(sd)
+    name = "layers.1.feed_forward.w2.weight"
+    packed, scale = O.nf4_quantize(sd[name], 64)
+    assert (q[name] == packed).all() and (q[name.replace(".weight", ".scale")].view(np.uint16) == scale.view(np.uint16)).all()
+    llm = Llama3(size="1B", args=TINY, quantize="nf4", max_context=64, tied_output=True, temperature=0).load_state_dict(q)
+    dev = llm.model.dev
+    out = Tensor.empty((sd[name].size,), "float16", dev)
+    dev.call("jg_dequant_nf4_f16", out.ptr, Tensor(packed, device=dev).ptr, Tensor(scale, device=dev).ptr, sd[name].size, 64)
+    assert (out.numpy().view(np.uint16) == O.nf4_dequant(packed, scale, (sd[name].size,)).view(np.uint16)).all()
+    # checker on the dequantised matrices
+    cfg = O.OracleConfig(dim=TINY["dim"], n_layers=TINY["n_layers"], n_heads=TINY["n_heads"], n_kv_heads=TINY["n_kv_heads"],
+                         hidden=TINY["hidden_dim"], vocab=TINY["vocab_size"], max_context=64, max_batch=1, eps=TINY["norm_eps"],
+                         theta=float(TINY["rope_theta"]))
+    m = O.OracleModel(cfg)
+    ids_of = {"attention.wq": O.WQ, "attention.wk": O.WK, "attention.wv": O.WV, "attention.wo": O.WO,
+              "feed_forward.w1": O.W1, "feed_forward.w2": O.W2, "feed_forward.w3": O.W3}
+    for l in range(TINY["n_layers"]):
+        for suffix, wid in ids_of.items():
+            k = f"layers.{l}.{suffix}.weight"
+            m.set_weight(l, wid, O.nf4_dequant(q[k], q[k.replace(".weight", ".scale")], shapes[suffix]))
+        m.set_weight(l, O.ATTN_NORM, sd["norm.weight"]); m.set_weight(l, O.FFN_NORM, sd["norm.weight"])
+    m.set_weight(-1, O.TOK_EMB, sd["tok_embeddings.weight"]); m.set_weight(-1, O.OUTPUT, sd["tok_embeddings.weight"])
+    m.set_weight(-1, O.NORM, sd["norm.weight"])
+    prompt = synth.prompt_tokens(6, TINY["vocab_size"], seed=5)
+    ref_ids, ref_logits, margins = oracle_greedy(m, prompt, 6)
+    ids, logits = greedy_with_logits(llm, prompt, 6)
+    assert np.abs(logits - ref_logits).max() <= LOGIT_TOL
+    ulp = 2.0 ** (np.floor(np.log2(np.abs(ref_logits.max(axis=2)))) - 10)
+    safe = (margins / ulp) >= 3
+    n = 6 if safe[:, 0].all() else int(np.argmin(safe[:, 0]))
+    assert (ids[0, :n] == ref_ids[0, :n]).all()
+
+
 def test_context_limit_is_enforced():
     llm = make("1B", args=TINY, max_context=16, tied_output=True)
     prompt = synth.prompt_tokens(10, TINY["vocab_size"], seed=9)
     with pytest.raises(ValueError):
         llm.generate(prompt, 8)  # 10 + 7 positions > 16
-    with pytest.raises(NotImplementedError):
-        llm.model.call(prompt[:, :1], 0, temperature=0.9)
+    tok = llm.model.call(prompt[:, :1], 0, temperature=0.9).numpy()  # the stochastic branch of `sample` runs too
+    assert tok.shape == (1,) and 0 <= int(tok[0]) < TINY["vocab_size"]
 
 
 # ------------------------------------------------------------------------------------------------ full-size C1
@@ -232,7 +283,8 @@ def test_c1_seed42_diverges_only_at_a_tie():
 
 
 # ------------------------------------------------------------------------------------------------ other architectures
-@pytest.mark.parametrize("size,quant,layers,batch", [("3B", "float16", 2, 1), ("8B", "int8", 2, 2), ("8B", "float16", 1, 4)])
+@pytest.mark.parametrize("size,quant,layers,batch", [("3B", "float16", 2, 1), ("8B", "int8", 2, 2), ("8B", "float16", 1, 4),
+                                                     ("70B", "int8", 2, 1), ("8B", "int8", 1, 8)])
 def test_reduced_depth_slices_of_larger_architectures(size, quant, layers, batch):
     """Full-width, reduced-depth slices (the checker needs seconds, not hours): 3B has 3 query heads per kv head and
     head_dim 128; the 8B int8 slice exercises the int8 kernels at their real shapes with an untied int8 lm_head."""
