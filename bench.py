@@ -509,6 +509,7 @@ def run_gpu(args) -> None:
         k_bytes = 2 * f * d * (1 if int8 else 2) + (2 * f * 2 if int8 else 0) + B * d * 2 + d * 2 + B * f * 2
         k_gbs = k_bytes / k_secs / 1e9
         traffic = captured_traffic(args.model, args.quant, B, world)
+        single = model._single_kernel_step(B) is not None  # the timed region is ONE launch of the persistent step kernel
 
         kernel_name = (("gemm_small_kernel (mma.sync, gate/up + SwiGLU instantiation)" if (int8 or B < 9) else
                         "gemm_tc_kernel (tcgen05, gate/up + SwiGLU instantiation)") if big else
@@ -530,6 +531,20 @@ def run_gpu(args) -> None:
                                   "frac": main["frac_of_hbm_roofline"],
                                   "hbm_roofline_tok_s": B * peak * 1e9 / main["bytes_per_step_per_gpu"], "per_gpu": True}},
         }
+        if single:
+            # the dominant (only) kernel of the timed region is the step kernel itself: one launch runs the K steps, its
+            # algorithmic bytes are K steps' worth; the stand-alone gate/up projection stays beside it for comparison
+            r = line["roofline"]
+            step_bytes = main["bytes_per_step_per_gpu"]
+            per_step = captured_traffic(args.model, args.quant, B, world, "dram_bytes_per_step", "/step")
+            line["roofline"] = {
+                "bound": "hbm", "kernel": "jg_step_kernel (the whole decode step as one persistent kernel; one launch = the region's steps)",
+                "achieved": step_bytes / (secs / K) / 1e9, "peak": peak, "peak_kind": peaks["kind"], "unit": "GB/s",
+                "frac": main["frac_of_hbm_roofline"], "traffic": per_step * K if per_step else None,
+                "bytes_per_launch": step_bytes * K, "us_per_launch": secs * 1e6, "steps_per_launch": K,
+                "step": r["step"],
+                "standalone_gate_up": {k: r[k] for k in ("kernel", "achieved", "frac", "traffic", "bytes_per_launch", "us_per_launch")},
+            }
         # ---- extra legs of the same metric family
         if not args.no_extra:
             extra = {}
@@ -590,12 +605,13 @@ def extra_legs(rig: Rig, args, repeats: int) -> dict:
     return out
 
 
-def captured_traffic(model: str, quant: str, batch: int, world: int):
+def captured_traffic(model: str, quant: str, batch: int, world: int, field: str = "dram_bytes_per_launch", suffix: str = ""):
     """DRAM bytes (read + write) of one launch of the dominant kernel from the committed profiler capture of this
-    workload, if there is one: profiles/traffic.json maps "<model>/<quant>/bs<batch>/tp<world>" to bytes per launch."""
+    workload, if there is one: profiles/traffic.json maps "<model>/<quant>/bs<batch>/tp<world>" to bytes per launch
+    (and the same key + "/step" to the bytes of one decode step of the single-kernel step)."""
     try:
         with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
-            return json.load(f).get(f"{model}/{quant}/bs{batch}/tp{world}", {}).get("dram_bytes_per_launch")
+            return json.load(f).get(f"{model}/{quant}/bs{batch}/tp{world}{suffix}", {}).get(field)
     except Exception:
         return None
 

@@ -32,6 +32,8 @@
 //
 // Every wait on another CTA is bounded (wall clock); a wait that runs out sets the device's error word and the CTA
 // leaves the kernel, so a lost CTA ends the launch with JG_ETIMEDOUT at the next synchronisation instead of hanging.
+#include <stdio.h>
+
 #include "common.cuh"
 #include "kvcache.cuh"
 #include "transcendental.cuh"
@@ -78,15 +80,15 @@ struct StepArgs {
   int n_layers, dim, hidden, H, G, vocab, M, table_rows, page, page_shift, max_pages_per_seq, max_ctx;
   int slices, chunk_cap;  // context slices per (row, kv head) and the scores one slice can hold
   int advance, n_steps;
-  int l2_gu_rows;  // rows of W1 / W3 (per CTA) asked into L2 during attention
+  int nslot;        // slots of the weight ring (passes in flight per CTA)
+  int bar_probe;    // JG_STEP_PROF=2: that many back-to-back grid barriers at the start of every launch, timed in slot 15
+  int slot_bytes;   // bytes of one slot = of one pass: a few whole rows of one matrix (or of the gate / up pair)
+  int ring_offset;  // bytes from the start of dynamic shared memory to the ring
+  unsigned long long* prof;  // JG_STEP_PROF=1: [2][16] nanoseconds per phase, summed over layers and steps (CTA 0, last CTA)
   float eps, scale, recip_dim;
 };
 
-struct StepMat {
-  const unsigned char* w[2];
-  int r0, r1;  // this CTA's rows
-  int KC;      // 16-byte chunks per row
-};
+constexpr int ST_MAX_SLOTS = 6;
 
 __device__ __forceinline__ unsigned long long st_now() {
   unsigned long long t;
@@ -94,36 +96,53 @@ __device__ __forceinline__ unsigned long long st_now() {
   return t;
 }
 __device__ __forceinline__ uint4 ld_cg_128(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+__device__ __forceinline__ uint32_t st_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-// Grid-wide barrier (sense by generation).  All CTAs are resident (cooperative launch).  Returns false when the wait
-// ran out; the caller leaves the kernel.
-__device__ __forceinline__ bool st_grid_sync(const StepArgs& a, unsigned& gen) {
+// Bounded wait for the phase of `bar` with the given parity (a bulk copy's bytes have landed); false = gave up.
+__device__ __forceinline__ bool st_mbar_wait(uint64_t* bar, uint32_t parity, unsigned long long timeout_ns) {
+  const uint32_t addr = st_smem_u32(bar);
+  unsigned long long t0 = 0;
+  for (unsigned polls = 1;; polls++) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((polls & 63u) == 0) {
+      const unsigned long long now = st_now();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > timeout_ns) return false;
+    }
+  }
+}
+
+// Grid-wide barrier: every CTA adds one to a counter the host zeroed before the launch and waits until the counter
+// reaches the barrier's ordinal times the grid size.  All CTAs are resident (cooperative launch).  Returns false when
+// the wait ran out; the caller leaves the kernel.
+__device__ __forceinline__ bool st_grid_sync(const StepArgs& a, unsigned& nbar) {
   __shared__ int s_ok;
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    gen++;
-    __threadfence();
-    unsigned prev;
-    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(a.bar) : "memory");
-    if (prev == gridDim.x - 1) {
-      asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(a.bar), "r"(0u) : "memory");
-      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(a.bar + 32), "r"(gen) : "memory");
-    } else {
+    nbar++;
+    const unsigned target = nbar * gridDim.x;
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.bar) : "memory");
+    unsigned long long t0 = 0;
+    for (unsigned polls = 1;; polls++) {
       unsigned v;
-      unsigned long long t0 = 0;
-      unsigned polls = 0;
-      for (;;) {
-        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.bar + 32) : "memory");
-        if (v == gen) break;
-        if ((++polls & 255u) == 0) {
-          const unsigned long long now = st_now();
-          if (t0 == 0) t0 = now;
-          else if (now - t0 > a.timeout_ns) { ok = 0; break; }
-        }
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(a.bar) : "memory");
+      if (v >= target) break;
+      if ((polls & 255u) == 0) {
+        const unsigned long long now = st_now();
+        if (t0 == 0) t0 = now;
+        else if (now - t0 > a.timeout_ns) { ok = 0; break; }
       }
     }
-    __threadfence();
+    asm volatile("fence.acq_rel.gpu;" ::: "memory");
     s_ok = ok;
     if (!ok) atomicCAS(a.err, 0, 4);
   }
@@ -131,96 +150,179 @@ __device__ __forceinline__ bool st_grid_sync(const StepArgs& a, unsigned& gen) {
   return s_ok != 0;
 }
 
-// ---- one pass of a projection: 8 x 16 bytes per lane
-template <int R, int NI, int NW>
-__device__ __forceinline__ void st_issue(const StepMat& m, int p, uint4 (&b)[8], int tid) {
-  static_assert(R * NI * NW == 8, "a pass is 8 loads per lane");
-#pragma unroll
-  for (int w = 0; w < NW; w++)
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-      const int row = m.r0 + p * R + r;
-      const bool rv = row < m.r1;
-      const unsigned char* base = m.w[w] + (size_t)(rv ? row : 0) * ((size_t)m.KC * 16);
-#pragma unroll
-      for (int i = 0; i < NI; i++) {
-        const int c = tid + ST_THREADS * i;
-        b[(w * R + r) * NI + i] = (rv && c < m.KC) ? ld_stream_128(base + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
-      }
-    }
+// ---- the weight stream.  Thread 0 of the CTA walks the step's projections in order (qkv, wo, gate/up, down of every
+// layer, then the output matrix, then the next step) and keeps `nslot` passes in flight as bulk copies into a ring of
+// shared-memory slots; the copy of pass q + nslot is issued the moment pass q has been consumed.  The walk does not stop
+// at phase boundaries: while the CTA stages activations, waits at a grid barrier or works on attention, the first
+// passes of the next projection are landing.
+// How an N-row matrix is dealt to the CTAs in passes of rs rows: CTA c takes passes c, c + grid, c + 2 grid, ... (at
+// any moment the grid reads one contiguous window of the matrix); the matrix's last pass may be short.  (Splitting the
+// rows that do not fill a whole round evenly over the CTAs was measured and is slower: every CTA then pays a pass's
+// fixed cost for a few rows.)
+struct StepSplit { int passes, last_rows; };  // passes of this CTA; rows of its last pass
+__device__ __forceinline__ StepSplit st_split(int N, int rs) {
+  const int bid = blockIdx.x, nb = gridDim.x;
+  const int total = (N + rs - 1) / rs;
+  StepSplit sp;
+  sp.passes = bid < total ? (total - bid + nb - 1) / nb : 0;
+  const bool short_last = sp.passes > 0 && bid + (sp.passes - 1) * nb == total - 1;
+  sp.last_rows = short_last ? N - (total - 1) * rs : rs;
+  return sp;
 }
 
-template <int R, int NI, int NW, int MT>
-__device__ __forceinline__ void st_consume(const uint4 (&b)[8], const __half* xs, int K, int KC, float* part, int tid) {
-  float acc[NW * R][MT];
-#pragma unroll
-  for (int j = 0; j < NW * R; j++)
-#pragma unroll
-    for (int m = 0; m < MT; m++) acc[j][m] = 0.f;
-#pragma unroll
-  for (int i = 0; i < NI; i++) {
-    const int c = tid + ST_THREADS * i;
-    if (c < KC) {
-#pragma unroll
-      for (int m = 0; m < MT; m++) {
-        float xf[8];
-        unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 8), xf);
-#pragma unroll
-        for (int j = 0; j < NW * R; j++) acc[j][m] = dot8_acc(acc[j][m], b[j * NI + i], xf);
-      }
-    }
+struct StepStream {
+  int step, layer, phase;  // phase: 0 qkv, 1 wo, 2 gate/up, 3 down, 4 output matrix; step == n_steps: nothing left
+  int left;                // passes this CTA still has to request in the phase
+  uint32_t pass_bytes;     // bytes of a full pass (per matrix), of this CTA's last pass of the phase
+  uint32_t tail_bytes;
+  const unsigned char* src0;  // next pass of the first (second) matrix
+  const unsigned char* src1;
+  uint32_t slot;           // ring slot the next pass goes to
+  size_t stride;           // bytes from one pass of this CTA to its next
+};
+
+// Position (step, layer, phase) -> matrix, this CTA's rows, passes (0 when the CTA has no rows in the phase).
+template <int RS_D, int RS_G, int RS_H>
+__device__ __forceinline__ void st_stream_enter(StepStream& st, const StepArgs& a, int qkv_dim) {
+  const int bid = blockIdx.x, nb = gridDim.x;
+  int N, rs;
+  const StepLayer* L = a.layers + st.layer;
+  const unsigned char* w0;
+  const unsigned char* w1 = nullptr;
+  uint32_t row_bytes = (uint32_t)a.dim * 2u;
+  switch (st.phase) {
+    case 0: N = qkv_dim; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(L->wqkv); break;
+    case 1: N = a.dim; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(L->wo); break;
+    case 2: N = a.hidden; rs = RS_G; w0 = reinterpret_cast<const unsigned char*>(L->w1); w1 = reinterpret_cast<const unsigned char*>(L->w3); break;
+    case 3: N = a.dim; rs = RS_H; w0 = reinterpret_cast<const unsigned char*>(L->w2); row_bytes = (uint32_t)a.hidden * 2u; break;
+    default: N = a.vocab; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(a.out_w); break;
   }
-  const int lane = tid & 31, warp = tid >> 5;
-#pragma unroll
-  for (int j = 0; j < NW * R; j++)
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-      const float v = warp_sum(acc[j][m]);
-      if (lane == 0) part[warp * ST_PART + j * MT + m] = v;
-    }
+  const StepSplit sp = st_split(N, rs);
+  st.left = sp.passes;
+  st.pass_bytes = (uint32_t)rs * row_bytes;
+  st.stride = (size_t)nb * st.pass_bytes;
+  st.tail_bytes = (uint32_t)sp.last_rows * row_bytes;
+  st.src0 = w0 + (size_t)bid * st.pass_bytes;
+  st.src1 = w1 ? w1 + (size_t)bid * st.pass_bytes : nullptr;
+}
+template <int RS_D, int RS_G, int RS_H>
+__device__ __forceinline__ void st_stream_next_phase(StepStream& st, const StepArgs& a, int qkv_dim) {
+  do {
+    if (st.phase == 4) { st.phase = 0; st.layer = 0; st.step++; }
+    else if (st.phase == 3) { st.layer++; st.phase = (st.layer < a.n_layers) ? 0 : 4; if (st.phase == 4) st.layer = 0; }
+    else st.phase++;
+    if (st.step >= a.n_steps) return;
+    st_stream_enter<RS_D, RS_G, RS_H>(st, a, qkv_dim);
+  } while (st.left <= 0);
+}
+// Request the next pass of the walk into the slot that has just been consumed (the CTA's producer thread only).
+template <int RS_D, int RS_G, int RS_H>
+__device__ __forceinline__ void st_stream_issue(StepStream& st, const StepArgs& a, int qkv_dim, unsigned char* ring, uint64_t* full) {
+  if (st.step >= a.n_steps) return;
+  const uint32_t bytes = st.left == 1 ? st.tail_bytes : st.pass_bytes;
+  const unsigned char* s0 = st.src0;
+  const unsigned char* s1 = st.src1;
+  const uint32_t bar = st_smem_u32(full + st.slot);
+  const uint32_t dst = st_smem_u32(ring) + st.slot * (uint32_t)a.slot_bytes;
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(st.src1 ? 2u * bytes : bytes) : "memory");
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(s0), "r"(bytes), "r"(bar) : "memory");
+  if (st.src1) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst + st.pass_bytes), "l"(s1), "r"(bytes), "r"(bar) : "memory");
+    st.src1 += st.stride;
+  }
+  st.src0 += st.stride;
+  st.slot = (st.slot + 1 == (uint32_t)a.nslot) ? 0u : st.slot + 1;
+  if (--st.left == 0) st_stream_next_phase<RS_D, RS_G, RS_H>(st, a, qkv_dim);
 }
 
-// The phase: on entry wv[0] / wv[1] hold passes 0 / 1 (issued before the preceding barrier); `epi(row, m, s_a, s_b)`
-// finishes one output; `next(q, buf)` issues pass q of whatever projection comes next into the buffer that just
-// became free.  The pass count is rounded up to an even number >= 2 (empty passes load nothing), so that the next
-// projection's passes 0 and 1 always land in wv[0] and wv[1].
-template <int R, int NI, int NW, int MT, class Epi, class Next>
-__device__ __forceinline__ void st_project(const StepMat& m, const __half* xs, int K, int M, float (*part)[ST_WARPS * ST_PART],
-                                           uint4 (&wv)[2][8], int tid, Epi epi, Next next) {
-  const int rows = m.r1 - m.r0;
-  int np = (rows + R - 1) / R;
-  np = np < 2 ? 2 : ((np + 1) & ~1);
-  for (int p = 0; p < np; p += 2) {
+// Where the consumer is in the ring: slot of the next pass and the parity of that slot's barrier.
+struct StepRing { uint32_t slot, parity; };
+
+constexpr int ST_PRODUCER = ST_THREADS - 32;  // the thread that requests the weight passes (lane 0 of the last warp)
+
+// One projection phase of this CTA: its passes of RS rows (of each of NW matrices) of an N-row matrix; thread t multiplies
+// the 16-byte chunks t, t + 512, ... of every row of the pass (read from the slot) with the activations; the per-warp
+// partial sums meet in shared memory at one barrier per pass, after which the producer thread refills the slot and
+// output o of the pass (o < RS * MT) is finished by lane 0 of warp o, in warp order (fixed summation order) — one
+// output per warp, so that no warp carries the whole epilogue.  `pre(row, m)` fetches what the epilogue needs from
+// global memory (the residual) before the pass is multiplied.  A data wait that runs out is recorded and the pass is
+// carried on with whatever the slot holds (the launch's results are void then).
+template <int RS, int NI, int NW, int MT, class Pre, class Epi, class Refill>
+__device__ __forceinline__ void st_project(int N, int KC, const __half* xs, int M, const unsigned char* ring, uint64_t* full,
+                                           StepRing& rg, unsigned& seq, float (*part)[ST_PART * ST_WARPS], const StepArgs& a, int tid,
+                                           Pre pre, Epi epi, Refill refill) {
+  static_assert(RS * NW * MT <= ST_PART && RS * MT <= ST_WARPS, "partial sums per warp; one output per finishing warp");
+  const int K = KC * 8;
+  const uint32_t row_bytes = (uint32_t)KC * 16u;
+  const int bid = blockIdx.x, nb = gridDim.x;
+  const StepSplit sp = st_split(N, RS);
+  const int np = sp.passes;
+  const int lane = tid & 31, warp = tid >> 5;
+  const int fr = warp / MT, fm = warp % MT;  // the output lane 0 of this warp finishes (warp < RS * MT)
+  for (int p = 0; p < np; p++) {
+    const int frow = (bid + p * nb) * RS + fr;
+    const bool fin = lane == 0 && warp < RS * MT && fm < M && frow < N;
+    __half prev = __float2half_rn(0.f);
+    if (fin) prev = pre(frow, fm);
+    if (!st_mbar_wait(full + rg.slot, rg.parity, a.timeout_ns)) atomicCAS(a.err, 0, 5);
+    const unsigned char* sl = ring + (size_t)rg.slot * a.slot_bytes;
+    float acc[NW * RS][MT];
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-      st_consume<R, NI, NW, MT>(wv[h], xs, K, m.KC, part[h], tid);
-      if (p + 2 + h < np) st_issue<R, NI, NW>(m, p + 2 + h, wv[h], tid);
-      else next(h, wv[h]);
-      __syncthreads();
-      if (tid < R * MT) {
-        const int r = tid / MT, mm = tid % MT;
-        const int row = m.r0 + (p + h) * R + r;
-        if (row < m.r1 && mm < M) {
-          float s_a = 0.f, s_b = 0.f;
+    for (int j = 0; j < NW * RS; j++)
 #pragma unroll
-          for (int w = 0; w < ST_WARPS; w++) s_a += part[h][w * ST_PART + r * MT + mm];
-          if (NW == 2) {
+      for (int m = 0; m < MT; m++) acc[j][m] = 0.f;
 #pragma unroll
-            for (int w = 0; w < ST_WARPS; w++) s_b += part[h][w * ST_PART + (R + r) * MT + mm];
-          }
-          epi(row, mm, s_a, s_b);
+    for (int i = 0; i < NI; i++) {
+      const int c = tid + ST_THREADS * i;
+      if (c < KC) {
+        float xf[MT][8];
+#pragma unroll
+        for (int m = 0; m < MT; m++) unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + (size_t)c * 8), xf[m]);
+#pragma unroll
+        for (int j = 0; j < NW * RS; j++) {
+          const uint4 wv = *reinterpret_cast<const uint4*>(sl + (size_t)j * row_bytes + (size_t)c * 16);
+#pragma unroll
+          for (int m = 0; m < MT; m++) acc[j][m] = dot8_acc(acc[j][m], wv, xf[m]);
         }
       }
     }
+    float* pp = part[seq & 1u];  // [value][warp]
+#pragma unroll
+    for (int j = 0; j < NW * RS; j++)
+#pragma unroll
+      for (int m = 0; m < MT; m++) {
+        const float v = warp_sum(acc[j][m]);
+        if (lane == 0) pp[(j * MT + m) * ST_WARPS + warp] = v;
+      }
+    __syncthreads();
+    if (tid == ST_PRODUCER) refill();
+    if (fin) {
+      auto sum16 = [&](int value) {
+        const float4* q = reinterpret_cast<const float4*>(pp + value * ST_WARPS);
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < ST_WARPS / 4; w++) {
+          const float4 v = q[w];
+          t += v.x; t += v.y; t += v.z; t += v.w;
+        }
+        return t;
+      };
+      const float s_a = sum16(fr * MT + fm);
+      const float s_b = NW == 2 ? sum16((RS + fr) * MT + fm) : 0.f;
+      epi(frow, fm, s_a, s_b, prev);
+    }
+    seq++;
+    if (++rg.slot == (uint32_t)a.nslot) { rg.slot = 0; rg.parity ^= 1u; }
   }
 }
 
-template <int MT, int HD, int NREP, int NI_D, int NI_H>
+// RS_D / RS_G / RS_H: rows per pass of a projection with K = dim (one matrix), of the gate / up pair (rows of each), with
+// K = hidden; NI_D / NI_H: 16-byte chunks per thread and row (K / 8 chunks over 512 threads).
+template <int MT, int HD, int NREP, int RS_D, int RS_G, int RS_H, int NI_D, int NI_H>
 __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a) {
   static_assert(NREP <= 4 && MT <= 2, "register budget of 128 per thread");
-  constexpr int R_D = 8 / NI_D;  // rows per pass, K = dim
-  constexpr int R_H = 8 / NI_H;  // rows per pass, K = hidden
-  constexpr int R_G = 4 / NI_D;  // gate/up row pairs per pass
   constexpr int LPR = HD / 8;    // lanes per K / V row
   constexpr int RPW = 32 / LPR;  // rows per warp pass
   constexpr int AU = 2;          // attention row passes in flight
@@ -230,12 +332,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
   __half* xs = reinterpret_cast<__half*>(st_smem);  // [MT][K] activation rows of a projection phase
   // the attention phases reuse the same bytes: raw scores, per-warp p.v partials, the CTA's p.v partial
   float* sc = reinterpret_cast<float*>(st_smem);                     // [NREP][chunk_cap]
-  float* pv_part = sc + (size_t)NREP * a.chunk_cap;                   // [ST_WARPS][NREP][HD]
-  float* o_part = pv_part + (size_t)ST_WARPS * NREP * HD;             // [NREP][HD]
-  __shared__ float part[2][ST_WARPS * ST_PART];
+  float* pv_part = sc + (size_t)NREP * a.chunk_cap;                   // [ST_WARPS / 2][NREP][HD]
+  unsigned char* ring = st_smem + a.ring_offset;                     // [nslot][slot_bytes] weight passes in flight
+  __shared__ __align__(8) uint64_t full[ST_MAX_SLOTS];
+  __shared__ __align__(16) float part[2][ST_PART * ST_WARPS];
   __shared__ float red[ST_WARPS][4];
   __shared__ float s_rs[MT];
-  __shared__ float s_m[4], s_l[4], s_M[4], s_rL[4];
+  __shared__ float s_m[4], s_M[4], s_rL[4];
   __shared__ int s_last;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -245,19 +348,46 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
   const int qkv_dim = (a.H + 2 * a.G) * HD;
   const float log2e = 1.4426950408889634f;
 
-  unsigned gen = 0;
-  if (tid == 0) asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(a.bar + 32) : "memory");
+  unsigned gen = 0;  // grid barriers passed
+  unsigned seq = 0;  // weight passes consumed
 
-  auto mat = [&](const __half* w0, const __half* w1, int N, int KC) {
-    StepMat m;
-    m.w[0] = reinterpret_cast<const unsigned char*>(w0);
-    m.w[1] = reinterpret_cast<const unsigned char*>(w1);
-    m.r0 = (int)((long long)bid * N / nb);
-    m.r1 = (int)((long long)(bid + 1) * N / nb);
-    m.KC = KC;
-    return m;
+  // the weight stream starts before anything else: nslot passes are on their way while the first rows are staged
+  StepStream st;
+  StepRing rg;
+  rg.slot = 0; rg.parity = 0;
+  unsigned issued = 0;  // passes requested (producer thread)
+  if (tid == ST_PRODUCER) {
+    for (int i = 0; i < a.nslot; i++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(st_smem_u32(full + i)) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    st.step = 0; st.layer = 0; st.phase = 0; st.slot = 0;
+    st_stream_enter<RS_D, RS_G, RS_H>(st, a, qkv_dim);
+    if (st.left <= 0) st_stream_next_phase<RS_D, RS_G, RS_H>(st, a, qkv_dim);
+    for (int i = 0; i < a.nslot; i++) {
+      if (st.step < a.n_steps) issued++;
+      st_stream_issue<RS_D, RS_G, RS_H>(st, a, qkv_dim, ring, full);
+    }
+  }
+  __syncthreads();
+  auto refill = [&]() {
+    if (st.step < a.n_steps) issued++;
+    st_stream_issue<RS_D, RS_G, RS_H>(st, a, qkv_dim, ring, full);
   };
-  auto no_next = [](int, uint4 (&)[8]) {};
+  auto no_pre = [](int, int) { return __float2half_rn(0.f); };
+  auto residual = [&](int row, int m) { return __ldcg(a.h + (size_t)m * dim + row); };
+  // a wait ran out: record it, let the copies still in flight land (bounded) so that none writes into shared memory of
+  // a CTA that has gone, and leave
+  auto give_up = [&](int code) {
+    if (tid == ST_PRODUCER) {
+      atomicCAS(a.err, 0, code);
+      StepRing r = rg;
+      for (unsigned q = seq; q < issued; q++) {
+        st_mbar_wait(full + r.slot, r.parity, a.timeout_ns);
+        if (++r.slot == (uint32_t)a.nslot) { r.slot = 0; r.parity ^= 1u; }
+      }
+    }
+    __syncthreads();
+  };
 
   // x <- RMSNorm(rows) * g into shared memory (rows beyond M are zero); src(m) = the row's address
   auto stage_norm = [&](auto src, const __half* g) {
@@ -322,13 +452,26 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
     posv[m] = (m < M) ? a.pos[m] : 0;
   }
 
-  uint4 wv[2][8];
-  {
-    const StepMat m0 = mat(a.layers[0].wqkv, nullptr, qkv_dim, KC_D);
-    st_issue<R_D, NI_D, 1>(m0, 0, wv[0], tid);
-    st_issue<R_D, NI_D, 1>(m0, 1, wv[1], tid);
+  // phase timing (diagnostic): CTA 0 and the last CTA add the time since their previous stamp to slot `i`
+  unsigned long long t_prev = 0;
+  const bool prof = a.prof != nullptr && tid == 0 && (bid == 0 || bid == nb - 1);
+  if (prof) {
+    t_prev = st_now();
+    if (bid == 0) { a.prof[14] += 1ull; a.prof[30] += (unsigned long long)a.n_steps; }  // launches and steps, replays included
   }
+  auto stamp = [&](int i) {
+    if (prof) {
+      const unsigned long long t = st_now();
+      a.prof[(bid == 0 ? 0 : 16) + i] += t - t_prev;
+      t_prev = t;
+    }
+  };
 
+  if (a.prof != nullptr && a.bar_probe > 0) {  // diagnostic: the cost of a grid barrier nobody arrives late at
+    for (int i = 0; i < a.bar_probe; i++)
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+    stamp(15);
+  }
   for (int step = 0; step < a.n_steps; step++) {
     for (int l = 0; l < a.n_layers; l++) {
       const StepLayer* L = a.layers + l;
@@ -350,24 +493,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
       } else {
         stage_norm([&](int m) -> const __half* { return a.h + (size_t)m * dim; }, L->attn_norm);
       }
-      {
-        const StepMat mq = mat(L->wqkv, nullptr, qkv_dim, KC_D);
-        st_project<R_D, NI_D, 1, MT>(mq, xs, dim, M, part, wv, tid,
-                                     [&](int row, int m, float s, float) { a.qkv[(size_t)m * qkv_dim + row] = __float2half_rn(s); },
-                                     no_next);
-      }
-      // while attention runs the memory pipe is idle: this CTA's rows of Wo and the head of its W1 / W3 rows -> L2
-      {
-        const StepMat mo = mat(L->wo, nullptr, dim, KC_D);
-        const uint32_t rb = (uint32_t)KC_D * 16u;
-        for (int r = mo.r0 + tid; r < mo.r1; r += ST_THREADS)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(mo.w[0] + (size_t)r * rb), "r"(rb) : "memory");
-        const StepMat mg = mat(L->w1, L->w3, hidden, KC_D);
-        const int ng = min(a.l2_gu_rows, mg.r1 - mg.r0);
-        for (int r = tid; r < 2 * ng; r += ST_THREADS)
-          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(mg.w[r & 1] + (size_t)(mg.r0 + (r >> 1)) * rb), "r"(rb) : "memory");
-      }
-      if (!st_grid_sync(a, gen)) return;
+      st_project<RS_D, NI_D, 1, MT>(qkv_dim, KC_D, xs, M, ring, full, rg, seq, part, a, tid, no_pre,
+                                         [&](int row, int m, float s, float, __half) { a.qkv[(size_t)m * qkv_dim + row] = __float2half_rn(s); },
+                                         refill);
+      stamp(0);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(1);
       if (l == 0 && bid == 0 && tid < M) a.key[tid] = 0ull;  // every CTA has read the previous step's key by now
 
       // ================================================================ P2: RoPE, cache write, scores of a context slice
@@ -470,7 +601,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
           ml[1] = v;
         }
       }
-      if (!st_grid_sync(a, gen)) return;
+      stamp(2);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(3);
 
       // ================================================================ P3: probabilities, p.v, fold over the slices
       if (att) {
@@ -526,18 +659,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
 #pragma unroll
             for (int o = 16; o >= LPR; o >>= 1) acc[r][i] += __shfl_xor_sync(0xffffffffu, acc[r][i], o);
           }
-        if (rgrp == 0) {
+        // the warps' partials meet in two rounds (upper half of the warps stores, lower half adds its own on top), which
+        // halves the scratch
+        if (rgrp == 0 && warp >= ST_WARPS / 2) {
 #pragma unroll
           for (int r = 0; r < NREP; r++)
 #pragma unroll
-            for (int i = 0; i < 8; i++) pv_part[((size_t)warp * NREP + r) * HD + sub * 8 + i] = acc[r][i];
+            for (int i = 0; i < 8; i++) pv_part[((size_t)(warp - ST_WARPS / 2) * NREP + r) * HD + sub * 8 + i] = acc[r][i];
+        }
+        __syncthreads();
+        if (rgrp == 0 && warp < ST_WARPS / 2) {
+#pragma unroll
+          for (int r = 0; r < NREP; r++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) pv_part[((size_t)warp * NREP + r) * HD + sub * 8 + i] += acc[r][i];
         }
         __syncthreads();
         float* po = a.att_o + ((size_t)pair * a.slices + slice) * (NREP * HD);
         for (int idx = tid; idx < NREP * HD; idx += ST_THREADS) {
           float s = 0.f;
 #pragma unroll
-          for (int w = 0; w < ST_WARPS; w++) s += pv_part[(size_t)w * NREP * HD + idx];
+          for (int w = 0; w < ST_WARPS / 2; w++) s += pv_part[(size_t)w * NREP * HD + idx];
           po[idx] = s;
         }
         // the last CTA of the pair to get here folds the slices in slice order
@@ -560,87 +702,62 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
           }
         }
       }
-      {
-        const StepMat mo = mat(L->wo, nullptr, dim, KC_D);
-        st_issue<R_D, NI_D, 1>(mo, 0, wv[0], tid);
-        st_issue<R_D, NI_D, 1>(mo, 1, wv[1], tid);
-      }
-      if (!st_grid_sync(a, gen)) return;
+      stamp(4);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(5);
 
       // ================================================================ P4: h += Wo attn
       stage_copy(a.attn, dim);
-      {
-        const StepMat mo = mat(L->wo, nullptr, dim, KC_D);
-        const StepMat mg = mat(L->w1, L->w3, hidden, KC_D);
-        st_project<R_D, NI_D, 1, MT>(mo, xs, dim, M, part, wv, tid,
-                                     [&](int row, int m, float s, float) {
-                                       __half* hp = a.h + (size_t)m * dim + row;
-                                       *hp = hadd1(__ldcg(hp), __float2half_rn(s));
-                                     },
-                                     [&](int q, uint4 (&buf)[8]) { st_issue<R_G, NI_D, 2>(mg, q, buf, tid); });
-      }
-      if (!st_grid_sync(a, gen)) return;
+      st_project<RS_D, NI_D, 1, MT>(dim, KC_D, xs, M, ring, full, rg, seq, part, a, tid, residual,
+                                         [&](int row, int m, float s, float, __half prev) {
+                                           a.h[(size_t)m * dim + row] = hadd1(prev, __float2half_rn(s));
+                                         },
+                                         refill);
+      stamp(6);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(7);
 
       // ================================================================ P5: norm -> silu(W1 x) * (W3 x)
       stage_norm([&](int m) -> const __half* { return a.h + (size_t)m * dim; }, L->ffn_norm);
-      {
-        const StepMat mg = mat(L->w1, L->w3, hidden, KC_D);
-        const StepMat md = mat(L->w2, nullptr, dim, KC_H);
-        st_project<R_G, NI_D, 2, MT>(mg, xs, dim, M, part, wv, tid,
-                                     [&](int row, int m, float sa, float sb) {
-                                       a.ffn[(size_t)m * hidden + row] = jg_silu_mul(__float2half_rn(sa), __float2half_rn(sb));
-                                     },
-                                     [&](int q, uint4 (&buf)[8]) { st_issue<R_H, NI_H, 1>(md, q, buf, tid); });
-      }
-      if (!st_grid_sync(a, gen)) return;
+      st_project<RS_G, NI_D, 2, MT>(hidden, KC_D, xs, M, ring, full, rg, seq, part, a, tid, no_pre,
+                                         [&](int row, int m, float sa, float sb, __half) {
+                                           a.ffn[(size_t)m * hidden + row] = jg_silu_mul(__float2half_rn(sa), __float2half_rn(sb));
+                                         },
+                                         refill);
+      stamp(8);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(9);
 
       // ================================================================ P6: h += W2 ffn
       stage_copy(a.ffn, hidden);
-      {
-        const StepMat md = mat(L->w2, nullptr, dim, KC_H);
-        const bool more = l + 1 < a.n_layers;
-        const StepMat mn = more ? mat(a.layers[l + 1].wqkv, nullptr, qkv_dim, KC_D) : mat(a.out_w, nullptr, a.vocab, KC_D);
-        st_project<R_H, NI_H, 1, MT>(md, xs, hidden, M, part, wv, tid,
-                                     [&](int row, int m, float s, float) {
-                                       __half* hp = a.h + (size_t)m * dim + row;
-                                       *hp = hadd1(__ldcg(hp), __float2half_rn(s));
-                                     },
-                                     [&](int q, uint4 (&buf)[8]) { st_issue<R_D, NI_D, 1>(mn, q, buf, tid); });
-      }
-      if (!st_grid_sync(a, gen)) return;
+      st_project<RS_H, NI_H, 1, MT>(dim, KC_H, xs, M, ring, full, rg, seq, part, a, tid, residual,
+                                         [&](int row, int m, float s, float, __half prev) {
+                                           a.h[(size_t)m * dim + row] = hadd1(prev, __float2half_rn(s));
+                                         },
+                                         refill);
+      stamp(10);
+      if (!st_grid_sync(a, gen)) { give_up(4); return; }
+      stamp(11);
     }
 
     // ================================================================== final norm -> logits, (value, lowest index) key
     stage_norm([&](int m) -> const __half* { return a.h + (size_t)m * dim; }, a.out_norm);
     {
       unsigned long long best = 0ull;
-      const StepMat ml = mat(a.out_w, nullptr, a.vocab, KC_D);
-      const bool again = step + 1 < a.n_steps;
-      const StepMat m0 = mat(a.layers[0].wqkv, nullptr, qkv_dim, KC_D);
-      st_project<R_D, NI_D, 1, MT>(ml, xs, dim, M, part, wv, tid,
-                                   [&](int row, int m, float s, float) {
-                                     const __half v = __float2half_rn(s);
-                                     a.logits[(size_t)m * a.vocab + row] = v;
-                                     const unsigned long long k = argmax_key(v, (uint32_t)row);
-                                     best = k > best ? k : best;
-                                   },
-                                   [&](int q, uint4 (&buf)[8]) {
-                                     if (again) st_issue<R_D, NI_D, 1>(m0, q, buf, tid);
-                                   });
-      if (warp == 0) {  // the finishing threads are tid < R_D * MT, row-major over (r, m)
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-          unsigned long long v = (tid < R_D * MT && (tid % MT) == m) ? best : 0ull;
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
-            v = other > v ? other : v;
-          }
-          if (lane == 0 && m < M && v != 0ull) atomicMax(a.key + m, v);
-        }
-      }
+      st_project<RS_D, NI_D, 1, MT>(a.vocab, KC_D, xs, M, ring, full, rg, seq, part, a, tid, no_pre,
+                                         [&](int row, int m, float s, float, __half) {
+                                           const __half v = __float2half_rn(s);
+                                           a.logits[(size_t)m * a.vocab + row] = v;
+                                           const unsigned long long k = argmax_key(v, (uint32_t)row);
+                                           best = k > best ? k : best;
+                                         },
+                                         refill);
+      // lane 0 of warp o finished output o = r * MT + m of every pass
+      if (lane == 0 && warp < RS_D * MT && (warp % MT) < M && best != 0ull) atomicMax(a.key + (warp % MT), best);
     }
-    if (!st_grid_sync(a, gen)) return;
+    stamp(12);
+    if (!st_grid_sync(a, gen)) { give_up(4); return; }
+    stamp(13);
     // every CTA reads the pick (the next step's embedding row); CTA 0 publishes it
 #pragma unroll
     for (int m = 0; m < MT; m++) {
@@ -665,27 +782,44 @@ struct jg_step {
   jg_kvcache* kv;
   StepArgs args;  // everything but the per-call buffers
   StepLayer* d_layers;
-  int variant;    // index into the instantiation table
+  int variant[2];  // index into the instantiation table: 1-row kernel, 2-row kernel
   int grid;
   int max_rows;
-  size_t smem;
+  size_t smem[2];      // dynamic shared memory of the 1-row and the 2-row kernel
+  int nslot[2], ring_offset[2], slot_bytes[2];
   int max_slices;
+  uint64_t steps_run, launches_run;
 };
 
 typedef void (*StepKernel)(const StepArgs);
-struct StepVariant { int mt, hd, nrep, ni_d, ni_h; StepKernel kern; };
-#define ST_VARIANT(MT, HD, NREP, NID, NIH) {MT, HD, NREP, NID, NIH, jg_step_kernel<MT, HD, NREP, NID, NIH>}
+struct StepVariant { int mt, hd, nrep, rs_d, rs_g, rs_h, ni_d, ni_h; StepKernel kern; };
+#define ST_VARIANT(MT, HD, NREP, RSD, RSG, RSH, NID, NIH) {MT, HD, NREP, RSD, RSG, RSH, NID, NIH, jg_step_kernel<MT, HD, NREP, RSD, RSG, RSH, NID, NIH>}
+// Per model shape: the 1-row kernel with 64 KB passes, the 1-row kernel with 32 KB passes, the 2-row kernel with 32 KB
+// passes (two activation rows leave room for fewer bytes of ring).
 static const StepVariant g_step_variants[] = {
-    ST_VARIANT(1, 128, 4, 1, 4), ST_VARIANT(2, 128, 4, 1, 4),  // Llama-3.1-8B: dim 4096, hidden 14336
-    ST_VARIANT(1, 64, 4, 1, 2),  ST_VARIANT(2, 64, 4, 1, 2),   // Llama-3.2-1B: dim 2048, hidden 8192
-    ST_VARIANT(1, 128, 3, 1, 2), ST_VARIANT(2, 128, 3, 1, 2),  // Llama-3.2-3B: dim 3072, hidden 8192
+    // Llama-3.1-8B: dim 4096, hidden 14336
+    ST_VARIANT(1, 128, 4, 8, 4, 2, 1, 4), ST_VARIANT(1, 128, 4, 4, 2, 1, 1, 4), ST_VARIANT(2, 128, 4, 4, 2, 1, 1, 4),
+    // Llama-3.2-1B: dim 2048, hidden 8192
+    ST_VARIANT(1, 64, 4, 8, 4, 4, 1, 2), ST_VARIANT(1, 64, 4, 8, 4, 2, 1, 2), ST_VARIANT(2, 64, 4, 8, 4, 2, 1, 2),
+    // Llama-3.2-3B: dim 3072, hidden 8192
+    ST_VARIANT(1, 128, 3, 8, 4, 4, 1, 2), ST_VARIANT(1, 128, 3, 5, 2, 2, 1, 2), ST_VARIANT(2, 128, 3, 5, 2, 2, 1, 2),
 };
 
-static int ni_for(int K) {  // chunk iterations per lane: the smallest of 1, 2, 4, 8 that covers K / 8 chunks with 512 lanes
-  const int kc = K / 8;
-  for (int ni = 1; ni <= 8; ni *= 2)
-    if (kc <= ST_THREADS * ni) return ni;
-  return 0;
+static int ni_for(int K) { return (K / 8 + ST_THREADS - 1) / ST_THREADS; }  // 16-byte chunks per thread and row
+static int rs_for(int slot_bytes, int K, int matrices, int cap) {            // whole rows of `matrices` matrices per slot
+  const int r = slot_bytes / (matrices * K * 2);
+  return r < cap ? r : cap;
+}
+static int find_variant(int mt, int hd, int nrep, int dim, int hidden, int slot_bytes) {
+  const int ni_d = ni_for(dim), ni_h = ni_for(hidden);
+  const int cap = ST_WARPS / mt;  // one output per finishing warp
+  const int rs_d = rs_for(slot_bytes, dim, 1, cap < 8 ? cap : 8), rs_g = rs_for(slot_bytes, dim, 2, 4), rs_h = rs_for(slot_bytes, hidden, 1, cap < 8 ? cap : 8);
+  const int nv = (int)(sizeof(g_step_variants) / sizeof(g_step_variants[0]));
+  for (int i = 0; i < nv; i++) {
+    const StepVariant& v = g_step_variants[i];
+    if (v.mt == mt && v.hd == hd && v.nrep == nrep && v.ni_d == ni_d && v.ni_h == ni_h && v.rs_d == rs_d && v.rs_g == rs_g && v.rs_h == rs_h) return i;
+  }
+  return -1;
 }
 
 static void step_destroy_now(void* p) {
@@ -696,6 +830,22 @@ static void step_destroy_now(void* p) {
   if (s->args.tickets) cudaFree(s->args.tickets);
   if (s->args.bar) cudaFree(s->args.bar);
   if (s->args.key) cudaFree(s->args.key);
+  if (s->args.prof) {
+    unsigned long long t[32];
+    if (cudaMemcpy(t, s->args.prof, sizeof(t), cudaMemcpyDeviceToHost) == cudaSuccess && t[30] > 0) {
+      s->steps_run = t[30];
+      s->launches_run = t[14];
+      static const char* names[14] = {"norm+qkv", "barrier", "scores", "barrier", "p.v+fold", "barrier", "wo", "barrier", "norm+gate/up",
+                                      "barrier", "down", "barrier", "norm+logits", "barrier"};
+      fprintf(stderr, "[jg_step] mean microseconds per step over %llu steps (CTA 0 | last CTA):\n", (unsigned long long)s->steps_run);
+      for (int i = 0; i < 14; i++)
+        fprintf(stderr, "[jg_step]   %-13s %9.1f | %9.1f\n", names[i], t[i] / 1e3 / (double)s->steps_run, t[16 + i] / 1e3 / (double)s->steps_run);
+      if (s->args.bar_probe > 0)
+        fprintf(stderr, "[jg_step]   %d back-to-back barriers per launch: %.2f us each\n", s->args.bar_probe,
+                t[15] / 1e3 / (double)s->launches_run / s->args.bar_probe);
+    }
+    cudaFree(s->args.prof);
+  }
   delete s;
 }
 
@@ -710,41 +860,51 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   JG_REQUIRE(jg_aligned(d.tok_embeddings, 16) && jg_aligned(d.out_norm, 16) && jg_aligned(d.output, 16) && jg_aligned(d.freqs_cis, 16) && d.freqs_rows > 0,
              "step_create: model tensors must be 16-byte aligned");
   const int nrep = k.n_heads / k.n_kv_heads;
-  const int ni_d = ni_for(d.dim), ni_h = ni_for(d.hidden_dim);
-  int variant = -1;
-  const int nv = (int)(sizeof(g_step_variants) / sizeof(g_step_variants[0]));
-  for (int i = 0; i < nv; i++)
-    if (g_step_variants[i].mt == 1 && g_step_variants[i].hd == k.head_dim && g_step_variants[i].nrep == nrep &&
-        g_step_variants[i].ni_d == ni_d && g_step_variants[i].ni_h == ni_h) { variant = i; break; }
-  if (variant < 0 || k.n_heads * k.head_dim != d.dim) {
-    jg_set_error("step_create: no single-kernel step for dim %d, hidden %d, head_dim %d, %d query heads per kv head", d.dim, d.hidden_dim, k.head_dim, nrep);
-    return JG_ENOTSUP;
-  }
   const int max_rows = 2;
   const int grid = dev->sm_count;
   JG_REQUIRE(grid >= max_rows * k.n_kv_heads, "step_create: fewer SMs than (row, kv head) pairs");
   // context slices per (row, kv head): as many as the CTAs allow (at most 32); one slice's scores must fit
   const int slices_min = grid / (max_rows * k.n_kv_heads) < 32 ? grid / (max_rows * k.n_kv_heads) : 32;
   const int chunk_cap = ((kv->max_ctx + slices_min - 1) / slices_min + 31) & ~31;
-  const size_t att_bytes = ((size_t)nrep * chunk_cap + (size_t)ST_WARPS * nrep * k.head_dim + (size_t)nrep * k.head_dim) * sizeof(float);
-  const size_t x_bytes = (size_t)max_rows * (d.dim > d.hidden_dim ? d.dim : d.hidden_dim) * sizeof(__half);
-  const size_t smem = att_bytes > x_bytes ? att_bytes : x_bytes;
-  if (smem + 8 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) {
-    jg_set_error("step_create: %zu bytes of shared memory per CTA needed, the device allows %zu", smem, (size_t)dev->prop.sharedMemPerBlockOptin);
-    return JG_ENOTSUP;
+  const size_t att_bytes = ((size_t)nrep * chunk_cap + (size_t)(ST_WARPS / 2) * nrep * k.head_dim) * sizeof(float);
+  size_t smem[2];
+  int nslot[2], ring_offset[2], slot_bytes[2], variant[2];
+  const char* ke = getenv("JG_STEP_SLOT_KB");
+  for (int mt = 1; mt <= 2; mt++) {
+    const size_t x_bytes = (size_t)mt * (d.dim > d.hidden_dim ? d.dim : d.hidden_dim) * sizeof(__half);
+    const size_t head = ((att_bytes > x_bytes ? att_bytes : x_bytes) + 127) & ~(size_t)127;
+    const long long room = (long long)dev->prop.sharedMemPerBlockOptin - 4096 - (long long)head;  // 4 KB: the kernel's static arrays
+    // 64 KB passes (half the barriers and epilogues per byte) where three of them fit, else 32 KB ones
+    int sb = (mt == 1 && room >= 3 * 65536) ? 65536 : 32768;
+    if (ke && atoi(ke) == 32) sb = 32768;
+    int ns = (int)(room / sb);
+    if (ns > ST_MAX_SLOTS) ns = ST_MAX_SLOTS;
+    const char* se = getenv("JG_STEP_SLOTS");
+    if (se && atoi(se) >= 2 && atoi(se) < ns) ns = atoi(se);
+    const int vi = (k.n_heads * k.head_dim == d.dim && nrep <= 4) ? find_variant(mt, k.head_dim, nrep, d.dim, d.hidden_dim, sb) : -1;
+    if (ns < 2 || vi < 0) {
+      jg_set_error("step_create: no single-kernel step for dim %d, hidden %d, head_dim %d, %d query heads per kv head (%d slots of %d bytes)",
+                   d.dim, d.hidden_dim, k.head_dim, nrep, ns, sb);
+      return JG_ENOTSUP;
+    }
+    nslot[mt - 1] = ns; ring_offset[mt - 1] = (int)head; slot_bytes[mt - 1] = sb; variant[mt - 1] = vi;
+    smem[mt - 1] = head + (size_t)ns * sb;
   }
   int coop = 0;
   JG_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev->ordinal));
   if (!coop) { jg_set_error("step_create: the device does not support cooperative launches"); return JG_ENOTSUP; }
-  for (int i = variant; i < variant + 2; i++) {
-    JG_CUDA(cudaFuncSetAttribute(g_step_variants[i].kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  for (int i = 0; i < 2; i++) {
+    JG_CUDA(cudaFuncSetAttribute(g_step_variants[variant[i]].kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem[i]));
     int per_sm = 0;
-    JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, g_step_variants[i].kern, ST_THREADS, smem));
+    JG_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, g_step_variants[variant[i]].kern, ST_THREADS, smem[i]));
     if (per_sm < 1) { jg_set_error("step_create: the step kernel does not fit an SM"); return JG_ENOTSUP; }
   }
   jg_step* s = new jg_step();
   memset(s, 0, sizeof(*s));
-  s->dev = dev; s->kv = kv; s->variant = variant; s->grid = grid; s->max_rows = max_rows; s->smem = smem; s->max_slices = 32;
+  s->dev = dev; s->kv = kv; s->grid = grid; s->max_rows = max_rows; s->max_slices = 32;
+  for (int i = 0; i < 2; i++) {
+    s->smem[i] = smem[i]; s->nslot[i] = nslot[i]; s->ring_offset[i] = ring_offset[i]; s->slot_bytes[i] = slot_bytes[i]; s->variant[i] = variant[i];
+  }
   StepArgs& a = s->args;
   a.tok_emb = (const __half*)d.tok_embeddings; a.out_norm = (const __half*)d.out_norm; a.out_w = (const __half*)d.output;
   a.table = (const __half*)d.freqs_cis; a.table_rows = d.freqs_rows;
@@ -753,10 +913,9 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   a.page = k.page_size; a.page_shift = ilog2(k.page_size); a.max_pages_per_seq = k.max_pages_per_seq; a.max_ctx = kv->max_ctx;
   a.chunk_cap = chunk_cap;
   a.eps = d.norm_eps; a.scale = 1.0f / sqrtf((float)k.head_dim); a.recip_dim = 1.0f / (float)d.dim;
+  a.bar_probe = (getenv("JG_STEP_PROF") != nullptr && atoi(getenv("JG_STEP_PROF")) == 2) ? 64 : 0;
   const char* te = getenv("JG_STEP_TIMEOUT_MS");
   a.timeout_ns = (unsigned long long)(te ? atoll(te) : 2000) * 1000000ull;
-  const char* ge = getenv("JG_STEP_L2_ROWS");
-  a.l2_gu_rows = ge ? atoi(ge) : 16;
   // the layers' tensors, as a device table
   const uint64_t* lp = (const uint64_t*)(uintptr_t)d.layers;
   StepLayer* hl = new StepLayer[d.n_layers];
@@ -776,6 +935,10 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   if (e == cudaSuccess) e = cudaMalloc(&a.tickets, pairs * sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMalloc(&a.bar, 64 * sizeof(unsigned int));
   if (e == cudaSuccess) e = cudaMalloc(&a.key, 2 * sizeof(unsigned long long));
+  if (e == cudaSuccess && getenv("JG_STEP_PROF") != nullptr && atoi(getenv("JG_STEP_PROF")) != 0) {
+    e = cudaMalloc(&a.prof, 32 * sizeof(unsigned long long));
+    if (e == cudaSuccess) e = cudaMemsetAsync(a.prof, 0, 32 * sizeof(unsigned long long), dev->stream);
+  }
   if (e == cudaSuccess) e = cudaMemsetAsync(a.tickets, 0, pairs * sizeof(unsigned int), dev->stream);
   if (e == cudaSuccess) e = cudaMemsetAsync(a.bar, 0, 64 * sizeof(unsigned int), dev->stream);
   if (e == cudaSuccess) e = cudaStreamSynchronize(dev->stream);
@@ -821,13 +984,17 @@ JG_API int jg_step_run(jg_step* s, uint64_t tokens, uint64_t pos, uint64_t h, ui
   if (sl > s->max_slices) sl = s->max_slices;
   a.slices = sl;
   JG_REQUIRE((long long)sl * a.chunk_cap >= a.max_ctx, "step_run: context slices do not cover the cache");
-  const StepVariant& v = g_step_variants[s->variant + (B > 1 ? 1 : 0)];
+  const int vi = B > 1 ? 1 : 0;
+  const StepVariant& v = g_step_variants[s->variant[vi]];
+  a.nslot = s->nslot[vi];
+  a.slot_bytes = s->slot_bytes[vi];
+  a.ring_offset = s->ring_offset[vi];
   // the arrival count starts at zero whatever an earlier launch that ran out of time left behind
   JG_CUDA(cudaMemsetAsync(a.bar, 0, sizeof(unsigned int), dev->stream));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(s->grid);
   cfg.blockDim = dim3(ST_THREADS);
-  cfg.dynamicSmemBytes = s->smem;
+  cfg.dynamicSmemBytes = s->smem[vi];
   cfg.stream = dev->stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeCooperative;
@@ -836,6 +1003,8 @@ JG_API int jg_step_run(jg_step* s, uint64_t tokens, uint64_t pos, uint64_t h, ui
   cfg.numAttrs = 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, v.kern, (const StepArgs)a);
   if (e != cudaSuccess) return jg_cuda_fail(e, "step", __FILE__, __LINE__);
+  s->steps_run += (uint64_t)n_steps;
+  s->launches_run++;
   dev->tc_pending = true;  // the error word is looked at after the next synchronisation
   return jg_after_launch(dev, "step");
 }

@@ -443,7 +443,7 @@ class Transformer:
         if self._step_plan is None:
             self._step_plan = False
             a0 = self.layers[0].attention
-            plain = (self.fused and self._tp is None and os.environ.get("JG_STEP_KERNEL", "0") != "0"
+            plain = (self.fused and self._tp is None and os.environ.get("JG_STEP_KERNEL", "1") != "0"
                      and type(a0.wo) is Linear and type(self.output) is Linear and type(self.tok_embeddings) is Embedding
                      and type(self.layers[0].feed_forward) is FeedForward)
             if plain:

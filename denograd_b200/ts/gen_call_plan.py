@@ -1,6 +1,6 @@
 """Writes call_plan.json next to this file: for each block-level method of llama_cuda.ts, the ordered list of C entry
-points it calls with their argument expressions, taken from the `cu(dev, '<entry>', ...)` lines of the TypeScript
-source.  tests/test_ts_seam.py holds both the TypeScript source and the Python twin (denograd_b200/llama.py, run on a
+points it calls with their argument expressions, taken from the `cu(dev, '<entry>', ...)` and
+`cu_h('<entry>', <handle>, ...)` lines of the TypeScript source (the handle is left out).  tests/test_ts_seam.py holds both the TypeScript source and the Python twin (denograd_b200/llama.py, run on a
 recording stand-in for the library) to this file, so the two host sides cannot drift apart unnoticed.
 
     python denograd_b200/ts/gen_call_plan.py
@@ -12,7 +12,7 @@ import os
 import re
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-METHODS = ("decode_step_fused", "decode_step_rows", "prefill_chunk", "decode_step", "forward")
+METHODS = ("decode_step_fused", "decode_step_rows", "prefill_chunk", "decode_step", "decode_step_single", "forward")
 
 
 def split_args(s: str) -> list[str]:
@@ -42,8 +42,10 @@ def parse_ts(path: str) -> dict[str, list[dict]]:
         end = src.index("\n  }\n", m.start())
         body = src[m.start():end]
         calls = []
-        for c in re.finditer(r"\bcu\(dev, '(jg_\w+)', (.*)\)\s*$", body, flags=re.M):
-            calls.append({"entry": c.group(1), "args": split_args(c.group(2))})
+        # `cu(dev, '<entry>', args...)`, or `cu_h('<entry>', <handle>, args...)` for entry points taking another handle
+        for c in re.finditer(r"\bcu(?:\(dev, |_h\()'(jg_\w+)', (.*)\)\s*$", body, flags=re.M):
+            args = split_args(c.group(2))
+            calls.append({"entry": c.group(1), "args": args[1:] if "cu_h(" in c.group(0) else args})
         plan[name] = calls
     return plan
 

@@ -205,6 +205,30 @@ export class CudaTransformerBlock {
   }
 }
 
+/** The model's decode step as one persistent kernel (jg_step_create): the table of the layers' tensors and the kernel's
+ *  scratch.  The tensors' addresses are fixed at creation, like those a captured graph holds.  `handle` stays null when
+ *  the library has no such kernel for the model's shape (status 95): the launch-per-op step is used then. */
+class StepPlan {
+  handle: Deno.PointerValue = null
+  private table: BigUint64Array // kept alive: the library reads it during create only, but the desc points at it
+  constructor(dev: CUDA, m: CudaTransformer) {
+    this.table = new BigUint64Array(m.layers.length * 7)
+    m.layers.forEach((l, i) => this.table.set([l.attention_norm.ptr, l.attention.wqkv.ptr, l.attention.wo.ptr, l.ffn_norm.ptr, l.feed_forward.w1.ptr, l.feed_forward.w3.ptr, l.feed_forward.w2.ptr], i * 7))
+    const desc = new DataView(new ArrayBuffer(72)) // jg_step_desc: 6 x int32, float, int32, 5 x uint64
+    ;[m.layers.length, m.dim, m.hidden_dim, m.n_heads, m.vocab_size, m.max_context * 2].forEach((v, i) => desc.setInt32(4 * i, v, true))
+    desc.setFloat32(24, m.norm.eps, true)
+    const table_addr = BigInt(Deno.UnsafePointer.value(Deno.UnsafePointer.of(this.table)))
+    ;[table_addr, m.tok_embeddings.ptr, m.norm.ptr, m.output.ptr, m.freqs_cis.ptr].forEach((v, i) => desc.setBigUint64(32 + 8 * i, v, true))
+    const out = new BigUint64Array(1)
+    try {
+      cu_h('jg_step_create', dev.handle, m.kv.handle as unknown as bigint, new Uint8Array(desc.buffer) as unknown as bigint, out as unknown as bigint)
+      this.handle = Deno.UnsafePointer.create(out[0])
+    } catch (e) {
+      if (!String(e).includes('status 95')) throw e
+    }
+  }
+}
+
 export class CudaTransformer {
   layers: CudaTransformerBlock[]
   norm: CudaRMSNorm
@@ -214,6 +238,7 @@ export class CudaTransformer {
   head_dim: number
   dev!: CUDA
   kv!: KVCache
+  private step_plan?: StepPlan
   private ws = new Map<number, Workspace>()
   private step_graph = new Map<number, CUDAGraph>()
   private calls = new Map<number, number>()
@@ -246,9 +271,23 @@ export class CudaTransformer {
     return this.ws.get(key)!
   }
 
+  /** The plan of the single-kernel step when this model and row count can take it: fp16 weights, 1-2 rows. */
+  private single_kernel_step = (B: number): StepPlan | undefined => {
+    if (B > 2 || this.output.scale_ptr !== 0n || this.tok_embeddings.scale_ptr !== 0n) return undefined
+    if (this.step_plan === undefined) this.step_plan = new StepPlan(this.dev, this)
+    return this.step_plan.handle !== null ? this.step_plan : undefined
+  }
+
+  /** The whole step as one launch of the persistent kernel (one step, nothing fed back). */
+  private decode_step_single = (plan: StepPlan, ws: Workspace, B: number) => {
+    cu_h('jg_step_run', plan.handle, ws.tokens, ws.pos, ws.h, ws.qkv, ws.attn, ws.ffn, ws.logits, ws.next_tokens, B, 1, 0)
+  }
+
   /** One token per row: reads ws.tokens / ws.pos, leaves the fp16 logits and the greedy ids in the workspace. */
   private decode_step = (ws: Workspace) => {
     const dev = this.dev, B = ws.B, int8 = this.output.scale_ptr !== 0n
+    const plan = this.single_kernel_step(B)
+    if (plan !== undefined) return this.decode_step_single(plan, ws, B)
     const fused = !norm_first(B, int8, this.dim)
     cu(dev, 'jg_embed', ws.h, ws.tokens, this.tok_embeddings, this.tok_embeddings.scale_ptr, B, this.dim, this.vocab_size)
     for (const layer of this.layers) {

@@ -35,7 +35,7 @@ class Recorder:
         elif name == "jg_alloc":
             args[2]._obj.value = self._next_ptr
             self._next_ptr += (int(args[1]) + 255) // 256 * 256
-        elif name in ("jg_kvcache_create", "jg_graph_end"):
+        elif name in ("jg_kvcache_create", "jg_graph_end", "jg_step_create"):
             args[-1]._obj.value = self._handle()
         elif name == "jg_host_alloc":
             buf = C.create_string_buffer(int(args[0]))
@@ -55,7 +55,8 @@ class Recorder:
         """Recorded compute calls (everything but allocation, copies and bookkeeping), device handle stripped."""
         skip = {"jg_alloc", "jg_free", "jg_copyin", "jg_copyout", "jg_memset", "jg_host_alloc", "jg_host_free", "jg_device_open",
                 "jg_device_props", "jg_device_sync", "jg_launch_count", "jg_kvcache_create", "jg_kvcache_destroy",
-                "jg_kvcache_bytes", "jg_copyin_async", "jg_copyout_async", "jg_copy", "jg_freqs_cis"}
+                "jg_kvcache_bytes", "jg_copyin_async", "jg_copyout_async", "jg_copy", "jg_freqs_cis", "jg_step_create",
+                "jg_step_destroy"}
         return [(c[0],) + c[2:] for c in self.calls[since:] if c[0] not in skip]
 
 

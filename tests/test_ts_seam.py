@@ -77,8 +77,9 @@ def check_calls(recorded: list[tuple], expected: list[dict], roots: dict, what: 
 
 
 @pytest.mark.parametrize("quant,B,mode", [("float16", 1, "fused"), ("float16", 2, "fused"), ("float16", 4, "rows"), ("int8", 1, "fused"), ("int8", 3, "rows")])
-def test_python_twin_issues_the_planned_decode_step(quant, B, mode):
+def test_python_twin_issues_the_planned_decode_step(quant, B, mode, monkeypatch):
     P = plan()
+    monkeypatch.setenv("JG_STEP_KERNEL", "0")  # the launch-per-op step (the single-kernel one has its own test below)
     with recording() as rec:
         from denograd_b200.llama3 import Llama3
         args = dict(TINY, dim=512) if quant == "int8" else TINY  # the int8 one-row kernel wants dim % 512 == 0
@@ -99,6 +100,26 @@ def test_python_twin_issues_the_planned_decode_step(quant, B, mode):
         tail = got[1 + L * per:]
         want_tail = [P["decode_step"][1], P["decode_step"][4]] if mode == "fused" else P["decode_step"][2:5]
         check_calls(tail, want_tail, top, "output layer")
+        del llm, m, ws
+
+
+@pytest.mark.parametrize("B", [1, 2])
+def test_python_twin_issues_the_single_kernel_step(B):
+    """fp16 weights, 1-2 rows: the whole step is one jg_step_run on the plan's handle, same arguments on both sides."""
+    P = plan()
+    with recording() as rec:
+        from denograd_b200.llama3 import Llama3
+        llm = Llama3(size="1B", args=TINY, max_context=64, max_batch=2, tied_output=False, temperature=0)
+        m = llm.model
+        ws = m._workspace(B)
+        n0 = len(rec.calls)
+        m._step(ws)
+        got = rec.kernels(n0)
+        created = [c for c in rec.calls[n0:] if c[0] == "jg_step_create"]
+        assert len(created) == 1 and [c[0] for c in got] == ["jg_step_run"], [c[0] for c in got]
+        check_calls(got[:1], P["decode_step_single"], {"ws": ws, "this": m, "B": B}, "single-kernel step")
+        m._step(ws)  # the plan is made once
+        assert sum(1 for c in rec.calls[n0:] if c[0] == "jg_step_create") == 1
         del llm, m, ws
 
 
