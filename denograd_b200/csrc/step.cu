@@ -78,7 +78,8 @@ struct StepArgs {
   size_t layer_elems;
   unsigned long long timeout_ns;
   int n_layers, dim, hidden, H, G, vocab, M, table_rows, page, page_shift, max_pages_per_seq, max_ctx;
-  int slices, chunk_cap;  // context slices per (row, kv head) and the scores one slice can hold
+  int slices, chunk_cap;  // most context slices per (row, kv head) and the scores one slice can hold
+  int slice_len;          // positions a slice aims at
   int advance, n_steps;
   int nslot;        // slots of the weight ring (passes in flight per CTA)
   int bar_probe;    // JG_STEP_PROF=2: that many back-to-back grid barriers at the start of every launch, timed in slot 15
@@ -131,6 +132,7 @@ __device__ __forceinline__ bool st_grid_sync(const StepArgs& a, unsigned& nbar) 
     nbar++;
     const unsigned target = nbar * gridDim.x;
     asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(a.bar) : "memory");
+    // (several polls in flight per CTA were measured: two change nothing, four slow the counter's line down: 1.44 -> 2.26 us)
     unsigned long long t0 = 0;
     for (unsigned polls = 1;; polls++) {
       unsigned v;
@@ -475,6 +477,33 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
   for (int step = 0; step < a.n_steps; step++) {
     for (int l = 0; l < a.n_layers; l++) {
       const StepLayer* L = a.layers + l;
+      // this CTA's share of attention: context slice `slice` of (row b, kv head g); the pages of its first rows are looked
+      // up now, so that the rows themselves can be requested without a dependent load when the projection is over
+      const int n_pairs = M * a.G;
+      const bool mine = bid < n_pairs * a.slices;  // a.slices: the most slices a pair can have (the scratch's stride)
+      const int pair = mine ? bid / a.slices : 0, slice = mine ? bid % a.slices : 0;
+      const int b = pair / a.G, g = pair % a.G;
+      const int sub = lane % LPR, rgrp = lane / LPR;
+      int pb = posv[0];
+#pragma unroll
+      for (int m = 1; m < MT; m++) pb = (b == m) ? posv[m] : pb;
+      const int T = min(max(pb + 1, 1), a.max_ctx);
+      const int pnew = T - 1;
+      // slices of this pair: about a.slice_len positions each (a short context keeps few CTAs busy and the exchanges of
+      // statistics and partials short), never more positions than a slice's scores have room for
+      const int S = min(a.slices, max((T + a.slice_len - 1) / a.slice_len, (T + a.chunk_cap - 1) / a.chunk_cap));
+      const bool att = mine && slice < S;
+      const int chunk = (T + S - 1) / S;
+      const int t0 = slice * chunk, t1 = att ? min(T, t0 + chunk) : t0;
+      const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
+      __half* k_layer = a.k_pool + (size_t)l * a.layer_elems;
+      __half* v_layer = a.v_pool + (size_t)l * a.layer_elems;
+      int pg0[AU];
+#pragma unroll
+      for (int u = 0; u < AU; u++) {
+        const int t = t0 + warp * RPW + rgrp + u * ST_WARPS * RPW;
+        pg0[u] = (att && t < t1) ? bt_row[t >> a.page_shift] : 0;
+      }
       // ================================================================ P1: norm -> qkv
       if (l == 0) {
         // the embedding rows are the block's input (a token outside the table matches no row: zeros); CTA 0 stores them
@@ -496,28 +525,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
       st_project<RS_D, NI_D, 1, MT>(qkv_dim, KC_D, xs, M, ring, full, rg, seq, part, a, tid, no_pre,
                                          [&](int row, int m, float s, float, __half) { a.qkv[(size_t)m * qkv_dim + row] = __float2half_rn(s); },
                                          refill);
+      // the first K and V rows of this CTA's context slice are requested now, ahead of the barrier: cached rows do not
+      // depend on this step's projection (the new position's row does and is fetched again once it has been written)
+      uint4 k0[AU], v0[AU];
+#pragma unroll
+      for (int u = 0; u < AU; u++) {
+        const int t = t0 + warp * RPW + rgrp + u * ST_WARPS * RPW;
+        const bool ld = att && t < t1 && t != pnew;
+        const size_t off = (((size_t)pg0[u] * a.G + g) * a.page + (t & (a.page - 1))) * HD + sub * 8;
+        k0[u] = ld ? ld_cg_128(k_layer + off) : make_uint4(0, 0, 0, 0);
+        v0[u] = ld ? ld_cg_128(v_layer + off) : make_uint4(0, 0, 0, 0);
+      }
       stamp(0);
       if (!st_grid_sync(a, gen)) { give_up(4); return; }
       stamp(1);
       if (l == 0 && bid == 0 && tid < M) a.key[tid] = 0ull;  // every CTA has read the previous step's key by now
 
       // ================================================================ P2: RoPE, cache write, scores of a context slice
-      const int n_pairs = M * a.G;
-      const bool att = bid < n_pairs * a.slices;
-      const int pair = att ? bid / a.slices : 0, slice = att ? bid % a.slices : 0;
-      const int b = pair / a.G, g = pair % a.G;
-      const int sub = lane % LPR, rgrp = lane / LPR;
-      int pb = posv[0];
-#pragma unroll
-      for (int m = 1; m < MT; m++) pb = (b == m) ? posv[m] : pb;
-      const int T = min(max(pb + 1, 1), a.max_ctx);
-      const int pnew = T - 1;
-      const int chunk = min((T + a.slices - 1) / a.slices, a.chunk_cap);
-      const int t0 = slice * chunk, t1 = att ? min(T, t0 + chunk) : t0;
-      const int32_t* bt_row = a.block_table + (size_t)b * a.max_pages_per_seq;
-      __half* k_layer = a.k_pool + (size_t)l * a.layer_elems;
-      __half* v_layer = a.v_pool + (size_t)l * a.layer_elems;
-      uint4 v0[AU];
       if (att) {
         const __half* xrow = a.qkv + (size_t)b * qkv_dim;
         const uint4 traw = ld_128(a.table + ((size_t)min(pnew, a.table_rows - 1) * (HD / 2) + (size_t)sub * 4) * 2);
@@ -542,13 +566,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
 #pragma unroll
           for (int u = 0; u < AU; u++) {
             const int t = tb + u * ST_WARPS * RPW;
-            kk[u] = (t < t1) ? ld_cg_128(kv_row(k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
-          }
-          if (base == t0) {
-#pragma unroll
-            for (int u = 0; u < AU; u++) {
-              const int t = tb + u * ST_WARPS * RPW;
-              v0[u] = (t < t1) ? ld_cg_128(kv_row(v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
+            if (base == t0 && t != pnew) {
+              kk[u] = k0[u];  // requested before the barrier
+            } else {
+              kk[u] = (t < t1) ? ld_cg_128(kv_row(k_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
+              if (base == t0) v0[u] = (t < t1) ? ld_cg_128(kv_row(v_layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + sub * 8) : make_uint4(0, 0, 0, 0);
             }
           }
 #pragma unroll
@@ -607,15 +629,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
 
       // ================================================================ P3: probabilities, p.v, fold over the slices
       if (att) {
+        // every (head, slice) pair of statistics is fetched by its own thread (one round trip to L2 for all of them), then
+        // one thread per head combines them in slice order
+        float* ml_s = pv_part;  // [NREP][slices][2], free until the p.v partials are stored
+        if (tid < NREP * S) {
+          const int r = tid / S, j = tid % S;
+          const float2 v = __ldcg(reinterpret_cast<const float2*>(a.att_ml + (((size_t)pair * NREP + r) * a.slices + j) * 2));
+          ml_s[2 * tid] = v.x;
+          ml_s[2 * tid + 1] = v.y;
+        }
+        __syncthreads();
         if (tid < NREP) {
-          const float* ml = a.att_ml + ((size_t)pair * NREP + tid) * a.slices * 2;
+          const float* ml = ml_s + (size_t)tid * S * 2;
           float Mx = -INFINITY;
-          for (int j = 0; j < a.slices; j++) Mx = fmaxf(Mx, __ldcg(ml + 2 * j));
+          for (int j = 0; j < S; j++) Mx = fmaxf(Mx, ml[2 * j]);
           float Ls = 0.f;
-          for (int j = 0; j < a.slices; j++) {
-            const float mj = __ldcg(ml + 2 * j), lj = __ldcg(ml + 2 * j + 1);
-            Ls = __fadd_rn(Ls, __fmul_rn(lj, jg_xexp2_f32(__fmul_rn(__fsub_rn(mj, Mx), log2e))));
-          }
+          for (int j = 0; j < S; j++)
+            Ls = __fadd_rn(Ls, __fmul_rn(ml[2 * j + 1], jg_xexp2_f32(__fmul_rn(__fsub_rn(ml[2 * j], Mx), log2e))));
           s_M[tid] = Mx;
           s_rL[tid] = __fdiv_rn(1.0f, Ls);
         }
@@ -682,13 +712,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
           for (int w = 0; w < ST_WARPS / 2; w++) s += pv_part[(size_t)w * NREP * HD + idx];
           po[idx] = s;
         }
-        // the last CTA of the pair to get here folds the slices in slice order
-        __threadfence();
+        // the last CTA of the pair to get here folds the slices in slice order (the ticket's release covers the whole
+        // CTA's stores: they are ordered before it by the barrier)
         __syncthreads();
         if (tid == 0) {
           unsigned prev;
           asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(prev) : "l"(a.tickets + pair) : "memory");
-          s_last = (prev == (unsigned)a.slices - 1u);
+          s_last = (prev == (unsigned)S - 1u);
           if (s_last) a.tickets[pair] = 0;
           __threadfence();
         }
@@ -697,7 +727,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
           const float* pall = a.att_o + (size_t)pair * a.slices * (NREP * HD);
           for (int idx = tid; idx < NREP * HD; idx += ST_THREADS) {
             float s = 0.f;
-            for (int j = 0; j < a.slices; j++) s = __fadd_rn(s, __ldcg(pall + (size_t)j * (NREP * HD) + idx));
+            for (int j0 = 0; j0 < S; j0 += 8) {  // eight slices' values requested together, added in slice order
+              float v[8];
+#pragma unroll
+              for (int jj = 0; jj < 8; jj++) v[jj] = (j0 + jj < S) ? __ldcg(pall + (size_t)(j0 + jj) * (NREP * HD) + idx) : 0.f;
+#pragma unroll
+              for (int jj = 0; jj < 8; jj++)
+                if (j0 + jj < S) s = __fadd_rn(s, v[jj]);
+            }
             a.attn[(size_t)b * a.H * HD + (size_t)g * NREP * HD + idx] = __float2half_rn(s);
           }
         }
@@ -902,6 +939,8 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   jg_step* s = new jg_step();
   memset(s, 0, sizeof(*s));
   s->dev = dev; s->kv = kv; s->grid = grid; s->max_rows = max_rows; s->max_slices = 32;
+  if (getenv("JG_STEP_SLICES") != nullptr && atoi(getenv("JG_STEP_SLICES")) >= slices_min) s->max_slices = atoi(getenv("JG_STEP_SLICES"));
+  s->args.slice_len = (getenv("JG_STEP_SLICE_LEN") != nullptr && atoi(getenv("JG_STEP_SLICE_LEN")) > 0) ? atoi(getenv("JG_STEP_SLICE_LEN")) : 48;
   for (int i = 0; i < 2; i++) {
     s->smem[i] = smem[i]; s->nslot[i] = nslot[i]; s->ring_offset[i] = ring_offset[i]; s->slot_bytes[i] = slot_bytes[i]; s->variant[i] = variant[i];
   }
