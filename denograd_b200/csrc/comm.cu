@@ -403,6 +403,15 @@ int jg_peer_fill_args(jg_comm* comm, PeerArgs* a, bool consume) {
   return JG_OK;
 }
 
+// The same for a launch that makes `count` exchanges itself (the single-kernel decode step): a->ord is the first of them.
+int jg_peer_fill_args_n(jg_comm* comm, PeerArgs* a, uint32_t count) {
+  JG_REQUIRE(comm != nullptr && count > 0, "peer exchange: null communicator or no exchanges");
+  int rc = jg_peer_fill_args(comm, a, false);
+  if (rc) return rc;
+  g_peer[comm->dev->ordinal].pending += count - 1;
+  return JG_OK;
+}
+
 // One thread: the exchanges of the run that ends here are done; later launches number theirs from the new base.
 __global__ void peer_advance_kernel(uint32_t* base, uint32_t n) {
   pdl_launch();

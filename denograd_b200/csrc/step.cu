@@ -36,6 +36,7 @@
 
 #include "common.cuh"
 #include "kvcache.cuh"
+#include "peer.cuh"
 #include "transcendental.cuh"
 
 constexpr int ST_THREADS = 512;
@@ -82,11 +83,16 @@ struct StepArgs {
   int slice_len;          // positions a slice aims at
   int advance, n_steps;
   int nslot;        // slots of the weight ring (passes in flight per CTA)
+  int q_dim;        // H * head_dim: columns of Wo (a rank's share of the heads under tensor parallelism)
+  int embed_rows;   // rows of the embedding table (the whole vocabulary on every rank)
+  int vocab_offset; // vocabulary index of row 0 of this rank's output matrix
+  uint32_t peer_ord0;  // tensor parallelism: ordinal of the launch's first exchange (peer.ord is not used)
   int bar_probe;    // JG_STEP_PROF=2: that many back-to-back grid barriers at the start of every launch, timed in slot 15
   int slot_bytes;   // bytes of one slot = of one pass: a few whole rows of one matrix (or of the gate / up pair)
   int ring_offset;  // bytes from the start of dynamic shared memory to the ring
   unsigned long long* prof;  // JG_STEP_PROF=1: [2][16] nanoseconds per phase, summed over layers and steps (CTA 0, last CTA)
   float eps, scale, recip_dim;
+  PeerArgs peer;  // tensor parallelism (peer.world > 1): the ranks' exchange buffers, as in the stand-alone projections
 };
 
 constexpr int ST_MAX_SLOTS = 6;
@@ -194,7 +200,7 @@ __device__ __forceinline__ void st_stream_enter(StepStream& st, const StepArgs& 
   uint32_t row_bytes = (uint32_t)a.dim * 2u;
   switch (st.phase) {
     case 0: N = qkv_dim; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(L->wqkv); break;
-    case 1: N = a.dim; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(L->wo); break;
+    case 1: N = a.dim; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(L->wo); row_bytes = (uint32_t)a.q_dim * 2u; break;
     case 2: N = a.hidden; rs = RS_G; w0 = reinterpret_cast<const unsigned char*>(L->w1); w1 = reinterpret_cast<const unsigned char*>(L->w3); break;
     case 3: N = a.dim; rs = RS_H; w0 = reinterpret_cast<const unsigned char*>(L->w2); row_bytes = (uint32_t)a.hidden * 2u; break;
     default: N = a.vocab; rs = RS_D; w0 = reinterpret_cast<const unsigned char*>(a.out_w); break;
@@ -342,11 +348,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
   __shared__ float s_rs[MT];
   __shared__ float s_m[4], s_M[4], s_rL[4];
   __shared__ int s_last;
+  __shared__ unsigned long long s_key[MT];
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int bid = blockIdx.x, nb = gridDim.x;
   const int dim = a.dim, hidden = a.hidden, M = a.M;
-  const int KC_D = dim / 8, KC_H = hidden / 8;
+  const int KC_D = dim / 8, KC_H = hidden / 8, KC_Q = a.q_dim / 8;
+  // tensor parallelism: Wo and W2 hold this rank's columns only, so their outputs are partial sums.  Each is sent to every
+  // rank (this one included) as a flag-in-data entry the moment it is complete; when the CTA has multiplied its last
+  // pass of the phase it collects, for the outputs it owns, the entries of all ranks (bounded wait), adds them in rank
+  // order and applies the residual.  Exchange k of the launch carries the number base + k; consecutive exchanges
+  // alternate between the two halves of the buffers, and the grid barrier after a phase keeps a rank from starting
+  // exchange k + 1 before all of its CTAs have read exchange k - 1.
+  const int world = a.peer.world > 1 ? a.peer.world : 1;
+  const uint32_t peer_base = world > 1 ? a.peer.epoch[0] + a.peer_ord0 : 0u;
   const int qkv_dim = (a.H + 2 * a.G) * HD;
   const float log2e = 1.4426950408889634f;
 
@@ -377,6 +392,38 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
   };
   auto no_pre = [](int, int) { return __float2half_rn(0.f); };
   auto residual = [&](int row, int m) { return __ldcg(a.h + (size_t)m * dim + row); };
+  const uint32_t ex_per_step = (uint32_t)(2 * a.n_layers + 1);  // exchanges of a step: Wo and W2 of every layer, the pick
+  // output (row, m) of a row-parallel projection: the residual add on one GPU, an entry for every rank otherwise
+  auto rowpar_epi = [&](uint32_t ex, int row, int m, float sum, __half prev) {
+    const size_t o = (size_t)m * dim + row;
+    if (world == 1) {
+      a.h[o] = hadd1(prev, __float2half_rn(sum));
+      return;
+    }
+    for (int p = 0; p < world; p++) peer_ll_store(peer_ll(a.peer.buf[p], (int)(ex & 1u), a.peer.rank) + o, sum, ex);
+  };
+  // after the phase's last pass: the outputs this CTA owns (its passes of rs rows) summed over the ranks in rank order
+  auto rowpar_gather = [&](uint32_t ex, int rs) {
+    if (world == 1) return;
+    const int total = (dim + rs - 1) / rs;
+    const int np = bid < total ? (total - bid + nb - 1) / nb : 0;
+    bool ok = true;
+    for (int i = tid; i < np * rs * M; i += ST_THREADS) {
+      const int m = i % M, rr = i / M;
+      const int row = (bid + (rr / rs) * nb) * rs + rr % rs;
+      if (row < dim) {
+        const size_t o = (size_t)m * dim + row;
+        float sum = 0.f;
+        for (int rk = 0; rk < world && ok; rk++) {
+          float v = 0.f;
+          ok = peer_ll_load(peer_ll(a.peer.buf[a.peer.rank], (int)(ex & 1u), rk) + o, ex, a.peer.timeout_ns, &v);
+          sum = __fadd_rn(sum, v);
+        }
+        a.h[o] = hadd1(__ldcg(a.h + o), __float2half_rn(sum));
+      }
+    }
+    if (!ok) atomicCAS(a.peer.err, 0, 1);  // a rank never arrived: the launch's results are void, nobody is waited for
+  };
   // a wait ran out: record it, let the copies still in flight land (bounded) so that none writes into shared memory of
   // a CTA that has gone, and leave
   auto give_up = [&](int code) {
@@ -509,7 +556,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
         // the embedding rows are the block's input (a token outside the table matches no row: zeros); CTA 0 stores them
         // as the residual stream
         auto emb = [&](int m) -> const __half* {
-          return ((unsigned)tok[m] < (unsigned)a.vocab) ? a.tok_emb + (size_t)tok[m] * dim : nullptr;
+          return ((unsigned)tok[m] < (unsigned)a.embed_rows) ? a.tok_emb + (size_t)tok[m] * dim : nullptr;
         };
         if (bid == 0) {
           for (int m = 0; m < M; m++)
@@ -744,12 +791,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
       stamp(5);
 
       // ================================================================ P4: h += Wo attn
-      stage_copy(a.attn, dim);
-      st_project<RS_D, NI_D, 1, MT>(dim, KC_D, xs, M, ring, full, rg, seq, part, a, tid, residual,
-                                         [&](int row, int m, float s, float, __half prev) {
-                                           a.h[(size_t)m * dim + row] = hadd1(prev, __float2half_rn(s));
-                                         },
-                                         refill);
+      stage_copy(a.attn, a.q_dim);
+      {
+        const uint32_t ex = peer_base + (uint32_t)step * ex_per_step + 2u * (uint32_t)l;
+        st_project<RS_D, NI_D, 1, MT>(dim, KC_Q, xs, M, ring, full, rg, seq, part, a, tid, residual,
+                                      [&](int row, int m, float s, float, __half prev) { rowpar_epi(ex, row, m, s, prev); }, refill);
+        rowpar_gather(ex, RS_D);
+      }
       stamp(6);
       if (!st_grid_sync(a, gen)) { give_up(4); return; }
       stamp(7);
@@ -767,11 +815,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
 
       // ================================================================ P6: h += W2 ffn
       stage_copy(a.ffn, hidden);
-      st_project<RS_H, NI_H, 1, MT>(dim, KC_H, xs, M, ring, full, rg, seq, part, a, tid, residual,
-                                         [&](int row, int m, float s, float, __half prev) {
-                                           a.h[(size_t)m * dim + row] = hadd1(prev, __float2half_rn(s));
-                                         },
-                                         refill);
+      {
+        const uint32_t ex = peer_base + (uint32_t)step * ex_per_step + 2u * (uint32_t)l + 1u;
+        st_project<RS_H, NI_H, 1, MT>(dim, KC_H, xs, M, ring, full, rg, seq, part, a, tid, residual,
+                                      [&](int row, int m, float s, float, __half prev) { rowpar_epi(ex, row, m, s, prev); }, refill);
+        rowpar_gather(ex, RS_H);
+      }
       stamp(10);
       if (!st_grid_sync(a, gen)) { give_up(4); return; }
       stamp(11);
@@ -785,7 +834,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
                                          [&](int row, int m, float s, float, __half) {
                                            const __half v = __float2half_rn(s);
                                            a.logits[(size_t)m * a.vocab + row] = v;
-                                           const unsigned long long k = argmax_key(v, (uint32_t)row);
+                                           const unsigned long long k = argmax_key(v, (uint32_t)(row + a.vocab_offset));
                                            best = k > best ? k : best;
                                          },
                                          refill);
@@ -795,11 +844,36 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
     stamp(12);
     if (!st_grid_sync(a, gen)) { give_up(4); return; }
     stamp(13);
-    // every CTA reads the pick (the next step's embedding row); CTA 0 publishes it
+    // every CTA reads the pick (the next step's embedding row); CTA 0 publishes it.  Under tensor parallelism every rank
+    // holds the best key of its share of the vocabulary: CTA 0 sends it to all ranks as a pair of entries, and every CTA
+    // of every rank takes the largest of the ranks' keys (largest value, lowest index among equals)
+    if (world > 1) {
+      const uint32_t ex = peer_base + (uint32_t)step * ex_per_step + 2u * (uint32_t)a.n_layers;
+      constexpr size_t KEY_AT = PEER_LL_VALUES / 2;  // entries [KEY_AT, KEY_AT + 2 M): beyond any [M][dim] sum
+      if (tid < M) {
+        if (bid == 0) {
+          const unsigned long long k = __ldcg(a.key + tid);
+          for (int p = 0; p < world; p++)
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %2};" ::"l"(peer_ll(a.peer.buf[p], (int)(ex & 1u), a.peer.rank) + KEY_AT + 2 * tid),
+                         "r"((uint32_t)(k & 0xFFFFFFFFull)), "r"(ex), "r"((uint32_t)(k >> 32)) : "memory");
+        }
+        unsigned long long best = 0ull;
+        bool ok = true;
+        for (int rk = 0; rk < world && ok; rk++) {
+          float lo = 0.f, hi = 0.f;
+          ok = peer_ll_load2(peer_ll(a.peer.buf[a.peer.rank], (int)(ex & 1u), rk) + KEY_AT + 2 * tid, ex, a.peer.timeout_ns, &lo, &hi);
+          const unsigned long long k = ((unsigned long long)__float_as_uint(hi) << 32) | (unsigned long long)__float_as_uint(lo);
+          best = k > best ? k : best;
+        }
+        if (!ok) atomicCAS(a.peer.err, 0, 1);
+        s_key[tid] = best;
+      }
+      __syncthreads();
+    }
 #pragma unroll
     for (int m = 0; m < MT; m++) {
       if (m < M) {
-        const unsigned long long k = __ldcg(a.key + m);
+        const unsigned long long k = world > 1 ? s_key[m] : __ldcg(a.key + m);
         tok[m] = (int32_t)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull));
         if (bid == 0 && tid == 0) a.next_tokens[(size_t)step * M + m] = tok[m];
         if (a.advance) posv[m] += 1;
@@ -814,9 +888,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
 }
 
 // ------------------------------------------------------------------------------------------------ host side
+struct jg_comm;
+int jg_peer_fill_args_n(jg_comm* comm, PeerArgs* a, uint32_t count);  // comm.cu: `count` consecutive exchange numbers
+
 struct jg_step {
   jg_dev* dev;
   jg_kvcache* kv;
+  jg_comm* comm;  // tensor parallelism: the rank's communicator (peer buffers open); null on one GPU
   StepArgs args;  // everything but the per-call buffers
   StepLayer* d_layers;
   int variant[2];  // index into the instantiation table: 1-row kernel, 2-row kernel
@@ -831,15 +909,20 @@ struct jg_step {
 typedef void (*StepKernel)(const StepArgs);
 struct StepVariant { int mt, hd, nrep, rs_d, rs_g, rs_h, ni_d, ni_h; StepKernel kern; };
 #define ST_VARIANT(MT, HD, NREP, RSD, RSG, RSH, NID, NIH) {MT, HD, NREP, RSD, RSG, RSH, NID, NIH, jg_step_kernel<MT, HD, NREP, RSD, RSG, RSH, NID, NIH>}
-// Per model shape: the 1-row kernel with 64 KB passes, the 1-row kernel with 32 KB passes, the 2-row kernel with 32 KB
-// passes (two activation rows leave room for fewer bytes of ring).
+// Per model shape: the 1-row and the 2-row kernel, each with 64 KB and with 32 KB passes.
 static const StepVariant g_step_variants[] = {
     // Llama-3.1-8B: dim 4096, hidden 14336
     ST_VARIANT(1, 128, 4, 8, 4, 2, 1, 4), ST_VARIANT(1, 128, 4, 4, 2, 1, 1, 4), ST_VARIANT(2, 128, 4, 4, 2, 1, 1, 4),
+    ST_VARIANT(2, 128, 4, 8, 4, 2, 1, 4),
+    // the same under tensor parallelism: a rank's share of the hidden width is 7168 (2 ranks), 3584 (4) or 1792 (8) columns
+    ST_VARIANT(1, 128, 4, 8, 4, 4, 1, 2), ST_VARIANT(2, 128, 4, 8, 4, 4, 1, 2),
+    ST_VARIANT(1, 128, 4, 8, 4, 8, 1, 1), ST_VARIANT(2, 128, 4, 8, 4, 8, 1, 1),
     // Llama-3.2-1B: dim 2048, hidden 8192
     ST_VARIANT(1, 64, 4, 8, 4, 4, 1, 2), ST_VARIANT(1, 64, 4, 8, 4, 2, 1, 2), ST_VARIANT(2, 64, 4, 8, 4, 2, 1, 2),
+    ST_VARIANT(2, 64, 4, 8, 4, 4, 1, 2),
     // Llama-3.2-3B: dim 3072, hidden 8192
     ST_VARIANT(1, 128, 3, 8, 4, 4, 1, 2), ST_VARIANT(1, 128, 3, 5, 2, 2, 1, 2), ST_VARIANT(2, 128, 3, 5, 2, 2, 1, 2),
+    ST_VARIANT(2, 128, 3, 8, 4, 4, 1, 2),
 };
 
 static int ni_for(int K) { return (K / 8 + ST_THREADS - 1) / ST_THREADS; }  // 16-byte chunks per thread and row
@@ -911,14 +994,17 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
     const size_t x_bytes = (size_t)mt * (d.dim > d.hidden_dim ? d.dim : d.hidden_dim) * sizeof(__half);
     const size_t head = ((att_bytes > x_bytes ? att_bytes : x_bytes) + 127) & ~(size_t)127;
     const long long room = (long long)dev->prop.sharedMemPerBlockOptin - 4096 - (long long)head;  // 4 KB: the kernel's static arrays
-    // 64 KB passes (half the barriers and epilogues per byte) where three of them fit, else 32 KB ones
-    int sb = (mt == 1 && room >= 3 * 65536) ? 65536 : 32768;
+    // 64 KB passes (half the barriers and epilogues per byte of 32 KB ones) where at least two of them fit: three beside
+    // one activation row, two beside two rows (8B shapes, two rows: 516 tok/s against 491 with five 32 KB passes)
+    int sb = room >= 2 * 65536 ? 65536 : 32768;
     if (ke && atoi(ke) == 32) sb = 32768;
     int ns = (int)(room / sb);
     if (ns > ST_MAX_SLOTS) ns = ST_MAX_SLOTS;
     const char* se = getenv("JG_STEP_SLOTS");
     if (se && atoi(se) >= 2 && atoi(se) < ns) ns = atoi(se);
-    const int vi = (k.n_heads * k.head_dim == d.dim && nrep <= 4) ? find_variant(mt, k.head_dim, nrep, d.dim, d.hidden_dim, sb) : -1;
+    const int q_dim = k.n_heads * k.head_dim;  // Wo's columns: all heads on one GPU, a rank's share under tensor parallelism
+    const bool heads_ok = d.comm != 0 ? (q_dim <= d.dim && q_dim % 8 == 0) : q_dim == d.dim;
+    const int vi = (heads_ok && nrep <= 4) ? find_variant(mt, k.head_dim, nrep, d.dim, d.hidden_dim, sb) : -1;
     if (ns < 2 || vi < 0) {
       jg_set_error("step_create: no single-kernel step for dim %d, hidden %d, head_dim %d, %d query heads per kv head (%d slots of %d bytes)",
                    d.dim, d.hidden_dim, k.head_dim, nrep, ns, sb);
@@ -938,7 +1024,7 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   }
   jg_step* s = new jg_step();
   memset(s, 0, sizeof(*s));
-  s->dev = dev; s->kv = kv; s->grid = grid; s->max_rows = max_rows; s->max_slices = 32;
+  s->dev = dev; s->kv = kv; s->grid = grid; s->comm = (jg_comm*)(uintptr_t)d.comm; s->max_rows = max_rows; s->max_slices = 32;
   if (getenv("JG_STEP_SLICES") != nullptr && atoi(getenv("JG_STEP_SLICES")) >= slices_min) s->max_slices = atoi(getenv("JG_STEP_SLICES"));
   s->args.slice_len = (getenv("JG_STEP_SLICE_LEN") != nullptr && atoi(getenv("JG_STEP_SLICE_LEN")) > 0) ? atoi(getenv("JG_STEP_SLICE_LEN")) : 48;
   for (int i = 0; i < 2; i++) {
@@ -949,6 +1035,7 @@ JG_API int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc,
   a.table = (const __half*)d.freqs_cis; a.table_rows = d.freqs_rows;
   a.k_pool = kv->k_pool; a.v_pool = kv->v_pool; a.block_table = kv->block_table; a.layer_elems = kv->layer_elems;
   a.n_layers = d.n_layers; a.dim = d.dim; a.hidden = d.hidden_dim; a.H = k.n_heads; a.G = k.n_kv_heads; a.vocab = d.vocab_size;
+  a.q_dim = k.n_heads * k.head_dim; a.embed_rows = d.embed_rows > 0 ? d.embed_rows : d.vocab_size; a.vocab_offset = d.vocab_offset;
   a.page = k.page_size; a.page_shift = ilog2(k.page_size); a.max_pages_per_seq = k.max_pages_per_seq; a.max_ctx = kv->max_ctx;
   a.chunk_cap = chunk_cap;
   a.eps = d.norm_eps; a.scale = 1.0f / sqrtf((float)k.head_dim); a.recip_dim = 1.0f / (float)d.dim;
@@ -1019,6 +1106,12 @@ JG_API int jg_step_run(jg_step* s, uint64_t tokens, uint64_t pos, uint64_t h, ui
   a.tokens = (int32_t*)tokens; a.pos = (int32_t*)pos; a.next_tokens = (int32_t*)next_tokens;
   a.h = (__half*)h; a.qkv = (__half*)qkv; a.attn = (__half*)attn; a.ffn = (__half*)ffn; a.logits = (__half*)logits;
   a.M = B; a.n_steps = n_steps; a.advance = advance ? 1 : 0;
+  if (s->comm != nullptr) {  // 2 exchanges per layer and one for the pick, per step
+    int rc = jg_peer_fill_args_n(s->comm, &a.peer, (uint32_t)n_steps * (uint32_t)(2 * a.n_layers + 1));
+    if (rc) return rc;
+    a.peer_ord0 = a.peer.ord;
+    JG_REQUIRE((size_t)B * a.dim <= PEER_LL_VALUES / 2, "step_run: %d rows of %d values exceed the exchange entries", B, a.dim);
+  }
   int sl = s->grid / (B * a.G);
   if (sl > s->max_slices) sl = s->max_slices;
   a.slices = sl;

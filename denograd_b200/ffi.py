@@ -34,8 +34,9 @@ class KvDesc(C.Structure):
 
 class StepDesc(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_layers", "dim", "hidden_dim", "n_heads", "vocab_size", "freqs_rows")] + \
-               [("norm_eps", C.c_float), ("reserved", C.c_int32)] + \
-               [(n, C.c_uint64) for n in ("layers", "tok_embeddings", "out_norm", "output", "freqs_cis")]
+               [("norm_eps", C.c_float), ("vocab_offset", C.c_int32)] + \
+               [(n, C.c_uint64) for n in ("layers", "tok_embeddings", "out_norm", "output", "freqs_cis", "comm")] + \
+               [("embed_rows", C.c_int64)]
 
 
 _vp, _i32, _i64, _u64, _f32, _f64, _sz = C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_float, C.c_double, C.c_size_t

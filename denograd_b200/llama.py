@@ -325,9 +325,12 @@ class _StepPlan:
             rows.append([layer.attention_norm.weight.ptr, a._wqkv.weight.ptr, a.wo.weight.ptr, layer.ffn_norm.weight.ptr,
                          f.w1.weight.ptr, f.w3.weight.ptr, f.w2.weight.ptr])
         table = np.ascontiguousarray(rows, dtype=np.uint64)
-        d = ffi.StepDesc(len(model.layers), model.dim, model.hidden_dim, model.n_heads, model.vocab_size,
-                         model.freqs_cis.shape[0], model.norm.eps, 0, table.ctypes.data, model.tok_embeddings.weight.ptr,
-                         model.norm.weight.ptr, model.output.weight.ptr, model.freqs_cis.ptr)
+        tp = model._tp  # tensor parallelism: the dimensions are this rank's shares, the exchanges happen inside the kernel
+        comm = tp.handle.value if tp is not None else 0
+        d = ffi.StepDesc(len(model.layers), model.dim, model.hidden_dim, model.n_heads, model.vocab_local,
+                         model.freqs_cis.shape[0], model.norm.eps, model.vocab_offset, table.ctypes.data,
+                         model.tok_embeddings.weight.ptr, model.norm.weight.ptr, model.output.weight.ptr, model.freqs_cis.ptr,
+                         comm or 0, model.vocab_size)
         self._dev = model.dev
         self.handle = C.c_void_p()
         ffi.call("jg_step_create", model.dev.handle, model._kv.handle, C.byref(d), C.byref(self.handle))
@@ -443,7 +446,8 @@ class Transformer:
         if self._step_plan is None:
             self._step_plan = False
             a0 = self.layers[0].attention
-            plain = (self.fused and self._tp is None and os.environ.get("JG_STEP_KERNEL", "1") != "0"
+            tp_ok = self._tp is None or (self._tp.peer_capacity > 0 and os.environ.get("JG_STEP_KERNEL_TP", "1") != "0")
+            plain = (self.fused and tp_ok and os.environ.get("JG_STEP_KERNEL", "1") != "0"
                      and type(a0.wo) is Linear and type(self.output) is Linear and type(self.tok_embeddings) is Embedding
                      and type(self.layers[0].feed_forward) is FeedForward)
             if plain:

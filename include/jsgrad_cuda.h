@@ -218,6 +218,11 @@ int jg_attn_chunk(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t out, uint
  * first weights of the next projection are already in flight when a CTA arrives at a barrier, so the HBM stream does
  * not drain at every kernel boundary.  fp16 weights, 1 or 2 rows, head_dim 64 / 128 with up to 4 query heads per kv
  * head, n_heads * head_dim == dim; other shapes: JG_ENOTSUP (the caller keeps the launch-per-op path).
+ * Tensor parallelism (`comm` set; every rank makes the same calls): the dimensions are the rank's shares as
+ * Llama3's shard plan cuts them (jsgrad/models/llama3.ts:239-249: wq|wk|wv and w1 / w3 by rows, wo and w2 by
+ * columns, `output` by vocabulary rows; n_heads and the cache's kv heads are the rank's); the partial sums of wo and
+ * w2 and the ranks' best (value, index) keys cross NVLink as flag-in-data entries inside the kernel, every wait
+ * bounded by the communicator's limit.
  * `layers` is a HOST pointer to n_layers x 7 device addresses: attention_norm.weight, wq|wk|wv (one allocation),
  * wo, ffn_norm.weight, w1, w3, w2.  The cache object supplies the K/V pools and the block table (identity row map). */
 typedef struct jg_step_desc {
@@ -228,12 +233,14 @@ typedef struct jg_step_desc {
   int32_t vocab_size;
   int32_t freqs_rows;      /* rows of the RoPE table */
   float norm_eps;
-  int32_t reserved;
+  int32_t vocab_offset;    /* tensor parallelism: vocabulary index of row 0 of `output` (0 on one GPU) */
   uint64_t layers;         /* host pointer, see above */
   uint64_t tok_embeddings; /* fp16 [vocab][dim] */
   uint64_t out_norm;       /* fp16 [dim] */
   uint64_t output;         /* fp16 [vocab][dim] */
   uint64_t freqs_cis;      /* fp16 [freqs_rows][head_dim/2][2] from jg_freqs_cis */
+  uint64_t comm;           /* tensor parallelism: the rank's jg_comm* with its peer buffers open; 0 on one GPU */
+  int64_t embed_rows;      /* rows of tok_embeddings (the whole vocabulary on every rank); 0 = vocab_size */
 } jg_step_desc;
 int jg_step_create(jg_dev* dev, jg_kvcache* kv, const jg_step_desc* desc, jg_step** out);
 int jg_step_destroy(jg_step* step);
