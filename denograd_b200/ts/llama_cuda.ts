@@ -214,11 +214,14 @@ class StepPlan {
   constructor(dev: CUDA, m: CudaTransformer) {
     this.table = new BigUint64Array(m.layers.length * 7)
     m.layers.forEach((l, i) => this.table.set([l.attention_norm.ptr, l.attention.wqkv.ptr, l.attention.wo.ptr, l.ffn_norm.ptr, l.feed_forward.w1.ptr, l.feed_forward.w3.ptr, l.feed_forward.w2.ptr], i * 7))
-    const desc = new DataView(new ArrayBuffer(72)) // jg_step_desc: 6 x int32, float, int32, 5 x uint64
+    const desc = new DataView(new ArrayBuffer(88)) // jg_step_desc: 6 x int32, float, int32, 6 x uint64, int64
     ;[m.layers.length, m.dim, m.hidden_dim, m.n_heads, m.vocab_size, m.max_context * 2].forEach((v, i) => desc.setInt32(4 * i, v, true))
     desc.setFloat32(24, m.norm.eps, true)
+    desc.setInt32(28, 0, true) // vocab_offset: one device holds the whole vocabulary
     const table_addr = BigInt(Deno.UnsafePointer.value(Deno.UnsafePointer.of(this.table)))
-    ;[table_addr, m.tok_embeddings.ptr, m.norm.ptr, m.output.ptr, m.freqs_cis.ptr].forEach((v, i) => desc.setBigUint64(32 + 8 * i, v, true))
+    // the last two: no communicator (one device), embedding rows = vocabulary
+    ;[table_addr, m.tok_embeddings.ptr, m.norm.ptr, m.output.ptr, m.freqs_cis.ptr, 0n].forEach((v, i) => desc.setBigUint64(32 + 8 * i, v, true))
+    desc.setBigInt64(80, BigInt(m.vocab_size), true)
     const out = new BigUint64Array(1)
     try {
       cu_h('jg_step_create', dev.handle, m.kv.handle as unknown as bigint, new Uint8Array(desc.buffer) as unknown as bigint, out as unknown as bigint)

@@ -82,3 +82,4 @@ def test_unsupported_shapes_keep_the_launch_per_op_path():
     prompt = synth.prompt_tokens(5, TINY["vocab_size"], batch=1, seed=3)
     greedy_with_logits(llm, prompt, 3)
     assert llm.model._single_kernel_step(1) is None
+

@@ -12,7 +12,7 @@ import pytest
 
 from denograd_b200 import ffi, synth
 from tests.golden.gen_golden import TINY
-from tests.util import ROOT, build_oracle, oracle_greedy
+from tests.util import ROOT, TP_STEP_ARCH, build_oracle, oracle_greedy
 
 pytestmark = pytest.mark.gpu
 
@@ -26,11 +26,14 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("peer,quant", [("1", "float16"), ("0", "float16"), ("1", "int8")])
-def test_two_rank_tensor_parallel_matches_the_checker(peer, quant):
+@pytest.mark.parametrize("peer,quant,arch", [("1", "float16", "tiny"), ("0", "float16", "tiny"), ("1", "int8", "tiny"),
+                                             ("1", "float16", "step")])
+def test_two_rank_tensor_parallel_matches_the_checker(peer, quant, arch):
+    """`step`: a shape whose decode step runs as the single persistent kernel, with the exchanges inside it."""
     batch, n_new, world = 2, 8, 2
+    P = TP_STEP_ARCH if arch == "step" else TINY
     with tempfile.TemporaryDirectory() as work:
-        env = dict(os.environ, NCCL_NVLS_ENABLE="0", JG_TP_PEER=peer, JG_PEER_TIMEOUT_MS="5000")
+        env = dict(os.environ, NCCL_NVLS_ENABLE="0", JG_TP_PEER=peer, JG_PEER_TIMEOUT_MS="5000", JG_TEST_ARCH=arch)
         logs = [open(os.path.join(work, f"rank{r}.log"), "w+") for r in range(world)]
         procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "tp_worker.py"), str(r), str(world), work,
                                    str(batch), str(n_new), quant], env=env, stdout=logs[r], stderr=subprocess.STDOUT)
@@ -46,10 +49,12 @@ def test_two_rank_tensor_parallel_matches_the_checker(peer, quant):
         res = [np.load(os.path.join(work, f"out_{r}.npz")) for r in range(world)]
         if peer == "1":  # the peer-memory path must really have been the one that ran
             assert all(open(os.path.join(work, f"peer_{r}.txt")).read() == "1" for r in range(world)), "peer memory not mapped"
-    m = build_oracle(TINY, max_context=64, max_batch=batch, int8=(quant == "int8"), tied=True)
-    prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
+        took_step = [open(os.path.join(work, f"step_{r}.txt")).read() == "1" for r in range(world)]
+        assert took_step == [arch == "step"] * world, took_step
+    m = build_oracle(P, max_context=64, max_batch=batch, int8=(quant == "int8"), tied=True)
+    prompt = synth.prompt_tokens(6, P["vocab_size"], batch=batch, seed=31)
     ref_ids, ref_logits, margins = oracle_greedy(m, prompt, n_new)
-    Vl = TINY["vocab_size"] // world
+    Vl = P["vocab_size"] // world
     for r in range(world):
         assert int(res[r]["offset"]) == r * Vl
         assert (res[r]["ids"] == res[0]["ids"]).all() and (res[r]["loop"] == res[0]["ids"]).all()

@@ -50,12 +50,18 @@ def main() -> None:
     if quant == "missing-peer":
         missing_peer(dev, tp, rank, work)
         return
-    llm = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
-    prompt = synth.prompt_tokens(6, TINY["vocab_size"], batch=batch, seed=31)
+    arch = TINY
+    if os.environ.get("JG_TEST_ARCH") == "step":  # a shape the single-kernel step takes under tensor parallelism
+        from tests.util import TP_STEP_ARCH
+        arch = TP_STEP_ARCH
+    llm = Llama3(size="1B", args=arch, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    prompt = synth.prompt_tokens(6, arch["vocab_size"], batch=batch, seed=31)
     ids = llm.generate(prompt, n_new)
+    with open(os.path.join(work, f"step_{rank}.txt"), "w") as f:
+        f.write("1" if llm.model._single_kernel_step(batch) is not None else "0")
     logits = llm.model.last_logits(batch)
     # the graph-replayed device loop must agree with the per-token API under sharding too
-    llm2 = Llama3(size="1B", args=TINY, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
+    llm2 = Llama3(size="1B", args=arch, quantize=quant, max_context=64, max_batch=batch, tied_output=True, temperature=0, device=f"CUDA:{rank}", tp=tp).load_synthetic()
     first = llm2._prefill(prompt).numpy()
     loop = llm2.model.decode_loop(first, llm2.start_pos, n_new - 1)
     np.savez(os.path.join(work, f"out_{rank}.npz"), ids=ids, logits=logits, offset=llm.model.vocab_offset,

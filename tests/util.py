@@ -83,3 +83,10 @@ def oracle_greedy(m: O.OracleModel, prompt: np.ndarray, n_new: int):
             logits, nxt = m.forward(nxt.reshape(B, 1), pos)
             pos += 1
     return ids, np.stack(all_logits), np.stack(margins)
+
+
+# A shape the single-kernel decode step is instantiated for when it is cut in two by tensor parallelism (per rank: 4
+# query heads of 64 on 1 kv head, 6656 hidden columns = four rows per 64 KB pass, as the 1B model's 8192) and whose
+# vocabulary shard (501 rows) does not divide by the number of CTAs.
+TP_STEP_ARCH = {"dim": 512, "n_heads": 8, "n_kv_heads": 2, "n_layers": 3, "norm_eps": 1e-5, "rope_theta": 500000,
+                "vocab_size": 1002, "hidden_dim": 13312}
