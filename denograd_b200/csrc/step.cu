@@ -413,13 +413,28 @@ __global__ void __launch_bounds__(ST_THREADS, 1) jg_step_kernel(const StepArgs a
       const int row = (bid + (rr / rs) * nb) * rs + rr % rs;
       if (row < dim) {
         const size_t o = (size_t)m * dim + row;
-        float sum = 0.f;
-        for (int rk = 0; rk < world && ok; rk++) {
-          float v = 0.f;
-          ok = peer_ll_load(peer_ll(a.peer.buf[a.peer.rank], (int)(ex & 1u), rk) + o, ex, a.peer.timeout_ns, &v);
-          sum = __fadd_rn(sum, v);
+        // the ranks' entries are requested together (one round trip to this GPU's memory for all of them); an entry
+        // that has not arrived yet is polled, bounded
+        uint32_t val[PEER_MAX_WORLD], tag[PEER_MAX_WORLD];
+        const __half h_old = __ldcg(a.h + o);
+#pragma unroll
+        for (int rk = 0; rk < PEER_MAX_WORLD; rk++) {
+          val[rk] = 0u;
+          tag[rk] = ex;
+          if (rk < world)
+            asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(val[rk]), "=r"(tag[rk])
+                         : "l"(peer_ll(a.peer.buf[a.peer.rank], (int)(ex & 1u), rk) + o) : "memory");
         }
-        a.h[o] = hadd1(__ldcg(a.h + o), __float2half_rn(sum));
+        float sum = 0.f;
+#pragma unroll
+        for (int rk = 0; rk < PEER_MAX_WORLD; rk++) {
+          if (rk < world) {
+            float v = __uint_as_float(val[rk]);
+            if (tag[rk] != ex && ok) ok = peer_ll_load(peer_ll(a.peer.buf[a.peer.rank], (int)(ex & 1u), rk) + o, ex, a.peer.timeout_ns, &v);
+            sum = __fadd_rn(sum, v);
+          }
+        }
+        a.h[o] = hadd1(h_old, __float2half_rn(sum));
       }
     }
     if (!ok) atomicCAS(a.peer.err, 0, 1);  // a rank never arrived: the launch's results are void, nobody is waited for
@@ -917,6 +932,10 @@ static const StepVariant g_step_variants[] = {
     // the same under tensor parallelism: a rank's share of the hidden width is 7168 (2 ranks), 3584 (4) or 1792 (8) columns
     ST_VARIANT(1, 128, 4, 8, 4, 4, 1, 2), ST_VARIANT(2, 128, 4, 8, 4, 4, 1, 2),
     ST_VARIANT(1, 128, 4, 8, 4, 8, 1, 1), ST_VARIANT(2, 128, 4, 8, 4, 8, 1, 1),
+    // ... with 32 KB passes (more passes per CTA when a rank's matrices are small)
+    ST_VARIANT(1, 128, 4, 4, 2, 2, 1, 2), ST_VARIANT(2, 128, 4, 4, 2, 2, 1, 2),
+    ST_VARIANT(1, 128, 4, 4, 2, 4, 1, 1), ST_VARIANT(2, 128, 4, 4, 2, 4, 1, 1),
+    ST_VARIANT(1, 128, 4, 4, 2, 8, 1, 1), ST_VARIANT(2, 128, 4, 4, 2, 8, 1, 1),
     // Llama-3.2-1B: dim 2048, hidden 8192
     ST_VARIANT(1, 64, 4, 8, 4, 4, 1, 2), ST_VARIANT(1, 64, 4, 8, 4, 2, 1, 2), ST_VARIANT(2, 64, 4, 8, 4, 2, 1, 2),
     ST_VARIANT(2, 64, 4, 8, 4, 4, 1, 2),
