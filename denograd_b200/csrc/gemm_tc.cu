@@ -15,6 +15,11 @@
 // (1,1,ks) share one output tile, each accumulating a slice of K; ranks > 0 then write their accumulators into rank 0's
 // (by then idle) pipeline buffers through distributed shared memory and rank 0 adds them in rank order before the
 // epilogue.  No cluster multicast is used anywhere: every CTA fetches its own tiles.
+// int8 weights (Int8Linear with many rows, jsgrad/models/llama3.ts:35): the weight tile arrives by TMA as int8 (8 KB
+// instead of 16), and the warps that will later run the epilogue — idle during the main loop — turn it into the fp16
+// tile the MMA reads: thread = one weight row of the tile, half(q) * scale rounded once per element, written in the
+// 128-byte swizzle pattern TMA would have produced (16-byte chunk c of row r lands at chunk c ^ (r % 8)), followed by a
+// proxy fence.  The weights cross HBM as int8 once per pass; no fp16 copy of a matrix is ever written.
 // Every mbarrier wait is bounded: a wait that does not complete sets an error word and the CTA winds down (cluster
 // barriers are still reached, tensor memory is released in every case); the host reports JG_ETIMEDOUT at the next
 // synchronisation.
@@ -43,6 +48,8 @@ struct TcArgs {
   int* err;  // device word: 0 = fine, otherwise the code of the first wait that gave up
   int M, N, K;
   int w_late;  // the weights were written by the preceding kernel: no load before the dependency wait
+  const __half* s0;  // int8 weights: per-output-row scales of the (first / second) matrix
+  const __half* s1;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -123,9 +130,10 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool W8 = false>
 struct TcCfg {
   static constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
+  static constexpr uint32_t RAW_BYTES = W8 ? TC_BM * TC_BK : 0;  // the int8 tile as it arrives (8 KB)
   static constexpr int NCOL = NW * TN;                 // accumulator columns
   // epilogue warps per tensor-memory quarter: wide tiles leave each of them 64 columns (measured at 512 rows: 12.1 ->
   // 11.8 ms per prefill against two warps), narrow ones are over before more warps would pay (batch 32: 6.92k tok/s
@@ -134,7 +142,8 @@ struct TcCfg {
   static constexpr int THREADS = tc_threads(EPW);
   static constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
   static constexpr uint32_t B_BYTES = TN * TC_BK * 2;
-  static constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
+  static constexpr uint32_t STAGE_BYTES = NW * (A_BYTES + RAW_BYTES) + B_BYTES;  // [A0 | A1 | B | raw0 | raw1]
+  static constexpr int CONV_WARPS = W8 ? 4 * NW : 0;  // epilogue warps that convert during the main loop
   static constexpr int STAGES_FIT = (225 * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr uint32_t TMEM_COLS = NCOL <= 32 ? 32 : (NCOL <= 64 ? 64 : (NCOL <= 128 ? 128 : (NCOL <= 256 ? 256 : 512)));
@@ -143,13 +152,32 @@ struct TcCfg {
   static constexpr int MAX_KS = 1 + (int)(((size_t)STAGES * STAGE_BYTES) / ((size_t)NCOL * TC_BM * 4));
 };
 
-template <int TN, int EPI>
-__global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
+// int8 x16 -> sixteen halves of half(q) * s (eight half2 registers in k order), each product rounded once
+__device__ __forceinline__ void tc_dequant16(const uint4& raw, __half2 s2, uint32_t (&out)[8]) {
+  const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+  const __half2 bias = __floats2half2_rn(1152.0f, 1152.0f);  // 1024 + 128
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const uint32_t v = words[i] ^ 0x80808080u;          // signed -> offset-binary
+    uint32_t lo = __byte_perm(v, 0x64646464u, 0x4140);  // bytes 0,1 -> halves 1024 + b
+    uint32_t hi = __byte_perm(v, 0x64646464u, 0x4342);  // bytes 2,3
+    const __half2 p = __hmul2_rn(__hsub2(*reinterpret_cast<__half2*>(&lo), bias), s2);
+    const __half2 q = __hmul2_rn(__hsub2(*reinterpret_cast<__half2*>(&hi), bias), s2);
+    out[2 * i] = *reinterpret_cast<const uint32_t*>(&p);
+    out[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&q);
+  }
+}
+
+template <int TN, int EPI, bool W8 = false>
+__global__ void __launch_bounds__(TcCfg<TN, EPI, W8>::THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
                                                              const __grid_constant__ CUtensorMap tm_w1,
                                                              const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
-  using Cfg = TcCfg<TN, EPI>;
+  using Cfg = TcCfg<TN, EPI, W8>;
   constexpr int NW = Cfg::NW, STAGES = Cfg::STAGES, NCOL = Cfg::NCOL;
   constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, TMEM_COLS = Cfg::TMEM_COLS;
+  constexpr uint32_t RAW_BYTES = Cfg::RAW_BYTES, B_BYTES = Cfg::B_BYTES, RAW_OFF = NW * A_BYTES + B_BYTES;
+  static_assert(!W8 || Cfg::CONV_WARPS <= 4 * Cfg::EPW, "the converting warps are epilogue warps");
+  __shared__ __align__(8) uint64_t raw_full[W8 ? STAGES : 1], a_full[W8 ? STAGES : 1];
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
@@ -163,6 +191,8 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    if (W8)
+      for (int s = 0; s < STAGES; s++) { mbar_init(&raw_full[s], 1); mbar_init(&a_full[s], Cfg::CONV_WARPS); }
     mbar_init(&acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -181,23 +211,32 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const 
     // ---- producer.  Weights do not depend on the preceding kernel: the first tiles are requested before the wait.
     const int pre = nk < STAGES ? nk : STAGES;
     if (a.w_late) pdl_wait();
-    for (int i = 0; i < pre; i++) {
-      unsigned char* st = tiles + (size_t)i * STAGE_BYTES;
-      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
-      tma_load_2d(st, &tm_w0, (kb0 + i) * TC_BK, feat0, &full_bar[i]);
-      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &full_bar[i]);
-    }
+    // fp16 weights land in the A tiles and complete full_bar together with the activations; int8 weights land in the
+    // raw tiles and complete raw_full (the converting warps then fill the A tiles and complete a_full)
+    auto load_w = [&](int i, int s) {
+      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+      if (W8) {
+        mbar_expect_tx(&raw_full[s], NW * RAW_BYTES);
+        tma_load_2d(st + RAW_OFF, &tm_w0, (kb0 + i) * TC_BK, feat0, &raw_full[s]);
+        if (NW == 2) tma_load_2d(st + RAW_OFF + RAW_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &raw_full[s]);
+        mbar_expect_tx(&full_bar[s], B_BYTES);
+      } else {
+        mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+        tma_load_2d(st, &tm_w0, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
+        if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
+      }
+    };
+    for (int i = 0; i < pre; i++) load_w(i, i);
     pdl_wait();  // X comes from the previous kernel
     for (int i = 0; i < pre; i++)
       tma_load_2d(tiles + (size_t)i * STAGE_BYTES + NW * A_BYTES, &tm_x, (kb0 + i) * TC_BK, tok0, &full_bar[i]);
     for (int i = pre; i < nk; i++) {
       const int s = i % STAGES;
+      // the MMAs of the stage's previous use are done: its A and B tiles are free, and so is its raw tile (converted
+      // before those MMAs could start)
       if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicCAS(a.err, 0, 1); break; }
-      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-      tma_load_2d(st, &tm_w0, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
-      if (NW == 2) tma_load_2d(st + A_BYTES, &tm_w1, (kb0 + i) * TC_BK, feat0, &full_bar[s]);
-      tma_load_2d(st + NW * A_BYTES, &tm_x, (kb0 + i) * TC_BK, tok0, &full_bar[s]);
+      load_w(i, s);
+      tma_load_2d(tiles + (size_t)s * STAGE_BYTES + NW * A_BYTES, &tm_x, (kb0 + i) * TC_BK, tok0, &full_bar[s]);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer: 4 x (128 x TN x 16) per stage and matrix, accumulating in tensor memory
@@ -209,6 +248,7 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const 
     for (int i = 0; i < nk; i++) {
       const int s = i % STAGES;
       if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 2); ok = false; break; }
+      if (W8 && !mbar_wait(&a_full[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 2); ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
       const uint64_t bdesc = umma_desc(st + NW * A_BYTES);
@@ -223,6 +263,30 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI>::THREADS) gemm_tc_kernel(const 
     }
     if (ok) umma_commit(&acc_bar);  // ... and when the whole accumulation is complete
   } else if (warp >= 2) {
+    if (W8 && warp - 2 < Cfg::CONV_WARPS) {
+      // ---- converter: this thread's weight row of every stage, int8 -> half(q) * scale -> swizzled fp16 tile
+      const int cw = warp - 2, w = cw >> 2, r = (cw & 3) * 32 + lane;
+      if (a.w_late) pdl_wait();
+      const __half2 sc = __half2half2((w == 0 ? a.s0 : a.s1)[min(feat0 + r, a.N - 1)]);
+      const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
+      for (int i = 0; i < nk; i++) {
+        const int s = i % STAGES;
+        if (!mbar_wait(&raw_full[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 1); break; }
+        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+        const uint4* src = reinterpret_cast<const uint4*>(st + RAW_OFF + w * RAW_BYTES + r * TC_BK);
+        unsigned char* dst = st + w * A_BYTES + row_off;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {  // 16 weights -> two 16-byte chunks (2j, 2j + 1) of the row
+          uint32_t d[8];
+          tc_dequant16(src[j], sc, d);
+          *reinterpret_cast<uint4*>(dst + (((2 * j) ^ (r & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
+          *reinterpret_cast<uint4*>(dst + (((2 * j + 1) ^ (r & 7)) << 4)) = make_uint4(d[4], d[5], d[6], d[7]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the MMA's reads
+        __syncwarp();
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&a_full[s])) : "memory");
+      }
+    }
     pdl_wait();  // the residual is read and Y written only after the previous kernel is done with them
     acc_ok = mbar_wait(&acc_bar, 0);
     if (!acc_ok && lane == 0) atomicCAS(a.err, 0, 3);
@@ -304,7 +368,9 @@ typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_
                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 static encode_tiled_fn g_encode = nullptr;
 
-static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what) {
+// `bytes` = element size: 2 for fp16 operands (128-byte swizzle, the layout the MMA descriptors name), 1 for int8
+// weight tiles, which land unswizzled (64-byte rows) for the converting warps
+static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what, int bytes = 2) {
   if (!g_encode) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -316,11 +382,12 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
     g_encode = (encode_tiled_fn)fn;
   }
   const cuuint64_t dims[2] = {cols, rows};           // innermost first
-  const cuuint64_t strides[1] = {cols * 2};          // bytes between rows
+  const cuuint64_t strides[1] = {cols * (cuuint64_t)bytes};  // bytes between rows
   const cuuint32_t box[2] = {(cuuint32_t)TC_BK, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+  CUresult r = g_encode(m, bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        bytes == 2 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     jg_set_error("tensor map for %s (%llu x %llu) rejected: CUresult %d", what, (unsigned long long)rows, (unsigned long long)cols, (int)r);
@@ -331,39 +398,39 @@ static int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t co
 
 // Encoded maps are kept per (base, rows, cols, box rows): a model's weights and workspaces keep their addresses, so a
 // step after the first finds all of its maps here instead of encoding three per launch.
-struct MapKey { const void* base; uint64_t rows, cols; uint32_t box_rows; };
+struct MapKey { const void* base; uint64_t rows, cols; uint32_t box_rows; int bytes; };
 struct MapSlot { MapKey k; CUtensorMap m; bool used; };
 constexpr int MAP_SLOTS = 1024;
 static MapSlot g_maps[MAP_SLOTS];
 
-static int cached_map(const CUtensorMap** out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what) {
-  uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull ^ (rows * 0xBF58476D1CE4E5B9ull) ^ (cols << 20) ^ box_rows;
+static int cached_map(const CUtensorMap** out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, const char* what, int bytes = 2) {
+  uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull ^ (rows * 0xBF58476D1CE4E5B9ull) ^ (cols << 20) ^ box_rows ^ ((uint64_t)bytes << 40);
   h ^= h >> 29;
   for (int probe = 0; probe < 8; probe++) {
     MapSlot& s = g_maps[(h + probe) % MAP_SLOTS];
-    if (s.used && s.k.base == base && s.k.rows == rows && s.k.cols == cols && s.k.box_rows == box_rows) { *out = &s.m; return JG_OK; }
+    if (s.used && s.k.base == base && s.k.rows == rows && s.k.cols == cols && s.k.box_rows == box_rows && s.k.bytes == bytes) { *out = &s.m; return JG_OK; }
     if (!s.used) {
-      int rc = make_map(&s.m, base, rows, cols, box_rows, what);
+      int rc = make_map(&s.m, base, rows, cols, box_rows, what, bytes);
       if (rc) return rc;
-      s.k = MapKey{base, rows, cols, box_rows};
+      s.k = MapKey{base, rows, cols, box_rows, bytes};
       s.used = true;
       *out = &s.m;
       return JG_OK;
     }
   }
   MapSlot& s = g_maps[h % MAP_SLOTS];  // neighbourhood full: replace
-  int rc = make_map(&s.m, base, rows, cols, box_rows, what);
+  int rc = make_map(&s.m, base, rows, cols, box_rows, what, bytes);
   if (rc) { s.used = false; return rc; }
-  s.k = MapKey{base, rows, cols, box_rows};
+  s.k = MapKey{base, rows, cols, box_rows, bytes};
   s.used = true;
   *out = &s.m;
   return JG_OK;
 }
 
-template <int TN, int EPI>
+template <int TN, int EPI, bool W8 = false>
 static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
-  using Cfg = TcCfg<TN, EPI>;
-  auto kern = gemm_tc_kernel<TN, EPI>;
+  using Cfg = TcCfg<TN, EPI, W8>;
+  auto kern = gemm_tc_kernel<TN, EPI, W8>;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   const int slot = dev->ordinal & 7;
   if (!attr_set[slot]) {
@@ -371,9 +438,9 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
     attr_set[slot] = true;
   }
   const CUtensorMap *pw0, *pw1, *px;
-  int rc = cached_map(&pw0, w0, a.N, a.K, TC_BM, "weights");
+  int rc = cached_map(&pw0, w0, a.N, a.K, TC_BM, "weights", W8 ? 1 : 2);
   if (rc) return rc;
-  rc = cached_map(&pw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
+  rc = cached_map(&pw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)", W8 ? 1 : 2);
   if (rc) return rc;
   rc = cached_map(&px, x, a.M, a.K, TN, "activations");
   if (rc) return rc;
@@ -415,6 +482,10 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
 
 template <int EPI>
 static int launch_tc_rows(jg_dev* dev, const void* x, const void* w0, const void* w1, const TcArgs& a) {
+  if (a.s0 != nullptr) {  // int8 weights: used from 65 rows on (fewer go to the mma.sync kernel)
+    if (a.M <= 128) return launch_tc<128, EPI, true>(dev, x, w0, w1, a);
+    return launch_tc<256, EPI, true>(dev, x, w0, w1, a);
+  }
   if (a.M <= 16) return launch_tc<16, EPI>(dev, x, w0, w1, a);
   if (a.M <= 32) return launch_tc<32, EPI>(dev, x, w0, w1, a);
   if (a.M <= 64) return launch_tc<64, EPI>(dev, x, w0, w1, a);
@@ -426,7 +497,9 @@ static int launch_tc_rows(jg_dev* dev, const void* x, const void* w0, const void
 bool jg_gemm_tc_fits(int N, int K) { return N % TC_BM == 0 && K % TC_BK == 0; }
 
 // Entry used by gemv.cu's public functions (fp16 weights, N % 128 == 0, K % 64 == 0).
-int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K) {
+// s0 / s1: per-row scales of int8 weights (w0 / w1 then hold int8), or null for fp16 weights.
+int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K,
+               const void* s0, const void* s1) {
   if (!jg_gemm_tc_fits(N, K)) {
     jg_set_error("projection: M=%d rows need N %% 128 == 0 and K %% 64 == 0 (N=%d, K=%d); split the rows into chunks of 64", M, N, K);
     return JG_ENOTSUP;
@@ -439,7 +512,8 @@ int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* 
   }
   TcArgs a = {};
   a.y = (__half*)y; a.y32 = (float*)y; a.residual = (const __half*)residual; a.err = dev->err_word; a.M = M; a.N = N; a.K = K;
-  a.w_late = jg_is_fresh(dev, w0) || jg_is_fresh(dev, w1);
+  a.w_late = jg_is_fresh(dev, w0) || jg_is_fresh(dev, w1) || jg_is_fresh(dev, s0) || jg_is_fresh(dev, s1);
+  a.s0 = (const __half*)s0; a.s1 = (const __half*)(s1 ? s1 : s0);
   switch (epi) {
     case TC_STORE: return launch_tc_rows<TC_STORE>(dev, x, w0, w1, a);
     case TC_RESIDUAL: return launch_tc_rows<TC_RESIDUAL>(dev, x, w0, w1, a);

@@ -487,7 +487,8 @@ int jg_matvec_w8(jg_dev* dev, int epi, const void* x, const void* norm_w, float 
 bool jg_matvec_w8_fits(const jg_dev* dev, int M, int K);
 
 // gemm_tc.cu: tcgen05 / TMA projection (fp16 weights, N % 128 == 0, K % 64 == 0), any number of rows
-int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K);
+int jg_gemm_tc(jg_dev* dev, int epi, const void* x, const void* w0, const void* w1, void* y, const void* residual, int M, int N, int K,
+               const void* s0, const void* s1);
 bool jg_gemm_tc_fits(int N, int K);
 
 // Fewest rows that go to the tcgen05 kernel when the shape allows it (JG_TC_MIN_M overrides; above 64 rows it is
@@ -509,6 +510,12 @@ static bool w8_mma() {
   return v != 0;
 }
 
+static bool w8_tc() {  // JG_W8_TC=0: int8 projections of more than 64 rows are refused (the caller dequantises to fp16 first)
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JG_W8_TC"); v = (e && atoi(e) == 0) ? 0 : 1; }
+  return v != 0;
+}
+
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (EPI == EPI_PEER || EPI == EPI_PUSH) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
@@ -520,7 +527,10 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
     return JG_ENOTSUP;
   }
   if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
-    return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K);
+    return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K, nullptr, nullptr);
+  // int8 weights and more rows than the mma.sync kernel takes: the tcgen05 kernel with the conversion inside it
+  if (W8 && !NORM && EPI != EPI_LOGITS && a.M > 64 && jg_gemm_tc_fits(a.N, a.K) && w8_tc())
+    return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K, a.s0, a.s1);
   // int8 weights, up to 8 rows: the kernel that keeps the rows in shared memory and streams the weights through the
   // tensor cores without a barrier in its k loop; it also takes the norm in its prologue
   if (W8 && a.M <= 8 && w8_mma() && jg_matvec_w8_fits(dev, a.M, a.K) && getenv("JG_W8_RESIDENT_X") == nullptr)

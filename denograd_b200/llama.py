@@ -446,7 +446,11 @@ class Transformer:
         if self._step_plan is None:
             self._step_plan = False
             a0 = self.layers[0].attention
-            tp_ok = self._tp is None or (self._tp.peer_capacity > 0 and os.environ.get("JG_STEP_KERNEL_TP", "1") != "0")
+            # tensor parallel: measured ahead of the launch-per-op step on 2 and 4 GPUs (506 against 443, 637 against 588
+            # tok/s on the 8B shapes), behind it on 8 (646 against 679), where the two exchanges per layer outweigh the
+            # rank's 8 us of weights; JG_STEP_KERNEL_TP=1 / 0 forces it on / off
+            want_tp = os.environ.get("JG_STEP_KERNEL_TP", "1" if (self._tp is None or self._tp.world <= 4) else "0") != "0"
+            tp_ok = self._tp is None or (self._tp.peer_capacity > 0 and want_tp)
             plain = (self.fused and tp_ok and os.environ.get("JG_STEP_KERNEL", "1") != "0"
                      and type(a0.wo) is Linear and type(self.output) is Linear and type(self.tok_embeddings) is Embedding
                      and type(self.layers[0].feed_forward) is FeedForward)
@@ -545,9 +549,10 @@ class Transformer:
 
     @staticmethod
     def _dequant_prefill() -> bool:
-        """int8 weights, more than 64 rows per chunk: each matrix is dequantised once per chunk into an fp16 scratch
-        (what the reference graph does for multi-row calls, jsgrad/models/llama3.ts:35) and goes through the tcgen05
-        projection; JG_W8_DEQUANT_PREFILL=0 keeps 64-row chunks on the mma.sync kernel instead."""
+        """int8 weights, more than 64 rows per chunk: the tcgen05 projection takes the int8 matrices and converts their
+        tiles in shared memory (JG_W8_TC=0: each matrix is dequantised once per chunk into an fp16 scratch first — what
+        the reference graph does for multi-row calls, jsgrad/models/llama3.ts:35); JG_W8_DEQUANT_PREFILL=0 keeps 64-row
+        chunks on the mma.sync kernel instead."""
         return os.environ.get("JG_W8_DEQUANT_PREFILL", "1") != "0"
 
     def _fp16_weights(self, *lins):
@@ -577,8 +582,11 @@ class Transformer:
         ws.seq.assign(np.tile(np.arange(B, dtype=np.int32), Sc))
         self.tok_embeddings.call(ws.tokens, out=ws.h)
         d = self.dim
-        # int8 weights and more rows than the mma.sync kernel takes: dequantised fp16 copies, made once per chunk
-        dq = R > 64 and self.output.scale_ptr != 0
+        # int8 weights and more rows than the mma.sync kernel takes: up to JG_W8_TC_ROWS rows the tcgen05 projection converts
+        # the int8 tiles itself (every 256-row tile of activations converts the weight tiles again); beyond, and with
+        # JG_W8_TC=0, it is given dequantised fp16 copies, made once per chunk
+        tc_rows = 0 if os.environ.get("JG_W8_TC", "1") == "0" else int(os.environ.get("JG_W8_TC_ROWS", "768"))
+        dq = R > 64 and self.output.scale_ptr != 0 and R > tc_rows
 
         def weights(*lins):
             return self._fp16_weights(*lins) if dq else [(l.weight.ptr, l.scale_ptr) for l in lins]
