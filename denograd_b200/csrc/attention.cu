@@ -791,7 +791,16 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   int cs = cluster;
   if (cs == 0) {
     cs = 8;
-    while (cs > 1 && (long long)B * G * cs > 2LL * dev->sm_count) cs >>= 1;
+    if (use_mma) {
+      // the tensor-core CTAs are light (4 warps) and the scores of a CTA's positions cost it shared memory, i.e. CTAs
+      // per SM: splitting the context keeps more warps and more K / V bytes in flight per SM.  Measured on the 8B shapes
+      // (8-layer slices, ms per step for 1 / 2 / 4 / 8 CTAs per pair): 32 rows over 4096 positions 2.46 / 2.54 / 2.14 /
+      // 2.24, over 1500 positions 1.65 / - / 1.53 / 1.58, over 512 positions 1.33 / 1.28 / 1.33 / 1.39; 8 rows over 4096
+      // positions - / 1.64 / 1.38 / 1.29.  Rule: up to 1024 CTAs, at least 256 positions of the cache's capacity each.
+      while (cs > 1 && ((long long)B * G * cs > 1024 || kv->max_ctx / cs < 256)) cs >>= 1;
+    } else {
+      while (cs > 1 && (long long)B * G * cs > 2LL * dev->sm_count) cs >>= 1;
+    }
     // ... but never more positions per CTA than its shared memory can hold scores for
     while (cs < 8 && (size_t)n_rep * cap_of(cs) * sizeof(float) + tile_bytes + 48 * 1024 > (size_t)dev->prop.sharedMemPerBlockOptin) cs <<= 1;
   }
