@@ -332,7 +332,7 @@ struct AttnFusedArgs {
   const int32_t* pos;
   const int32_t* seq;  // row -> sequence (block-table row); null = identity.  Several rows may belong to one sequence
   __half* out;
-  int table_rows, qkv_stride, H, G, page, page_shift, max_pages_per_seq, max_ctx, chunk_cap;
+  int table_rows, qkv_stride, H, G, page, page_shift, max_pages_per_seq, max_ctx, chunk_cap, stages;
   int n_seq;  // rows of the block table: a row whose seq[] entry lies outside [0, n_seq) is skipped (output untouched)
   int pre;  // 1: Q is already rotated and K/V are already in the cache (multi-position calls): attend only
   float scale;
@@ -782,9 +782,11 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   // Eight query heads per kv head (70B shapes) fill the MMA's eight columns and overwhelm the CUDA-core kernel's
   // registers: one row over 8200 positions takes 49 us against 95 us.
   const int use_mma = mma_env >= 0 ? mma_env : ((long long)B * G >= 16 || n_rep >= 8);
-  const size_t tile_bytes = use_mma ? (size_t)2 * AM_TK * (hd + 8) * sizeof(__half) : 0;
+  static int stages = 0;
+  if (!stages) { const char* e = getenv("JG_ATTN_STAGES"); stages = e ? atoi(e) : 2; if (stages < 2 || stages > 4) stages = 2; }
+  const size_t tile_bytes = use_mma ? (size_t)stages * AM_TK * (hd + 8) * sizeof(__half) : 0;
   // scores per CTA: rows of chunk_cap floats; the tensor-core variant pads the row so that heads fall on distinct banks
-  auto cap_of = [&](int c) { const int per = (kv->max_ctx + c - 1) / c; return use_mma ? (((per + 31) & ~31) + 8) : ((per + 3) & ~3); };
+  auto cap_of = [&](int c) { const int per = (kv->max_ctx + c - 1) / c; return use_mma ? (((per + AM_TK - 1) & ~(AM_TK - 1)) + 8) : ((per + 3) & ~3); };
   // CTAs per (row, kv head): as many as it takes to put about two CTAs on every SM, at most 8 — one row alone is
   // latency-bound and wants its context spread widely, many rows fill the machine by themselves and every extra
   // CTA only adds a cluster barrier to a short loop.
@@ -816,7 +818,7 @@ static int attn_fused_impl(jg_dev* dev, jg_kvcache* kv, int32_t layer, uint64_t 
   a.block_table = kv->block_table; a.pos = (const int32_t*)pos; a.out = (__half*)out;
   a.seq = (const int32_t*)seq; a.pre = pre; a.n_seq = kv->d.max_batch;
   a.qkv_stride = (H + 2 * G) * hd; a.H = H; a.G = G; a.page = kv->d.page_size; a.page_shift = ilog2(kv->d.page_size);
-  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap;
+  a.max_pages_per_seq = kv->d.max_pages_per_seq; a.max_ctx = kv->max_ctx; a.chunk_cap = chunk_cap; a.stages = stages;
   a.scale = (float)(1.0 / (double)(float)sqrt((double)hd));
 #define JG_ATT_CASE(HD_, NR_)                                                                   \
   if (hd == HD_ && n_rep == NR_)                                                                \

@@ -23,10 +23,6 @@ __device__ __forceinline__ void am_cp16(void* dst, const void* src, bool valid) 
   const int n = valid ? 16 : 0;  // 0 source bytes: zero fill
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ uint32_t am_pack(float lo, float hi) {
-  const __half2 h = __halves2half2(__float2half_rn(lo), __float2half_rn(hi));
-  return *reinterpret_cast<const uint32_t*>(&h);
-}
 // apply_rotary_emb on one (even, odd) pair: x = (a, b), t = (cos, sin) -> (a*cos - b*sin, a*sin + b*cos), each fp16 op
 // rounded once (jsgrad/models/llama.ts:17-32)
 __device__ __forceinline__ uint32_t am_rope2(uint32_t xraw, uint32_t traw) {
@@ -52,7 +48,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
   const int g = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int qr = lane >> 2, qc = (lane & 3) * 2;
-  __half* tiles = reinterpret_cast<__half*>(sc + (size_t)NREP * a.chunk_cap);  // [2][AM_TK][LD]
+  __half* tiles = reinterpret_cast<__half*>(sc + (size_t)NREP * a.chunk_cap);  // [a.stages][AM_TK][LD]
   pdl_launch();
   pdl_wait();
 
@@ -60,8 +56,10 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
   if ((unsigned)sq >= (unsigned)a.n_seq) return;  // no such block-table row: skipped by every CTA of the cluster alike
   const int T = min(max(a.pos[b] + 1, 1), a.max_ctx);
   const int p = T - 1;  // position of the new token
-  const int chunk = min((T + CS - 1) / CS, a.chunk_cap);
-  const int t0 = rank * chunk, t1 = min(T, t0 + chunk);
+  // positions per rank: a whole number of tiles, so that every tile starts on a multiple of AM_TK (the host sizes
+  // chunk_cap to CS * (chunk_cap - 8) >= max_ctx rounded likewise)
+  const int chunk = min(((T + CS - 1) / CS + AM_TK - 1) & ~(AM_TK - 1), a.chunk_cap - 8);
+  const int t0 = min(rank * chunk, T), t1 = min(T, t0 + chunk);
   const int n_local = max(t1 - t0, 0);
   const int n_tiles = (n_local + AM_TK - 1) / AM_TK;
   const int32_t* bt_row = a.block_table + (size_t)sq * a.max_pages_per_seq;
@@ -95,7 +93,23 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
   }
   __syncthreads();  // the new K / V rows are visible to this CTA's loads below
 
+  // A tile starts on a multiple of AM_TK, so with pages of AM_TK or more positions its rows lie back to back in one
+  // page: one block-table lookup per tile and constant strides between a thread's copies.  Smaller pages take the
+  // row-by-row path.
+  const bool one_page = a.page >= AM_TK;
   auto load_tile = [&](const __half* layer, int j, __half* dst) {
+    if (one_page) {
+      const int ts = t0 + j * AM_TK, n_valid = t1 - ts;
+      const __half* src = kv_row(layer, bt_row, ts, g, a.G, a.page, a.page_shift, HD) + tid * 8;
+      __half* d = dst + (tid / (HD / 8)) * LD + (tid % (HD / 8)) * 8;
+      constexpr int RPP = AM_THREADS / (HD / 8);  // rows per pass of the CTA
+#pragma unroll
+      for (int i = 0; i < AM_TK / RPP; i++) {
+        const bool ok = tid / (HD / 8) + i * RPP < n_valid;
+        am_cp16(d + i * RPP * LD, ok ? src + i * AM_THREADS * 8 : layer, ok);
+      }
+      return;
+    }
     for (int idx = tid; idx < AM_TK * (HD / 8); idx += AM_THREADS) {
       const int row = idx / (HD / 8), c = idx % (HD / 8);
       const int t = t0 + j * AM_TK + row;
@@ -103,29 +117,40 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
       const __half* src = ok ? kv_row(layer, bt_row, t, g, a.G, a.page, a.page_shift, HD) + c * 8 : layer;
       am_cp16(dst + row * LD + c * 8, src, ok);
     }
+  };
+  // The tiles travel through a ring of a.stages buffers, a.stages - 1 of them in flight while one is read.  Every
+  // iteration commits exactly one group (an empty one past the last tile), so "all but the newest a.stages - 1 groups
+  // have landed" always names the tile about to be read.
+  const int S = a.stages;
+  auto stage = [&](const __half* layer, int j) {
+    if (j < n_tiles) load_tile(layer, j, tiles + (j % S) * AM_TK * LD);
     asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  auto landed = [&]() {
+    if (S == 2) asm volatile("cp.async.wait_group 1;" ::: "memory");
+    else if (S == 3) asm volatile("cp.async.wait_group 2;" ::: "memory");
+    else asm volatile("cp.async.wait_group 3;" ::: "memory");
   };
 
   // ---- scores of this rank's positions -> shared memory; warp w takes positions [16w, 16w+16) of every tile
   float lmax0 = -INFINITY, lmax1 = -INFINITY;  // heads qc and qc+1
-  if (n_tiles > 0) load_tile(a.k_layer, 0, tiles);
+  for (int j = 0; j < S - 1; j++) stage(a.k_layer, j);
 #pragma unroll 1
   for (int j = 0; j < n_tiles; j++) {
-    if (j + 1 < n_tiles) {
-      load_tile(a.k_layer, j + 1, tiles + ((j + 1) & 1) * AM_TK * LD);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    stage(a.k_layer, j + S - 1);  // into the buffer that iteration j - 1 read
+    landed();
     __syncthreads();
-    const __half* Ks = tiles + (j & 1) * AM_TK * LD + (warp * 16) * LD;
+    // A fragments of the warp's 16 positions: four 8x8 blocks per k-step in one ldmatrix; lane l names row
+    // l%8 + 8*((l/8)%2) at dims 8*(l/16)
+    const uint32_t ks = (uint32_t)__cvta_generic_to_shared(
+        tiles + (j % S) * AM_TK * LD + (warp * 16 + (lane & 7) + (((lane >> 3) & 1) << 3)) * LD + ((lane >> 4) << 3));
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int k = 0; k < KS; k++) {
-      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(Ks + qr * LD + k * 16 + qc);
-      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(Ks + (qr + 8) * LD + k * 16 + qc);
-      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(Ks + qr * LD + k * 16 + 8 + qc);
-      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(Ks + (qr + 8) * LD + k * 16 + 8 + qc);
+      uint32_t a0, a1, a2, a3;
+      asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                   : "=r"(a0), "=r"(a1), "=r"(a2), "=r"(a3)
+                   : "r"(ks + k * 32));
       am_mma(c, a0, a1, a2, a3, qf[k][0], qf[k][1]);
     }
     const int ia = j * AM_TK + warp * 16 + qr, ib = ia + 8;  // local positions of this lane's two rows
@@ -137,10 +162,10 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
       if (ia < n_local) { const float s = __fmul_rn(c[1], a.scale); sc[(size_t)(qc + 1) * a.chunk_cap + ia] = s; lmax1 = fmaxf(lmax1, s); }
       if (ib < n_local) { const float s = __fmul_rn(c[3], a.scale); sc[(size_t)(qc + 1) * a.chunk_cap + ib] = s; lmax1 = fmaxf(lmax1, s); }
     }
-    __syncthreads();  // the buffer read here is refilled two iterations on
+    __syncthreads();  // the buffer read here is refilled by the next iteration
   }
-  // V tile 0 travels while the statistics are worked out
-  if (n_tiles > 0) load_tile(a.v_layer, 0, tiles);
+  // the first V tiles travel while the statistics are worked out
+  for (int j = 0; j < S - 1; j++) stage(a.v_layer, j);
 #pragma unroll
   for (int o = 4; o < 32; o <<= 1) {
     lmax0 = fmaxf(lmax0, __shfl_xor_sync(0xffffffffu, lmax0, o));
@@ -190,12 +215,22 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
     s_rL[tid] = __fdiv_rn(1.0f, L);
   }
   __syncthreads();
-  // ---- probabilities in place: p = half(exp2((s-M)/ln2) * 1/L), kept as the fp32 value of that fp16
-  for (int t = tid; t < n_local; t += AM_THREADS) {
+  // ---- probabilities p = half(exp2((s-M)/ln2) * 1/L), written as fp16 over the front half of each score row (zero
+  // up to the end of the last tile).  The halves of positions [128i, 128i+128) land on the floats of positions
+  // [64i, 64i+64), all of which every thread has read once the barrier of round i is passed.
+  const int n_pad = n_tiles * AM_TK;
+  for (int base = 0; base < n_pad; base += AM_THREADS) {
+    const int t = base + tid;
+    __half ph[NREP];
 #pragma unroll
     for (int r = 0; r < NREP; r++) {
-      const float e = jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_M[r]), log2e));
-      sc[(size_t)r * a.chunk_cap + t] = __half2float(__float2half_rn(__fmul_rn(e, s_rL[r])));
+      const float e = t < n_local ? jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_M[r]), log2e)) : 0.f;
+      ph[r] = __float2half_rn(__fmul_rn(e, s_rL[r]));
+    }
+    __syncthreads();
+    if (t < n_pad) {
+#pragma unroll
+      for (int r = 0; r < NREP; r++) reinterpret_cast<__half*>(sc + (size_t)r * a.chunk_cap)[t] = ph[r];
     }
   }
   __syncthreads();
@@ -204,26 +239,19 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
   float acc[MPW][4];
 #pragma unroll
   for (int m = 0; m < MPW; m++) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
-  const float* prow = sc + (size_t)min(qr, NREP - 1) * a.chunk_cap;  // B column n = lane/4 is head n (clamped)
+  // B column n = lane/4 is head n (clamped); the lane's elements of a k-step are positions qc, qc+1 and qc+8, qc+9
+  const __half* prow = reinterpret_cast<const __half*>(sc + (size_t)min(qr, NREP - 1) * a.chunk_cap) + qc;
 #pragma unroll 1
   for (int j = 0; j < n_tiles; j++) {
-    if (j + 1 < n_tiles) {
-      load_tile(a.v_layer, j + 1, tiles + ((j + 1) & 1) * AM_TK * LD);
-      asm volatile("cp.async.wait_group 1;" ::: "memory");
-    } else {
-      asm volatile("cp.async.wait_group 0;" ::: "memory");
-    }
+    stage(a.v_layer, j + S - 1);
+    landed();
     __syncthreads();
-    const __half* Vs = tiles + (j & 1) * AM_TK * LD;
+    const __half* Vs = tiles + (j % S) * AM_TK * LD;
     if (warp * MPW < MT) {
 #pragma unroll
       for (int kk = 0; kk < AM_TK / 16; kk++) {
-        const int i0 = j * AM_TK + kk * 16 + qc, i1 = i0 + 8;  // local positions of this lane's B elements
-        const float2 pa = (i0 + 1 < n_local) ? *reinterpret_cast<const float2*>(prow + i0)
-                                             : make_float2(i0 < n_local ? prow[i0] : 0.f, 0.f);
-        const float2 pb = (i1 + 1 < n_local) ? *reinterpret_cast<const float2*>(prow + i1)
-                                             : make_float2(i1 < n_local ? prow[i1] : 0.f, 0.f);
-        const uint32_t b0 = am_pack(pa.x, pa.y), b1 = am_pack(pb.x, pb.y);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(prow + j * AM_TK + kk * 16);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(prow + j * AM_TK + kk * 16 + 8);
 #pragma unroll
         for (int m = 0; m < MPW; m++) {
           const int mt = warp * MPW + m;

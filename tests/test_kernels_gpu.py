@@ -297,6 +297,39 @@ def test_rope_cache_attention(dev, hd, H, G, B, T, n_split):
     kv2.close()
 
 
+@pytest.mark.parametrize("page", [16, 32, 64])
+@pytest.mark.parametrize("hd,H,G,B,T", [(128, 32, 8, 2, 333), (64, 16, 8, 4, 70), (128, 8, 8, 3, 1)])
+def test_fused_attention_page_sizes(dev, hd, H, G, B, T, page):
+    """The one-launch decode attention over pages smaller than and equal to its staged tile of 64 positions (16 or more
+    (row, kv head) pairs: the tensor-core variant), pages scattered over the pool."""
+    rng = np.random.default_rng(hd + H + T + page)
+    max_ctx = 512
+    kv = KVCache(dev, 1, H, G, hd, max_ctx, B, page_size=page)
+    table = rng.permutation(kv.n_pages).astype(np.int32).reshape(B, kv.max_pages_per_seq)
+    kv.set_block_table(table)
+    freqs = precompute_freqs_cis(hd, 2 * max_ctx, 500000.0, dev)
+    ftab = freqs.numpy()
+    stride = (H + 2 * G) * hd
+    qkv_all = (rng.standard_normal((T, B, stride)) * 0.7).astype(np.float16)
+    k_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    v_ref = np.zeros((B, max_ctx, G, hd), np.float16)
+    qkv = Tensor.empty((B, stride), "float16", dev)
+    pos = Tensor.zeros((B,), "int32", dev)
+    for t in range(T):
+        qkv.assign(qkv_all[t])
+        pos.assign(np.full((B,), t, np.int32))
+        if t < T - 1:
+            dev.call("jg_rope_kvwrite", kv.handle, 0, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, B, H)
+        k_ref[:, t] = O.rope(qkv_all[t][:, H * hd:(H + G) * hd].reshape(B, G, hd), ftab, [t] * B)
+        v_ref[:, t] = qkv_all[t][:, (H + G) * hd:].reshape(B, G, hd)
+    q_rot = O.rope(qkv_all[T - 1][:, :H * hd].reshape(B, H, hd), ftab, [T - 1] * B)
+    out = Tensor.empty((B, H * hd), "float16", dev)
+    dev.call("jg_attn_decode_fused", kv.handle, 0, out.ptr, qkv.ptr, freqs.ptr, freqs.shape[0], pos.ptr, B, H)
+    ref = O.attention(q_rot.reshape(B, 1, H, hd), k_ref, v_ref, T - 1).reshape(B, H * hd)
+    assert_reduction_close(out.numpy(), ref, max_ulp=2, max_frac=0.10, what=f"fused attention page {page} hd{hd} B{B} T{T}")
+    kv.close()
+
+
 @pytest.mark.parametrize("hd,H,G", [(64, 32, 8), (128, 24, 8), (128, 8, 8), (64, 4, 2), (128, 16, 2)])
 @pytest.mark.parametrize("B,start,Sc", [(1, 0, 16), (1, 0, 200), (2, 37, 75), (3, 130, 9), (1, 500, 140)])
 def test_chunk_attention_on_tensor_cores(dev, hd, H, G, B, start, Sc):
