@@ -103,6 +103,14 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
       const __half* src = kv_row(layer, bt_row, ts, g, a.G, a.page, a.page_shift, HD) + tid * 8;
       __half* d = dst + (tid / (HD / 8)) * LD + (tid % (HD / 8)) * 8;
       constexpr int RPP = AM_THREADS / (HD / 8);  // rows per pass of the CTA
+      if (n_valid >= AM_TK) {  // a whole tile (all but a rank's last): no per-row tests
+        const uint32_t ds = (uint32_t)__cvta_generic_to_shared(d);
+#pragma unroll
+        for (int i = 0; i < AM_TK / RPP; i++)
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(ds + i * RPP * LD * 2), "l"(src + i * AM_THREADS * 8)
+                       : "memory");
+        return;
+      }
 #pragma unroll
       for (int i = 0; i < AM_TK / RPP; i++) {
         const bool ok = tid / (HD / 8) + i * RPP < n_valid;
@@ -134,6 +142,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
 
   // ---- scores of this rank's positions -> shared memory; warp w takes positions [16w, 16w+16) of every tile
   float lmax0 = -INFINITY, lmax1 = -INFINITY;  // heads qc and qc+1
+  float* const srow = sc + min(qc, NREP - 1) * a.chunk_cap + warp * 16 + qr;  // head qc, this lane's first row of tile 0
   for (int j = 0; j < S - 1; j++) stage(a.k_layer, j);
 #pragma unroll 1
   for (int j = 0; j < n_tiles; j++) {
@@ -154,6 +163,19 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
       am_mma(c, a0, a1, a2, a3, qf[k][0], qf[k][1]);
     }
     const int ia = j * AM_TK + warp * 16 + qr, ib = ia + 8;  // local positions of this lane's two rows
+    if ((j + 1) * AM_TK <= n_local) {  // a whole tile
+      float* s0 = srow + j * AM_TK;
+      if (qc < NREP) {
+        const float x = __fmul_rn(c[0], a.scale), y = __fmul_rn(c[2], a.scale);
+        s0[0] = x; s0[8] = y; lmax0 = fmaxf(lmax0, fmaxf(x, y));
+      }
+      if (qc + 1 < NREP) {
+        const float x = __fmul_rn(c[1], a.scale), y = __fmul_rn(c[3], a.scale);
+        s0[a.chunk_cap] = x; s0[a.chunk_cap + 8] = y; lmax1 = fmaxf(lmax1, fmaxf(x, y));
+      }
+      __syncthreads();
+      continue;
+    }
     if (qc < NREP) {
       if (ia < n_local) { const float s = __fmul_rn(c[0], a.scale); sc[(size_t)qc * a.chunk_cap + ia] = s; lmax0 = fmaxf(lmax0, s); }
       if (ib < n_local) { const float s = __fmul_rn(c[2], a.scale); sc[(size_t)qc * a.chunk_cap + ib] = s; lmax0 = fmaxf(lmax0, s); }
@@ -178,22 +200,31 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
     for (int w = 1; w < AM_WARPS; w++) m = fmaxf(m, red[w][tid]);
     s_m[tid] = m;
   }
+  cluster.sync();  // every rank's max is published (a rank without positions publishes -inf)
+  if (tid < NREP) {
+    float M = -INFINITY;
+    for (int rk = 0; rk < CS; rk++) M = fmaxf(M, *cluster.map_shared_rank(&s_m[tid], rk));
+    s_M[tid] = M;
+  }
   __syncthreads();
-  // ---- sum of exponentials relative to this rank's own max (combined across ranks below)
+  // ---- e = exp2((s - M)/ln 2) against the global max, kept in place of the score, and this rank's sum of them
   const float log2e = 1.4426950408889634f;
   float lsum[NREP];
 #pragma unroll
   for (int r = 0; r < NREP; r++) lsum[r] = 0.f;
   for (int t = tid; t < n_local; t += AM_THREADS) {
 #pragma unroll
-    for (int r = 0; r < NREP; r++)
-      lsum[r] = __fadd_rn(lsum[r], jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_m[r]), log2e)));
+    for (int r = 0; r < NREP; r++) {
+      float* sp = sc + r * a.chunk_cap + t;
+      const float e = jg_xexp2_f32(__fmul_rn(__fsub_rn(*sp, s_M[r]), log2e));
+      *sp = e;
+      lsum[r] = __fadd_rn(lsum[r], e);
+    }
   }
-  __syncthreads();  // `red` is reused
 #pragma unroll
   for (int r = 0; r < NREP; r++) {
     const float v = warp_sum(lsum[r]);
-    if (lane == 0) red[warp][r] = v;
+    if (lane == 0) red[warp][r] = v;  // `red` was last read before the cluster barrier above
   }
   __syncthreads();
   if (tid < NREP) {
@@ -202,20 +233,14 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
     s_l[tid] = v;
   }
   cluster.sync();
-  // ---- global max M and normaliser L = sum_j l_j * exp2((m_j - M)/ln2) over the ranks, in rank order
+  // ---- normaliser L = the ranks' sums added in rank order
   if (tid < NREP) {
-    float M = -INFINITY;
-    for (int rk = 0; rk < CS; rk++) M = fmaxf(M, *cluster.map_shared_rank(&s_m[tid], rk));
     float L = 0.f;
-    for (int rk = 0; rk < CS; rk++) {
-      const float mj = *cluster.map_shared_rank(&s_m[tid], rk), lj = *cluster.map_shared_rank(&s_l[tid], rk);
-      L = __fadd_rn(L, __fmul_rn(lj, jg_xexp2_f32(__fmul_rn(__fsub_rn(mj, M), log2e))));
-    }
-    s_M[tid] = M;
+    for (int rk = 0; rk < CS; rk++) L = __fadd_rn(L, *cluster.map_shared_rank(&s_l[tid], rk));
     s_rL[tid] = __fdiv_rn(1.0f, L);
   }
   __syncthreads();
-  // ---- probabilities p = half(exp2((s-M)/ln2) * 1/L), written as fp16 over the front half of each score row (zero
+  // ---- probabilities p = half(e * 1/L), written as fp16 over the front half of each score row (zero
   // up to the end of the last tile).  The halves of positions [128i, 128i+128) land on the floats of positions
   // [64i, 64i+64), all of which every thread has read once the barrier of round i is passed.
   const int n_pad = n_tiles * AM_TK;
@@ -224,7 +249,7 @@ __global__ void __launch_bounds__(AM_THREADS) attn_decode_mma_kernel(const AttnF
     __half ph[NREP];
 #pragma unroll
     for (int r = 0; r < NREP; r++) {
-      const float e = t < n_local ? jg_xexp2_f32(__fmul_rn(__fsub_rn(sc[(size_t)r * a.chunk_cap + t], s_M[r]), log2e)) : 0.f;
+      const float e = t < n_local ? sc[r * a.chunk_cap + t] : 0.f;
       ph[r] = __float2half_rn(__fmul_rn(e, s_rL[r]));
     }
     __syncthreads();
