@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(OUT_DIR, "libjsgrad_cuda.so")
-SOURCES = ["device.cu", "elementwise.cu", "gemv.cu", "matvec_w8.cu", "gemm_small.cu", "gemm_tc.cu", "attention.cu", "attention_chunk.cu", "comm.cu", "sample.cu", "step.cu"]
+SOURCES = ["device.cu", "elementwise.cu", "gemv.cu", "matvec_w8.cu", "gemm_small.cu", "gemm_tc.cu", "attention.cu", "attention_chunk.cu", "comm.cu", "sample.cu", "step.cu", "program.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr"]
 
@@ -53,7 +53,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     if force or procs or _stale(LIB, objs):
-        cmd = [nvcc(), *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC"]
+        cmd = [nvcc(), *ARCH, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fPIC", "-ldl"]
         subprocess.run(cmd, check=True)
     return LIB
 

@@ -8,7 +8,11 @@ Same roles and names as the reference so that the model code above it reads like
   * ``Buffer``         — jsgrad/device.ts:66-172 (allocate / view / copyin / copyout);
   * ``Tensor``         — only the slice of jsgrad/tensor.ts the Llama path touches: a realized fp16/int8/int32 buffer
                           with a shape.  There is no lazy graph here: every op is one of the library's kernels.
-  * ``CUDAGraph``      — the GraphRunner a TinyJit batch becomes (jsgrad/engine/jit.ts:71-141).
+  * ``CUDAGraph``      — the GraphRunner a TinyJit batch becomes (jsgrad/engine/jit.ts:71-141);
+  * ``CUDACompiler`` / ``CUDAProgram`` — Compiler / Program (jsgrad/runtime/allocator.ts:98-139, instance
+                          jsgrad/runtime/ops_clang.ts:7-54) for CUDA C source such as the reference's CUDARenderer
+                          emits (jsgrad/renderer/cstyle.ts:348-419): NVRTC to a cubin, loaded and launched on the
+                          device's stream.  The way out for an AST without a hand-written kernel.
 All device work goes through the C ABI in ``ffi`` (no torch, no CPU fallback).
 """
 from __future__ import annotations
@@ -302,6 +306,80 @@ class Tensor:
         out = Tensor.empty(self.shape, self.dtype, dst)
         dst.allocator._transfer(out.ptr, self.ptr, self.nbytes, self.dev, dst)
         return out
+
+
+class CompileError(RuntimeError):
+    """jsgrad/runtime/allocator.ts:121."""
+
+
+class CUDACompiler:
+    """Compiler (jsgrad/runtime/allocator.ts:123-139): ``compile(src) -> bytes`` (a cubin) with a cache keyed by the
+    source, as ``compile_cached`` keeps one on disk.  Needs no device."""
+
+    def __init__(self, arch: str = "sm_100a"):
+        self.arch = arch
+        self._cache: dict[str, bytes] = {}
+
+    def compile(self, src: str) -> bytes:
+        ffi.load()
+        image, size = C.c_void_p(), C.c_uint64(0)
+        try:
+            ffi.call("jg_cuda_compile", src.encode(), self.arch.encode(), C.byref(image), C.byref(size))
+        except ffi.JgError as e:
+            if e.status == ffi.JG_EINVAL:
+                raise CompileError(str(e)) from None
+            raise
+        try:
+            return C.string_at(image, size.value)
+        finally:
+            ffi.call("jg_cuda_image_free", image)
+
+    def compile_cached(self, src: str) -> bytes:
+        lib = self._cache.get(src)
+        if lib is None:
+            lib = self._cache[src] = self.compile(src)
+        return lib
+
+
+class CUDAProgram:
+    """Program (jsgrad/runtime/allocator.ts:99-107; ops_clang.ts:30-54): ``CUDAProgram(dev, name, lib)`` loads the
+    kernel ``name`` of the cubin ``lib``; calling it launches ``global_size`` blocks of ``local_size`` threads with
+    the buffers as device pointers followed by ``vals`` as 32-bit ints.  ``wait=True`` returns the elapsed device
+    time in seconds."""
+
+    def __init__(self, dev: CUDA, name: str, lib: bytes):
+        if not lib:
+            raise ValueError("Lib is empty")  # ops_clang.ts:34
+        if not name:
+            raise ValueError("Name can't be undefined")  # ops_clang.ts:35
+        self.dev, self.name, self.lib = dev, name, lib
+        self.handle: C.c_void_p | None = None
+        h = C.c_void_p()
+        ffi.call("jg_program_load", dev.handle, name.encode(), lib, len(lib), C.byref(h))
+        self.handle = h
+
+    def __call__(self, *bufs, global_size: Sequence[int] | None = None, local_size: Sequence[int] | None = None,
+                 vals: Sequence[int] = (), wait: bool = False) -> float | None:
+        ptrs = [b if isinstance(b, int) else b.ptr for b in bufs]
+        barr = (C.c_uint64 * max(len(ptrs), 1))(*ptrs)
+        varr = (C.c_int32 * max(len(vals), 1))(*[int(v) for v in vals])
+        three = lambda v: None if v is None else (C.c_uint32 * 3)(*(list(v) + [1, 1, 1])[:3])
+        if wait:
+            self.dev.timer_start()
+        ffi.call("jg_program_call", self.handle, barr, len(ptrs), varr, len(vals), three(global_size), three(local_size))
+        return self.dev.timer_stop() if wait else None
+
+    def close(self) -> None:
+        if self.handle is not None:
+            ffi.call("jg_program_destroy", self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            if self.dev.handle is not None:
+                self.close()
+        except Exception:
+            pass
 
 
 class CUDAGraph:

@@ -63,6 +63,11 @@ SIGNATURES: dict[str, list] = {
     "jg_copyout_async": [_vp, _vp, _u64, _sz],
     "jg_timer_start": [_vp],
     "jg_timer_stop": [_vp, _P(_f64)],
+    "jg_cuda_compile": [C.c_char_p, C.c_char_p, _P(_vp), _P(_u64)],
+    "jg_cuda_image_free": [_vp],
+    "jg_program_load": [_vp, C.c_char_p, _vp, _u64, _P(_vp)],
+    "jg_program_call": [_vp, _vp, _i32, _vp, _i32, _vp, _vp],
+    "jg_program_destroy": [_vp],
     "jg_graph_begin": [_vp],
     "jg_graph_end": [_vp, _P(_vp)],
     "jg_graph_launch": [_vp, _vp],

@@ -417,7 +417,8 @@ class Transformer:
         else:
             self.output = Linear(dim, vocab_size, False, device=dev) if embedding is Embedding else linear(dim, vocab_size, False, device=dev)
         self.freqs_cis = precompute_freqs_cis(self.head_dim, self.max_context * 2, rope_theta, device=dev)
-        self._kv = KVCache(dev, n_layers, n_heads, self.n_kv_heads, self.head_dim, max_context, max_batch, page_size, n_split)
+        self._kv_args = (n_layers, n_heads, self.n_kv_heads, self.head_dim, max_context, max_batch, page_size, n_split)
+        self._kv = KVCache(dev, *self._kv_args)
         for i, layer in enumerate(self.layers):
             layer.attention._kv, layer.attention._layer = self._kv, i
         self._ws: dict[int, _Workspace] = {}
@@ -425,6 +426,19 @@ class Transformer:
         self._forward_jit: dict[int, TinyJit] = {}
         self._loop_graph: dict[int, CUDAGraph] = {}
         self._step_plan = None  # None: not tried yet, False: this model keeps the launch-per-op step
+
+    def new_cache(self) -> None:
+        """An empty (all-zero) KV cache in place of the current one, as a newly built model has (the lazily created
+        Attention.cache_kv of jsgrad/models/llama.ts:78-90).  Everything that holds the old cache's addresses goes
+        with it: the captured decode graphs and the single-kernel step plan are rebuilt on their next use."""
+        self._forward_jit.clear()
+        self._loop_graph.clear()
+        self._step_plan = None
+        self.dev.synchronize()
+        old, self._kv = self._kv, KVCache(self.dev, *self._kv_args)
+        for layer in self.layers:
+            layer.attention._kv = self._kv
+        old.close()
 
     # ------------------------------------------------------------------------------------------ internals
     def _workspace(self, B: int, rows: bool = False) -> _Workspace:

@@ -14,7 +14,7 @@ import { Allocator, type BufferSpec, Compiled, Compiler, Program, type ProgramCa
 import type { MemoryView } from '../helpers/memoryview.ts'
 import { env } from '../env/index.ts'
 import { vars } from '../helpers/helpers.ts'
-import { Renderer } from '../renderer/index.ts'
+import { CUDARenderer } from '../renderer/cstyle.ts'
 import type { Buffer } from '../device.ts'
 import { type ExecItem } from '../engine/realize.ts'
 import { GraphRunner } from '../engine/jit.ts'
@@ -45,6 +45,11 @@ export const SYMBOLS = {
   jg_copyout_async: fn([ptr, ptr, u64, usize]),
   jg_timer_start: fn([ptr]),
   jg_timer_stop: fn([ptr, buf], true),
+  jg_cuda_compile: fn([buf, buf, buf, buf]),
+  jg_cuda_image_free: fn([ptr]),
+  jg_program_load: fn([ptr, buf, buf, u64, buf]),
+  jg_program_call: fn([ptr, buf, i32, buf, i32, buf, buf]),
+  jg_program_destroy: fn([ptr]),
   jg_graph_begin: fn([ptr]),
   jg_graph_end: fn([ptr, buf]),
   jg_graph_launch: fn([ptr, ptr]),
@@ -143,23 +148,64 @@ export class CUDAAllocator extends Allocator<bigint> {
     check(lib!.symbols.jg_transfer(dest_dev.handle, dest, src_dev.handle, src, BigInt(sz)))
 }
 
-/** A kernel of the library addressed by name.  `lib` bytes are a UTF-8 descriptor `{entry, order}`: which entry point,
- *  and how its arguments interleave buffer slots (numbers), symbolic variables from args.vals ('v0', 'v1', ...) and
- *  literals.  Nothing is compiled at run time.  Program contract: allocator.ts:98-107.  The class is created per
- *  device (`CUDAProgram.bind(dev)`), because `Runtime.init(name, lib)` carries no device (engine/realize.ts:52-54). */
+const is_descriptor = (b: Uint8Array | string) => (typeof b === 'string' ? b.charCodeAt(0) : b[0]) === 0x7b // '{'
+const cstr = (s: string) => new TextEncoder().encode(s + '\0')
+
+/** Compiler (allocator.ts:123-139).  Two kinds of "source" reach it: the kernel descriptors the layers of
+ *  llama_cuda.ts write (JSON, passed through as bytes — nothing to compile), and CUDA C from the reference's own
+ *  CUDARenderer (renderer/cstyle.ts:348-419) for an AST without a hand-written kernel, which NVRTC turns into a cubin
+ *  (jg_cuda_compile; a source that does not compile throws with the compiler's log, like ops_clang.ts:21). */
+export class CUDACompiler extends Compiler {
+  constructor(public arch = 'sm_100a') {
+    super(`compile_cuda_${arch}`)
+  }
+  override compile = (src: string): Uint8Array => {
+    if (is_descriptor(src)) return new TextEncoder().encode(src)
+    const image = out64(), size = out64()
+    check(lib!.symbols.jg_cuda_compile(cstr(src), cstr(this.arch), image, size))
+    const p = Deno.UnsafePointer.create(image[0])
+    try {
+      return new Uint8Array(Deno.UnsafePointerView.getArrayBuffer(p!, Number(size[0]))).slice()
+    } finally {
+      check(lib!.symbols.jg_cuda_image_free(p))
+    }
+  }
+}
+
+/** Program contract: allocator.ts:98-107.  `lib` bytes are either a UTF-8 descriptor `{entry, order}` — a kernel of the
+ *  library addressed by name: which entry point, and how its arguments interleave buffer slots (numbers), symbolic
+ *  variables from args.vals ('v0', 'v1', ...) and literals — or a cubin from CUDACompiler, loaded once
+ *  (jg_program_load) and launched over args.global_size x args.local_size with the buffers as pointers and
+ *  args.vals as 32-bit ints (jg_program_call; argument order of ops_clang.ts:44-52).  The class is created per device
+ *  (`CUDAProgram.bind(dev)`), because `Runtime.init(name, lib)` carries no device (engine/realize.ts:52-54). */
 export class CUDAProgram extends Program {
   static bind = (dev: CUDA): typeof Program =>
     class extends CUDAProgram {
       static override init = (name: string, lib: Uint8Array) => new this(name, lib, dev)
     } as unknown as typeof Program
+  program: Deno.PointerValue = null
   constructor(name: string, lib: Uint8Array, public dev: CUDA) {
     super(name, lib)
+    if (!lib?.length) throw new Error('Lib is empty')
+    if (!name) throw new Error("Name can't be undefined")
+    if (!is_descriptor(lib)) {
+      const o = out64()
+      check(lib!.symbols.jg_program_load(dev.handle, cstr(name), lib, BigInt(lib.length), o))
+      this.program = Deno.UnsafePointer.create(o[0])
+    }
   }
   override call = async (bufs: bigint[], args: ProgramCallArgs, wait = false) => {
-    const d = JSON.parse(new TextDecoder().decode(this.lib)) as { entry: keyof typeof SYMBOLS; order: (number | string)[] }
     if (wait) check(lib!.symbols.jg_timer_start(this.dev.handle))
-    const argv = d.order.map((o) => typeof o === 'number' ? bufs[o] : (o.startsWith('v') ? args.vals![Number(o.slice(1))] : Number(o)))
-    check(lib!.symbols[d.entry](this.dev.handle, ...argv))
+    if (this.program) {
+      const vals = args.vals ?? []
+      if (vals.some((x) => x === undefined)) throw new Error(`${vals}`)
+      const three = (v?: number[]) => v ? new Uint32Array([...v, 1, 1, 1].slice(0, 3)) : null
+      check(lib!.symbols.jg_program_call(this.program, new BigUint64Array(bufs), bufs.length, new Int32Array(vals), vals.length, three(args.global_size), three(args.local_size)))
+    } else {
+      const d = JSON.parse(new TextDecoder().decode(this.lib)) as { entry: keyof typeof SYMBOLS; order: (number | string)[] }
+      const argv = d.order.map((o) => typeof o === 'number' ? bufs[o] : (o.startsWith('v') ? args.vals![Number(o.slice(1))] : Number(o)))
+      check(lib!.symbols[d.entry](this.dev.handle, ...argv))
+    }
     if (wait) {
       const s = new Float64Array(1)
       check(await lib!.symbols.jg_timer_stop(this.dev.handle, s))
@@ -168,15 +214,15 @@ export class CUDAProgram extends Program {
   }
 }
 
-/** Kernel descriptors for CUDAProgram, written by the layers of llama_cuda.ts (one per entry point they call): the
- *  device has no code generator; an AST that reaches `render` has no hand-written kernel behind it. */
-export class CUDADescriptorRenderer extends Renderer {
-  override device = 'CUDA'
-  override has_local = true
-  static descriptor = (entry: keyof typeof SYMBOLS, order: (number | string)[]) => JSON.stringify({ entry, order })
-  override render = (name: string, _uops: unknown[]): string => {
-    throw new Error(`CUDA device: no hand-written kernel for the scheduled AST '${name}'; build the model from models/llama_cuda.ts`)
+/** The device's renderer is the reference's own CUDARenderer: an AST that the scheduler hands to `render` has no
+ *  hand-written kernel behind it and is generated, compiled (CUDACompiler) and launched (CUDAProgram) like on any
+ *  other compiled device.  The layers of llama_cuda.ts bypass it with kernel descriptors (one per entry point they
+ *  call), written by `descriptor`. */
+export class CUDADescriptorRenderer extends CUDARenderer {
+  constructor() {
+    super('sm_100')
   }
+  static descriptor = (entry: keyof typeof SYMBOLS, order: (number | string)[]) => JSON.stringify({ entry, order })
 }
 
 /** A captured kernel list replayed with one launch: the GraphRunner TinyJit asks `Compiled.graph` for
@@ -216,7 +262,7 @@ export class CUDA extends Compiled {
   handle: Deno.PointerValue = null
   ordinal: number
   constructor(device: string) {
-    super(device, undefined, new CUDADescriptorRenderer(), new Compiler(), undefined, undefined)
+    super(device, undefined, new CUDADescriptorRenderer(), new CUDACompiler(), undefined, undefined)
     this.ordinal = device.includes(':') ? Number(device.split(':')[1]) : 0
     this.allocator = new CUDAAllocator(this)
     this.runtime = CUDAProgram.bind(this) // per device: two CUDA:n devices in one process keep their own handles

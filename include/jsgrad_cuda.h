@@ -39,6 +39,7 @@ typedef struct jg_graph jg_graph;     /* a captured, replayable list of launches
 typedef struct jg_kvcache jg_kvcache; /* paged K/V pool of one model on one device */
 typedef struct jg_comm jg_comm;       /* tensor-parallel communicator of one rank */
 typedef struct jg_step jg_step;       /* one model's decode step as a single persistent kernel */
+typedef struct jg_program jg_program; /* one run-time compiled kernel loaded on one device */
 
 /* ---- Compiled: jsgrad/runtime/allocator.ts:166-191 (ctor/init/synchronize), device lookup
  *      jsgrad/device.ts:26-35 (`new DEVICES['CUDA']('CUDA:3')`: the ordinal is parsed from the device name). */
@@ -81,6 +82,26 @@ int jg_copyout_async(jg_dev* dev, void* pinned_host, uint64_t src, size_t nbytes
  *      `wait=true` is start -> calls -> stop; stop blocks and returns the elapsed device time in seconds. */
 int jg_timer_start(jg_dev* dev);
 int jg_timer_stop(jg_dev* dev, double* seconds);
+
+/* ---- Compiler / Program for generated source: jsgrad/runtime/allocator.ts:98-107 (Program), :121-139 (CompileError,
+ *      Compiler); the reference's own instance of the pair is jsgrad/runtime/ops_clang.ts:7-54.  The reference ships a
+ *      CUDA code generator (CUDARenderer, jsgrad/renderer/cstyle.ts:348-419) and no CUDA runtime; these entry points are
+ *      that runtime, for every scheduled AST the hand-written kernels below do not cover.
+ *      jg_cuda_compile: Compiler.compile — CUDA C source -> cubin for `arch` (null or "" = "sm_100a") through NVRTC; needs
+ *      no device; a source that does not compile is JG_EINVAL with the compiler's log in jg_last_error (CompileError).
+ *      The image is released with jg_cuda_image_free (its bytes may be kept in the engine's compile cache and loaded
+ *      again later).
+ *      jg_program_load: Program.init(name, lib) — `name` is the kernel function (`extern "C" __global__`).
+ *      jg_program_call: Program.call(bufs, {global_size, local_size, vals}) — the kernel receives every buffer as a
+ *      device pointer, then every variable as a 32-bit int (ops_clang.ts:44-52); global_size / local_size point at
+ *      three numbers each (null = 1, 1, 1) and become the grid and the block.  The launch is ordered on the device's
+ *      stream with all other kernels, is recorded by a graph capture and timed by jg_timer_start / jg_timer_stop. */
+int jg_cuda_compile(const char* src, const char* arch, uint8_t** image, uint64_t* size);
+int jg_cuda_image_free(uint8_t* image);
+int jg_program_load(jg_dev* dev, const char* name, const uint8_t* image, uint64_t size, jg_program** out);
+int jg_program_call(jg_program* program, const uint64_t* bufs, int32_t n_bufs, const int32_t* vals, int32_t n_vals,
+                    const uint32_t* global_size, const uint32_t* local_size);
+int jg_program_destroy(jg_program* program);
 
 /* ---- Compiled.graph / GraphRunner: jsgrad/engine/jit.ts:14-144 (batching of a captured kernel list) and
  *      CapturedJit replay jsgrad/engine/jit.ts:190-217.  Between begin and end every launch on `dev` is recorded

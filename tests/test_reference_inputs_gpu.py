@@ -35,13 +35,7 @@ def test_reference_test_inputs_agree_between_device_and_checker():
         m.close()
         llm.reset()
         dev = llm.model.dev
-        # empty cache: earlier cases must not leak into this one
-        llm.model._kv.close()
-        from denograd_b200.llama import KVCache
-        llm.model._kv = KVCache(dev, p["n_layers"], p["n_heads"], p["n_kv_heads"], p["dim"] // p["n_heads"], 64, 1)
-        for i, layer in enumerate(llm.model.layers):
-            layer.attention._kv = llm.model._kv
-        llm.model._forward_jit.clear(); llm.model._loop_graph.clear()
+        llm.model.new_cache()  # empty cache: earlier cases must not leak into this one
         llm.model.forward(np.array([[tok]], np.int32), start_pos, 0.0)
         logits = llm.model.last_logits(1)
         dl = float(np.abs(logits - ref_logits).max())
