@@ -53,7 +53,7 @@ __device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
 }
 
 template <int HD, int NREP>
-__global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a) {
+__global__ void __launch_bounds__(NREP * 32, NREP <= 4 ? 3 : 1) attn_chunk_kernel(const ChunkArgs a) {
   constexpr int LD = HD + 8;          // padded row: 32-bit fragment loads and ldmatrix rows fall on distinct banks
   constexpr int NT = NREP * 32;
   constexpr int KS = HD / 16;         // k-steps of q.k^T
@@ -109,12 +109,17 @@ __global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a
 #pragma unroll
     for (int n = 0; n < NS; n++) {
       s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
-      const __half* krow = Ks + (n * 8 + qr) * LD + qc;
+      // B fragments of two k-steps in one ldmatrix: four 8x8 blocks of the 8 positions n*8.., lane l names position
+      // n*8 + l%8 at dims 8*(l/8)
+      const uint32_t kaddr = (uint32_t)__cvta_generic_to_shared(Ks + (n * 8 + (lane & 7)) * LD + ((lane >> 3) << 3));
 #pragma unroll
-      for (int k = 0; k < KS; k++) {
-        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + k * 16);
-        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + k * 16 + 8);
+      for (int k = 0; k < KS; k += 2) {
+        uint32_t b0, b1, b2, b3;
+        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                     : "r"(kaddr + k * 32));
         mma_16816(s[n], qf[k], b0, b1);
+        mma_16816(s[n], qf[k + 1], b2, b3);
       }
       const int t = j * CH_KV + n * 8 + qc;
       s[n][0] = (t <= prow_a) ? __fmul_rn(s[n][0], a.scale) : -INFINITY;
@@ -156,12 +161,27 @@ __global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a
     const float n_a = fmaxf(m_a, t_a), n_b = fmaxf(m_b, t_b);
     if (n_a != m_a) { l_a = __fmul_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(m_a, n_a), log2e))); m_a = n_a; }
     if (n_b != m_b) { l_b = __fmul_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(m_b, n_b), log2e))); m_b = n_b; }
+    // exponents in place of the scores; when the whole warp's lie within (-125, 125) — every tile but the one on the
+    // diagonal, whose masked scores are -inf, and rows with a score 86 below their maximum — the short exp2 serves
+    bool mid = true;
 #pragma unroll
     for (int n = 0; n < NS; n++) {
-      l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][0], m_a), log2e)));
-      l_a = __fadd_rn(l_a, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][1], m_a), log2e)));
-      l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][2], m_b), log2e)));
-      l_b = __fadd_rn(l_b, jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][3], m_b), log2e)));
+      s[n][0] = __fmul_rn(__fsub_rn(s[n][0], m_a), log2e); s[n][1] = __fmul_rn(__fsub_rn(s[n][1], m_a), log2e);
+      s[n][2] = __fmul_rn(__fsub_rn(s[n][2], m_b), log2e); s[n][3] = __fmul_rn(__fsub_rn(s[n][3], m_b), log2e);
+      mid = mid && fabsf(s[n][0]) < 125.0f && fabsf(s[n][1]) < 125.0f && fabsf(s[n][2]) < 125.0f && fabsf(s[n][3]) < 125.0f;
+    }
+    if (__all_sync(0xffffffffu, mid)) {
+#pragma unroll
+      for (int n = 0; n < NS; n++) {
+        l_a = __fadd_rn(l_a, jg_xexp2_f32_mid(s[n][0])); l_a = __fadd_rn(l_a, jg_xexp2_f32_mid(s[n][1]));
+        l_b = __fadd_rn(l_b, jg_xexp2_f32_mid(s[n][2])); l_b = __fadd_rn(l_b, jg_xexp2_f32_mid(s[n][3]));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NS; n++) {
+        l_a = __fadd_rn(l_a, jg_xexp2_f32(s[n][0])); l_a = __fadd_rn(l_a, jg_xexp2_f32(s[n][1]));
+        l_b = __fadd_rn(l_b, jg_xexp2_f32(s[n][2])); l_b = __fadd_rn(l_b, jg_xexp2_f32(s[n][3]));
+      }
     }
     __syncthreads();  // the buffer read here is refilled two iterations on
   }
@@ -192,17 +212,29 @@ __global__ void __launch_bounds__(NREP * 32) attn_chunk_kernel(const ChunkArgs a
     float s[NS][4];
     score_tile(Kb + (j & 1) * CH_KV * LD, j, s);
     uint32_t pf[CH_KV / 16][4];
+    bool mid = true;
 #pragma unroll
     for (int n = 0; n < NS; n++) {
-      const float e0 = jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][0], m_a), log2e));
-      const float e1 = jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][1], m_a), log2e));
-      const float e2 = jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][2], m_b), log2e));
-      const float e3 = jg_xexp2_f32(__fmul_rn(__fsub_rn(s[n][3], m_b), log2e));
-      // masked scores are -inf: force an exact zero so that no unrelated cache row can leak through 0 * x
-      const float p0 = s[n][0] == -INFINITY ? 0.f : __fmul_rn(e0, rl_a), p1 = s[n][1] == -INFINITY ? 0.f : __fmul_rn(e1, rl_a);
-      const float p2 = s[n][2] == -INFINITY ? 0.f : __fmul_rn(e2, rl_b), p3 = s[n][3] == -INFINITY ? 0.f : __fmul_rn(e3, rl_b);
-      pf[n >> 1][(n & 1) * 2 + 0] = pack_h2(p0, p1);
-      pf[n >> 1][(n & 1) * 2 + 1] = pack_h2(p2, p3);
+      s[n][0] = __fmul_rn(__fsub_rn(s[n][0], m_a), log2e); s[n][1] = __fmul_rn(__fsub_rn(s[n][1], m_a), log2e);
+      s[n][2] = __fmul_rn(__fsub_rn(s[n][2], m_b), log2e); s[n][3] = __fmul_rn(__fsub_rn(s[n][3], m_b), log2e);
+      mid = mid && fabsf(s[n][0]) < 125.0f && fabsf(s[n][1]) < 125.0f && fabsf(s[n][2]) < 125.0f && fabsf(s[n][3]) < 125.0f;
+    }
+    if (__all_sync(0xffffffffu, mid)) {  // no masked score in the warp's tile: the short exp2, no zero test
+#pragma unroll
+      for (int n = 0; n < NS; n++) {
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_h2(__fmul_rn(jg_xexp2_f32_mid(s[n][0]), rl_a), __fmul_rn(jg_xexp2_f32_mid(s[n][1]), rl_a));
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_h2(__fmul_rn(jg_xexp2_f32_mid(s[n][2]), rl_b), __fmul_rn(jg_xexp2_f32_mid(s[n][3]), rl_b));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NS; n++) {
+        const float e0 = jg_xexp2_f32(s[n][0]), e1 = jg_xexp2_f32(s[n][1]), e2 = jg_xexp2_f32(s[n][2]), e3 = jg_xexp2_f32(s[n][3]);
+        // masked scores are -inf: force an exact zero so that no unrelated cache row can leak through 0 * x
+        const float p0 = s[n][0] == -INFINITY ? 0.f : __fmul_rn(e0, rl_a), p1 = s[n][1] == -INFINITY ? 0.f : __fmul_rn(e1, rl_a);
+        const float p2 = s[n][2] == -INFINITY ? 0.f : __fmul_rn(e2, rl_b), p3 = s[n][3] == -INFINITY ? 0.f : __fmul_rn(e3, rl_b);
+        pf[n >> 1][(n & 1) * 2 + 0] = pack_h2(p0, p1);
+        pf[n >> 1][(n & 1) * 2 + 1] = pack_h2(p2, p3);
+      }
     }
     const __half* Vs = Vb + (j & 1) * CH_KV * LD;
 #pragma unroll

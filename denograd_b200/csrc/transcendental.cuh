@@ -27,6 +27,23 @@ __device__ __forceinline__ float jg_xexp2_f32(float d) {
   return u;
 }
 
+// The same function, bit for bit, for arguments with |d| < 125 only (the caller checks; every score within 86 of its
+// row's maximum qualifies): the argument is finite, so the sanitising selects and the range patches are no-ops, and with
+// q in [-125, 125] both power-of-two factors and their product 2^q are normal numbers, so scaling the polynomial (a
+// value in (0.5, 2)) in one multiply or in two gives the same exact result.  Straight-line code: several calls interleave.
+__device__ __forceinline__ float jg_xexp2_f32_mid(float d) {
+  const int q = (int)__fadd_rn(d, d < 0.0f ? -0.5f : 0.5f);
+  const float s = __fsub_rn(d, (float)q);
+  float u = 0.1535920892e-3f;
+  u = __fadd_rn(__fmul_rn(u, s), 0.1339262701e-2f);
+  u = __fadd_rn(__fmul_rn(u, s), 0.9618384764e-2f);
+  u = __fadd_rn(__fmul_rn(u, s), 0.5550347269e-1f);
+  u = __fadd_rn(__fmul_rn(u, s), 0.2402264476e+0f);
+  u = __fadd_rn(__fmul_rn(u, s), 0.6931471825e+0f);
+  u = __fadd_rn(__fmul_rn(u, s), 1.0f);
+  return __fmul_rn(u, jg_pow2i(q));
+}
+
 // xexp2, fp16 branch: the same graph with every op in fp16 (int16 rintk, bounds 23 / -22).
 __device__ __forceinline__ __half jg_xexp2_f16(__half d) {
   const float df = __half2float(d);
