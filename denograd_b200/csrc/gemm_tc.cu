@@ -445,13 +445,26 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
   rc = cached_map(&px, x, a.M, a.K, TN, "activations");
   if (rc) return rc;
   const CUtensorMap tw0 = *pw0, tw1 = *pw1, tx = *px;
-  // split K over a cluster until the launch has CTAs for about two thirds of the SMs, keeping at least 8 k-blocks
-  // per CTA and the peers' partial sums within rank 0's pipeline buffers
+  // up to 128 rows (weight streaming): split K over a cluster until the launch has CTAs for about two thirds of the
+  // SMs, keeping at least 8 k-blocks per CTA and the peers' partial sums within rank 0's pipeline buffers
   const int tiles = ((a.M + TN - 1) / TN) * (a.N / TC_BM), n_kb = a.K / TC_BK;
   static int ks_env = -1;
   if (ks_env < 0) { const char* e = getenv("JG_TC_SPLITK"); ks_env = e ? atoi(e) : 0; }
   int ks = 1;
-  while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 && n_kb / (ks + 1) >= 8) ks++;
+  if (a.M > 128) {
+    // compute-bound tiles: the launch runs in waves of one CTA per SM, each costing its k-blocks (0.28 us apiece at
+    // the tensor peak) plus about 18 us of fill, epilogue and cluster reduction (measured cold at 512 and 1024 rows:
+    // qkv 36.9 us unsplit against 53.3 split in two, which makes 192 CTAs = two waves; wo 38.9 against 34.8; the
+    // down projection 96.3 against 69.7).  Take the split with the smallest estimate.
+    float best = 0.f;
+    for (int c = 1; c <= Cfg::MAX_KS && c <= 8 && n_kb / c >= 8; c++) {
+      const int waves = (tiles * c + dev->sm_count - 1) / dev->sm_count;
+      const float t = (float)waves * ((float)(n_kb / c) * 0.28f + 18.f);
+      if (c == 1 || t < best) { best = t; ks = c; }
+    }
+  } else {
+    while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 && n_kb / (ks + 1) >= 8) ks++;
+  }
   if (ks_env >= 1 && ks_env <= 8 && ks_env <= Cfg::MAX_KS && n_kb / ks_env >= 1) ks = ks_env;
   dev->tc_pending = true;
   cudaLaunchConfig_t cfg = {};
