@@ -362,6 +362,186 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI, W8>::THREADS) gemm_tc_kernel(co
   }
 }
 
+// ------------------------------------------------------------------------------------------------ CTA pairs
+// The same projection with tcgen05.mma.cta_group::2 for many activation rows: two CTAs of a cluster (2,1,1) hold two
+// adjacent 128-row weight tiles and share one 256-row activation tile, each fetching only its half of it (rows
+// 128 * rank ..): the MMAs, issued by rank 0 for both, read A from each CTA's own shared memory into that CTA's tensor
+// memory and the two halves of B from both.  Per k-block a CTA moves 32 KB (48 KB for the gate / up pair) instead of 48 KB
+// (64 KB) for the same MMA work, and the ring is 7 (4) stages deep instead of 4 (3).
+// Signals: every TMA load of either CTA completes on rank 0's full barrier (cp.async.bulk.tensor with .cta_group::2 may
+// name the peer's barrier; no multicast anywhere); the MMA issuer commits each stage to both CTAs' empty barriers and
+// the final accumulation to both CTAs' accumulator barriers (one tcgen05.commit per CTA).  Tensor memory is allocated
+// and released by warp 1 of both CTAs together (.cta_group::2).  No split-K.
+template <int EPI>
+struct Tc2Cfg {
+  static constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
+  static constexpr int TN = 256;                        // activation rows of the pair's tile
+  static constexpr int NCOL = NW * TN;
+  static constexpr int EPW = 4;
+  static constexpr int THREADS = tc_threads(EPW);
+  static constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;       // 16 KB: this CTA's weight rows
+  static constexpr uint32_t B_BYTES = (TN / 2) * TC_BK * 2;    // 16 KB: this CTA's half of the activation tile
+  static constexpr uint32_t STAGE_BYTES = NW * A_BYTES + B_BYTES;
+  static constexpr int STAGES_FIT = (225 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
+  static constexpr uint32_t TMEM_COLS = NCOL <= 256 ? 256 : 512;
+  static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
+};
+
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, uint32_t bar_cluster_addr) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at shared::cluster address `bar` once the pair's MMAs issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(Tc2Cfg<EPI>::THREADS) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w0,
+                                                                            const __grid_constant__ CUtensorMap tm_w1,
+                                                                            const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
+  using Cfg = Tc2Cfg<EPI>;
+  constexpr int NW = Cfg::NW, STAGES = Cfg::STAGES, TN = Cfg::TN;
+  constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, TMEM_COLS = Cfg::TMEM_COLS;
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ uint32_t s_tmem;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  // grid (2 x activation tiles, pairs of weight tiles): the two CTAs of a pair are neighbours along x (a launch whose
+  // pairs lay along y was refused as a cluster misconfiguration), and the pairs that share weights follow each other
+  const int tok0 = (int)(blockIdx.x >> 1) * TN, feat0 = ((int)blockIdx.y * 2 + (int)rank) * TC_BM;
+  const int nk = a.K / TC_BK;
+  pdl_launch();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {  // warp 1 of both CTAs together: the same columns of both CTAs' tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_barrier();  // the peer's barriers exist before anything is signalled across
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = s_tmem;
+  bool acc_ok = false;
+
+  if (warp == 0 && lane == 0) {
+    // ---- producer of this CTA's tiles; all completions go to rank 0's full barrier, which rank 0 arms for both CTAs
+    const int pre = nk < STAGES ? nk : STAGES;
+    if (a.w_late) pdl_wait();
+    auto full0 = [&](int s) { return map_to_rank(smem_u32(&full_bar[s]), 0); };
+    auto load_w = [&](int i, int s) {
+      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+      if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
+      tma_load_2d_pair(st, &tm_w0, i * TC_BK, feat0, full0(s));
+      if (NW == 2) tma_load_2d_pair(st + A_BYTES, &tm_w1, i * TC_BK, feat0, full0(s));
+    };
+    auto load_x = [&](int i, int s) {
+      tma_load_2d_pair(tiles + (size_t)s * STAGE_BYTES + NW * A_BYTES, &tm_x, i * TC_BK, tok0 + (int)rank * (TN / 2), full0(s));
+    };
+    for (int i = 0; i < pre; i++) load_w(i, i);
+    pdl_wait();  // X comes from the previous kernel
+    for (int i = 0; i < pre; i++) load_x(i, i);
+    for (int i = pre; i < nk; i++) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1)) { atomicCAS(a.err, 0, 1); break; }
+      load_w(i, s);
+      load_x(i, s);
+    }
+  } else if (warp == 1 && lane == 0 && rank == 0) {
+    // ---- MMA issuer of the pair: 4 x (256 x 256 x 16) per stage and matrix
+    const uint32_t idesc = (1u << 4) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)((2 * TC_BM) >> 4) << 24);
+    bool ok = true;
+    pdl_wait();
+    for (int i = 0; i < nk; i++) {
+      const int s = i % STAGES;
+      if (!mbar_wait(&full_bar[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 2); ok = false; break; }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+      const uint64_t bdesc = umma_desc(st + NW * A_BYTES);
+#pragma unroll
+      for (int w = 0; w < NW; w++) {
+        const uint64_t adesc = umma_desc(st + w * A_BYTES);
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; k++)
+          umma_f16_pair(tmem_base + w * TN, adesc + 2 * k, bdesc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit_pair(smem_u32(&empty_bar[s]));                  // this CTA's stage is free ...
+      umma_commit_pair(map_to_rank(smem_u32(&empty_bar[s]), 1));  // ... and the peer's
+    }
+    if (ok) {
+      umma_commit_pair(smem_u32(&acc_bar));
+      umma_commit_pair(map_to_rank(smem_u32(&acc_bar), 1));
+    }
+  } else if (warp >= 2) {
+    pdl_wait();  // the residual is read and Y written only after the previous kernel is done with them
+    acc_ok = mbar_wait(&acc_bar, 0);
+    if (!acc_ok && lane == 0) atomicCAS(a.err, 0, 3);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  }
+
+  // lane l of quarter q is weight row feat0 + 32q + l of this CTA; the four warps of a quarter split the columns
+  const int q = warp & 3, row = q * 32 + lane;
+  const int part = (warp - 2) >> 2;
+  constexpr int TN_PER = TN / Cfg::EPW;
+  const int tn_lo = part * TN_PER, tn_hi = tn_lo + TN_PER;
+  const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+  if (warp >= 2 && acc_ok) {
+    const int feat = feat0 + row;
+#pragma unroll 1
+    for (int c0 = tn_lo; c0 < tn_hi; c0 += 16) {
+      float r0[16], r1[16];
+      tmem_ld16(t_lane + c0, r0);
+      if (NW == 2) tmem_ld16(t_lane + TN + c0, r1);
+      if (feat < a.N) {
+        __half res[16];
+        if (EPI == TC_RESIDUAL) {
+#pragma unroll
+          for (int j = 0; j < 16; j++)
+            res[j] = (tok0 + c0 + j < a.M) ? a.residual[(size_t)(tok0 + c0 + j) * a.N + feat] : __float2half_rn(0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+          const int tok = tok0 + c0 + j;
+          if (tok < a.M) {
+            const size_t o = (size_t)tok * a.N + feat;
+            if (EPI == TC_PARTIAL) { a.y32[o] = r0[j]; continue; }
+            __half v = __float2half_rn(r0[j]);
+            if (EPI == TC_RESIDUAL) v = hadd1(res[j], v);
+            if (EPI == TC_SWIGLU) v = jg_silu_mul(v, __float2half_rn(r1[j]));
+            a.y[o] = v;
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_barrier();  // neither CTA leaves, or gives its tensor memory back, while the other may still use either's
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -493,8 +673,65 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
   return jg_after_launch(dev, "gemm_tc");
 }
 
+// CTA pairs (gemm_tc_pair_kernel): fp16 weights, more than 128 rows, an even number of weight tiles.  Used for the
+// gate / up pair, the one projection that cannot split K and that the pairs serve 2-7 % faster at every row count
+// measured (8B shapes, us per launch, pairs against single CTAs: 256 rows 80 / 86, 512 rows 131 / 139, 768 rows 188 /
+// 191, 1536 rows 307 / 311, 2048 rows 427 / 423); the single-matrix projections are level or slower in pairs (they lose
+// their split-K at few rows: down projection at 512 rows 90 against 70 us), so they take them only when forced
+// (JG_TC_PAIR=2; JG_TC_PAIR=0 turns the pairs off).
+template <int EPI>
+static int launch_tc_pair(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
+  using Cfg = Tc2Cfg<EPI>;
+  auto kern = gemm_tc_pair_kernel<EPI>;
+  static bool attr_set[8] = {false, false, false, false, false, false, false, false};
+  const int slot = dev->ordinal & 7;
+  if (!attr_set[slot]) {
+    JG_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+    attr_set[slot] = true;
+  }
+  const CUtensorMap *pw0, *pw1, *px;
+  int rc = cached_map(&pw0, w0, a.N, a.K, TC_BM, "weights");
+  if (rc) return rc;
+  rc = cached_map(&pw1, Cfg::NW == 2 ? w1 : w0, a.N, a.K, TC_BM, "weights (second matrix)");
+  if (rc) return rc;
+  rc = cached_map(&px, x, a.M, a.K, Cfg::TN / 2, "activations (half tile)");
+  if (rc) return rc;
+  const CUtensorMap tw0 = *pw0, tw1 = *pw1, tx = *px;
+  dev->tc_pending = true;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * ((a.M + Cfg::TN - 1) / Cfg::TN), a.N / (2 * TC_BM), 1);
+  cfg.blockDim = dim3(Cfg::THREADS);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = dev->stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  attr[na].id = cudaLaunchAttributeClusterDimension;
+  attr[na].val.clusterDim.x = 2;
+  attr[na].val.clusterDim.y = 1;
+  attr[na].val.clusterDim.z = 1;
+  na++;
+  if (dev->pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    na++;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tw0, tw1, tx, a);
+  if (e != cudaSuccess) return jg_cuda_fail(e, "gemm_tc_pair", __FILE__, __LINE__);
+  return jg_after_launch(dev, "gemm_tc_pair");
+}
+
+static bool tc_pair_wanted(const TcArgs& a, bool gate_up) {
+  static int env = -1;
+  if (env < 0) { const char* e = getenv("JG_TC_PAIR"); env = e ? atoi(e) : 1; }
+  if (env == 0 || a.s0 != nullptr || a.M <= 128 || (a.N / TC_BM) % 2 != 0) return false;
+  return env == 2 || gate_up;
+}
+
 template <int EPI>
 static int launch_tc_rows(jg_dev* dev, const void* x, const void* w0, const void* w1, const TcArgs& a) {
+  if (tc_pair_wanted(a, EPI == TC_SWIGLU)) return launch_tc_pair<EPI>(dev, x, w0, w1, a);
   if (a.s0 != nullptr) {  // int8 weights: used from 65 rows on (fewer go to the mma.sync kernel)
     if (a.M <= 128) return launch_tc<128, EPI, true>(dev, x, w0, w1, a);
     return launch_tc<256, EPI, true>(dev, x, w0, w1, a);

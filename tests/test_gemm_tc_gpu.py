@@ -1,5 +1,9 @@
 """GPU parity of the tcgen05 / TMA projection (3 activation rows and more) against fp32 host arithmetic and, on
 sampled rows, against the CPU checker's sequential fp32 accumulation."""
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 
@@ -13,7 +17,8 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 256, 512), (200, 384, 1024), (512, 6144, 4096), (300, 4096, 14336),
                                    # few rows: weight streaming with split-K over a cluster (8, 2, 3, 4 CTAs per tile)
                                    (3, 256, 512), (5, 2048, 2048), (9, 256, 512), (16, 4096, 4096), (32, 1024, 14336), (48, 6144, 4096), (64, 4096, 4096),
-                                   (512, 4096, 4096)])
+                                   # gate / up in CTA pairs (tcgen05 cta_group::2), the last tile partly out of range
+                                   (512, 4096, 4096), (300, 1024, 512)])
 def test_dense_projection_all_epilogues(dev, M, N, K):
     rng = np.random.default_rng(M + N + K)
     x = rng.standard_normal((M, K)).astype(np.float16)
@@ -42,3 +47,13 @@ def test_dense_projection_all_epilogues(dev, M, N, K):
         up = (x.astype(np.float32) @ w3.astype(np.float32).T).astype(np.float16)
         assert_reduction_close(y.numpy(), O.swiglu(ref, up), max_ulp=3, max_frac=0.12, what="tcgen05 swiglu")
     dev.synchronize()
+
+
+def test_cta_pairs_forced_for_every_epilogue():
+    """JG_TC_PAIR=2 sends every fp16 projection above 128 rows through the paired kernel (by default only the gate / up
+    pair takes it).  The choice is read once per process, hence the child process."""
+    pick = "512-6144-4096 or 300-4096-14336 or 512-4096-4096 or 300-1024-512"
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.abspath(__file__), "-q", "-x", "-m", "gpu", "-k",
+                        f"test_dense_projection_all_epilogues and ({pick})"], env=dict(os.environ, JG_TC_PAIR="2"),
+                       capture_output=True, text=True, timeout=900, cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "4 passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
