@@ -130,7 +130,7 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
-template <int TN, int EPI, bool W8 = false>
+template <int TN, int EPI, bool W8 = false, bool HALF = false>
 struct TcCfg {
   static constexpr int NW = (EPI == TC_SWIGLU) ? 2 : 1;
   static constexpr uint32_t RAW_BYTES = W8 ? TC_BM * TC_BK : 0;  // the int8 tile as it arrives (8 KB)
@@ -144,7 +144,8 @@ struct TcCfg {
   static constexpr uint32_t B_BYTES = TN * TC_BK * 2;
   static constexpr uint32_t STAGE_BYTES = NW * (A_BYTES + RAW_BYTES) + B_BYTES;  // [A0 | A1 | B | raw0 | raw1]
   static constexpr int CONV_WARPS = W8 ? 4 * NW : 0;  // epilogue warps that convert during the main loop
-  static constexpr int STAGES_FIT = (225 * 1024) / STAGE_BYTES;
+  // HALF: a ring of half the shared memory, so that two CTAs share an SM (few activation rows only)
+  static constexpr int STAGES_FIT = ((HALF ? 110 : 225) * 1024) / STAGE_BYTES;
   static constexpr int STAGES = STAGES_FIT > 10 ? 10 : STAGES_FIT;
   static constexpr uint32_t TMEM_COLS = NCOL <= 32 ? 32 : (NCOL <= 64 ? 64 : (NCOL <= 128 ? 128 : (NCOL <= 256 ? 256 : 512)));
   static constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + 1024;
@@ -168,11 +169,11 @@ __device__ __forceinline__ void tc_dequant16(const uint4& raw, __half2 s2, uint3
   }
 }
 
-template <int TN, int EPI, bool W8 = false>
-__global__ void __launch_bounds__(TcCfg<TN, EPI, W8>::THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
+template <int TN, int EPI, bool W8 = false, bool HALF = false>
+__global__ void __launch_bounds__(TcCfg<TN, EPI, W8, HALF>::THREADS, HALF ? 2 : 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w0,
                                                              const __grid_constant__ CUtensorMap tm_w1,
                                                              const __grid_constant__ CUtensorMap tm_x, const TcArgs a) {
-  using Cfg = TcCfg<TN, EPI, W8>;
+  using Cfg = TcCfg<TN, EPI, W8, HALF>;
   constexpr int NW = Cfg::NW, STAGES = Cfg::STAGES, NCOL = Cfg::NCOL;
   constexpr uint32_t A_BYTES = Cfg::A_BYTES, STAGE_BYTES = Cfg::STAGE_BYTES, TMEM_COLS = Cfg::TMEM_COLS;
   constexpr uint32_t RAW_BYTES = Cfg::RAW_BYTES, B_BYTES = Cfg::B_BYTES, RAW_OFF = NW * A_BYTES + B_BYTES;
@@ -607,10 +608,10 @@ static int cached_map(const CUtensorMap** out, const void* base, uint64_t rows, 
   return JG_OK;
 }
 
-template <int TN, int EPI, bool W8 = false>
+template <int TN, int EPI, bool W8 = false, bool HALF = false>
 static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1, TcArgs a) {
-  using Cfg = TcCfg<TN, EPI, W8>;
-  auto kern = gemm_tc_kernel<TN, EPI, W8>;
+  using Cfg = TcCfg<TN, EPI, W8, HALF>;
+  auto kern = gemm_tc_kernel<TN, EPI, W8, HALF>;
   static bool attr_set[8] = {false, false, false, false, false, false, false, false};
   const int slot = dev->ordinal & 7;
   if (!attr_set[slot]) {
@@ -643,7 +644,7 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
       if (c == 1 || t < best) { best = t; ks = c; }
     }
   } else {
-    while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 && n_kb / (ks + 1) >= 8) ks++;
+    while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 * (HALF ? 2 : 1) && n_kb / (ks + 1) >= 8) ks++;
   }
   if (ks_env >= 1 && ks_env <= 8 && ks_env <= Cfg::MAX_KS && n_kb / ks_env >= 1) ks = ks_env;
   dev->tc_pending = true;
@@ -735,6 +736,17 @@ static int launch_tc_rows(jg_dev* dev, const void* x, const void* w0, const void
   if (a.s0 != nullptr) {  // int8 weights: used from 65 rows on (fewer go to the mma.sync kernel)
     if (a.M <= 128) return launch_tc<128, EPI, true>(dev, x, w0, w1, a);
     return launch_tc<256, EPI, true>(dev, x, w0, w1, a);
+  }
+  // Up to 32 rows the single-matrix projections run with half-size rings, two CTAs to an SM and twice the split-K:
+  // a qkv or wo launch is a few hundred KB per CTA, mostly fixed cost (measured cold and alone at 32 rows on the 8B
+  // shapes: qkv 29.2 -> 22.6 us, wo 19.4 -> 18.5 at split 4, down 36.9 -> 37.9; the batch-32 decode step 4.27 -> 4.16 ms,
+  // batch 16 4.04 -> 3.93).  JG_TC_HALF=0 turns it off.  The gate / up pair keeps the full ring (three stages would
+  // not cover its loads).
+  static int half_env = -1;
+  if (half_env < 0) { const char* e = getenv("JG_TC_HALF"); half_env = e ? atoi(e) : 1; }
+  if (half_env && EPI != TC_SWIGLU && a.M <= 32) {
+    if (a.M <= 16) return launch_tc<16, EPI, false, true>(dev, x, w0, w1, a);
+    return launch_tc<32, EPI, false, true>(dev, x, w0, w1, a);
   }
   if (a.M <= 16) return launch_tc<16, EPI>(dev, x, w0, w1, a);
   if (a.M <= 32) return launch_tc<32, EPI>(dev, x, w0, w1, a);
