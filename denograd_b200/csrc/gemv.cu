@@ -516,6 +516,15 @@ static bool w8_tc() {  // JG_W8_TC=0: int8 projections of more than 64 rows are 
   return v != 0;
 }
 
+// int8 weights: from this many rows on the tcgen05 kernel with the conversion inside it is ahead of the mma.sync
+// kernel (8B int8 decode, ms per step, mma.sync / tcgen05: 8 rows 3.79 / 4.82, 16 rows 4.30 / 4.76, 24 rows 5.34 /
+// 4.87, 32 rows 5.73 / 4.96, 48 rows 10.7 / 6.65, 64 rows 11.3 / 6.84).  JG_W8_TC_MIN overrides.
+static int w8_tc_min_rows() {
+  static int v = -1;
+  if (v < 0) { const char* e = getenv("JG_W8_TC_MIN"); v = e ? atoi(e) : 20; if (v < 3) v = 3; }
+  return v;
+}
+
 template <bool W8, int EPI, bool NORM>
 static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   if (EPI == EPI_PEER || EPI == EPI_PUSH) {  // fused with its all-reduce: matrix-vector kernels only (up to 8 rows)
@@ -528,8 +537,8 @@ static int dispatch_m(jg_dev* dev, const GemvArgs& a, const char* name) {
   }
   if (!W8 && !NORM && EPI != EPI_LOGITS && (a.M > 64 || (a.M >= tc_min_rows() && jg_gemm_tc_fits(a.N, a.K))))
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K, nullptr, nullptr);
-  // int8 weights and more rows than the mma.sync kernel takes: the tcgen05 kernel with the conversion inside it
-  if (W8 && !NORM && EPI != EPI_LOGITS && a.M > 64 && jg_gemm_tc_fits(a.N, a.K) && w8_tc())
+  // int8 weights and enough rows: the tcgen05 kernel with the conversion inside it
+  if (W8 && !NORM && EPI != EPI_LOGITS && a.M >= w8_tc_min_rows() && jg_gemm_tc_fits(a.N, a.K) && w8_tc())
     return jg_gemm_tc(dev, EPI, a.x, a.w0, a.w1, EPI == EPI_PARTIAL ? (void*)a.y32 : (void*)a.y, a.residual, a.M, a.N, a.K, a.s0, a.s1);
   // int8 weights, up to 8 rows: the kernel that keeps the rows in shared memory and streams the weights through the
   // tensor cores without a barrier in its k loop; it also takes the norm in its prologue
