@@ -13,4 +13,4 @@ def test_every_mode_prints_its_lines(capsys):
     microbench.main(["decode-attention", "--batch", "9", "--context", "300"] + small)
     out = capsys.readouterr().out.splitlines()
     assert len(out) == 7 and all(" us " in line for line in out), out
-    assert out[4].split()[1] == "layer"
+    assert out[4].split()[2] == "layer"
