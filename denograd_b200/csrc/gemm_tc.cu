@@ -648,7 +648,9 @@ static int launch_tc(jg_dev* dev, const void* x, const void* w0, const void* w1,
       if (c == 1 || t < best) { best = t; ks = c; }
     }
   } else {
-    while (ks < 8 && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 * (HALF ? 2 : 1) && n_kb / (ks + 1) >= 8) ks++;
+    // half-size rings (two CTAs per SM): CTAs for four thirds of the SMs, but no more than four to a tile — beyond
+    // that the cluster reduction costs more than the shorter streams save (wo at 32 rows: 18.5 us split in 4, 20.5 in 7)
+    while (ks < (HALF ? 4 : 8) && ks < Cfg::MAX_KS && tiles * ks * 3 < dev->sm_count * 2 * (HALF ? 2 : 1) && n_kb / (ks + 1) >= 8) ks++;
   }
   if (ks_env >= 1 && ks_env <= 8 && ks_env <= Cfg::MAX_KS && n_kb / ks_env >= 1) ks = ks_env;
   dev->tc_pending = true;
