@@ -17,7 +17,7 @@
 // epilogue.  No cluster multicast is used anywhere: every CTA fetches its own tiles.
 // int8 weights (Int8Linear with many rows, jsgrad/models/llama3.ts:35): the weight tile arrives by TMA as int8 (8 KB
 // instead of 16), and the warps that will later run the epilogue — idle during the main loop — turn it into the fp16
-// tile the MMA reads: one to four threads per weight row of the tile, half(q) * scale rounded once per element, written in the
+// tile the MMA reads: thread = one weight row of the tile, half(q) * scale rounded once per element, written in the
 // 128-byte swizzle pattern TMA would have produced (16-byte chunk c of row r lands at chunk c ^ (r % 8)), followed by a
 // proxy fence.  The weights cross HBM as int8 once per pass; no fp16 copy of a matrix is ever written.
 // Every mbarrier wait is bounded: a wait that does not complete sets an error word and the CTA winds down (cluster
@@ -143,8 +143,9 @@ struct TcCfg {
   static constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;  // 16 KB
   static constexpr uint32_t B_BYTES = TN * TC_BK * 2;
   static constexpr uint32_t STAGE_BYTES = NW * (A_BYTES + RAW_BYTES) + B_BYTES;  // [A0 | A1 | B | raw0 | raw1]
-  // int8: every epilogue warp converts during the main loop; a weight row's four 16-weight pieces of a k-block are
-  // shared by CONV_SPLIT threads (EPW / NW of them: 1, 2 or 4)
+  // int8: every epilogue warp converts during the main loop, in CONV_SPLIT groups (EPW / NW: 1, 2 or 4) of four warps per
+  // matrix (one thread per weight row); group g takes the k-blocks g, g + CONV_SPLIT, ..., so that many k-blocks are being
+  // converted at once and a group's fixed costs (barrier wait, proxy fence, arrival) hide behind the other groups' work
   static constexpr int CONV_SPLIT = W8 ? (EPW / NW >= 1 ? EPW / NW : 1) : 1;
   static constexpr int CONV_WARPS = W8 ? 4 * NW * CONV_SPLIT : 0;
   // HALF: a ring of half the shared memory, so that two CTAs share an SM (few activation rows only)
@@ -196,7 +197,7 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI, W8, HALF>::THREADS, HALF ? 2 : 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
     if (W8)
-      for (int s = 0; s < STAGES; s++) { mbar_init(&raw_full[s], 1); mbar_init(&a_full[s], Cfg::CONV_WARPS); }
+      for (int s = 0; s < STAGES; s++) { mbar_init(&raw_full[s], 1); mbar_init(&a_full[s], 4 * NW); }
     mbar_init(&acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -270,18 +271,18 @@ __global__ void __launch_bounds__(TcCfg<TN, EPI, W8, HALF>::THREADS, HALF ? 2 : 
     if (W8 && warp - 2 < Cfg::CONV_WARPS) {
       // ---- converter: this thread's weight row of every stage, int8 -> half(q) * scale -> swizzled fp16 tile
       constexpr int CS = Cfg::CONV_SPLIT;
-      const int cw = warp - 2, w = cw / (4 * CS), idx = cw % (4 * CS), r = (idx & 3) * 32 + lane, piece0 = (idx >> 2) * (4 / CS);
+      const int cw = warp - 2, w = cw / (4 * CS), idx = cw % (4 * CS), r = (idx & 3) * 32 + lane, group = idx >> 2;
       if (a.w_late) pdl_wait();
       const __half2 sc = __half2half2((w == 0 ? a.s0 : a.s1)[min(feat0 + r, a.N - 1)]);
       const uint32_t row_off = (uint32_t)(r >> 3) * 1024u + (uint32_t)(r & 7) * 128u;
-      for (int i = 0; i < nk; i++) {
+      for (int i = group; i < nk; i += CS) {
         const int s = i % STAGES;
         if (!mbar_wait(&raw_full[s], (i / STAGES) & 1)) { atomicCAS(a.err, 0, 1); break; }
         unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
         const uint4* src = reinterpret_cast<const uint4*>(st + RAW_OFF + w * RAW_BYTES + r * TC_BK);
         unsigned char* dst = st + w * A_BYTES + row_off;
 #pragma unroll
-        for (int j = piece0; j < piece0 + 4 / CS; j++) {  // 16 weights -> two 16-byte chunks (2j, 2j + 1) of the row
+        for (int j = 0; j < 4; j++) {  // 16 weights -> two 16-byte chunks (2j, 2j + 1) of the row
           uint32_t d[8];
           tc_dequant16(src[j], sc, d);
           *reinterpret_cast<uint4*>(dst + (((2 * j) ^ (r & 7)) << 4)) = make_uint4(d[0], d[1], d[2], d[3]);
