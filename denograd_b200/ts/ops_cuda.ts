@@ -212,6 +212,11 @@ export class CUDAProgram extends Program {
       return s[0]
     }
   }
+  /** Unloads a compiled kernel's module (descriptor programs hold nothing). */
+  destroy = () => {
+    if (this.program) check(lib!.symbols.jg_program_destroy(this.program))
+    this.program = null
+  }
 }
 
 /** The device's renderer is the reference's own CUDARenderer: an AST that the scheduler hands to `render` has no
