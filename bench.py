@@ -584,8 +584,8 @@ def extra_legs(rig: Rig, args, repeats: int) -> dict:
         rig.release()
     if rig.world > 1 or args.model != "8B" or args.quant != "float16" or LAYERS_OVERRIDE:
         return out
-    # int8 weights (untied int8 output layer): batch 1 and 8 at a 2048-token context, and the 2048-token prompt itself
-    for b in (1, 8):
+    # int8 weights (untied int8 output layer): batch 1, 8 and 32 at a 2048-token context, and the 2048-token prompt itself
+    for b in (1, 8, 32):
         llm = rig.llama("8B", "int8", (2048 + (R + 1) * kb + W + 64 + 63) // 64 * 64, b)
         out[f"int8_bs{b}_ctx2048"] = strip(decode_leg(rig, llm, b, 2048, kb, W, R, tied8, True, check_steps=4))
         if b == 1:
